@@ -1,0 +1,519 @@
+// One-off calibration kernels: the exact integer histogram of block-normalised gradients, the
+// block-period scores and the Lloyd-Max accumulation / MSE kernels.
+//
+// Reference behaviour:
+//   histogram   kernels/exact_histogram_fused_kernel.cu:17-85
+//   scores      kernels/period_variance_kernel.cu:13-165 and the host post-ops at :242, :311-317, :392-395
+//   Lloyd-Max   kernels/lloyd_max_fused_kernel.cu:50-195
+//
+// All of them are one read of the gradient from HBM (the reference reads it twice per kernel and,
+// for the adjacent-log score, twice per candidate period). A warp owns a block; the second look at
+// a block's elements, where one is needed, comes from L1.
+#include "common.cuh"
+
+namespace gefen {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+static int persistent_grid(long long groups, int groups_per_cta, int ctas_per_sm) {
+    long long ctas = (groups + groups_per_cta - 1) / groups_per_cta;
+    const long long cap = static_cast<long long>(sm_count()) * ctas_per_sm;
+    if (ctas > cap) ctas = cap;
+    if (ctas < 1) ctas = 1;
+    return static_cast<int>(ctas);
+}
+
+// NaN-ignoring max |g| over one block, by one warp (GROUP=32) or one CTA (GROUP=256).
+template <typename S, int GROUP>
+__device__ __forceinline__ float block_absmax(const S* g, long long period, int tig, float* red) {
+    float m = 0.0f;
+    for (long long i = tig; i < period; i += GROUP) m = fmaxf(m, fabsf(ScalarIO<S>::load(g + i)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (GROUP > 32) {
+        __syncthreads();
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+        __syncthreads();
+        m = red[0];
+#pragma unroll
+        for (int w = 1; w < kWarps; ++w) m = fmaxf(m, red[w]);
+    }
+    return m;
+}
+
+// ------------------------------------------------------------------------------- histogram
+// bin = clamp(floor((g/absmax + 1) * bins/2), 0, bins-1); counts are integers and therefore
+// independent of the order of accumulation. Increments into the CTA's shared histogram are
+// aggregated across the lanes of a warp that hit the same bin (one atomic per distinct bin).
+template <typename S, int GROUP>
+__global__ void __launch_bounds__(kThreads) histogram_kernel(const S* __restrict__ g, long long period,
+                                                             long long num_blocks, int bins,
+                                                             unsigned long long* __restrict__ counts) {
+    __shared__ unsigned int hist[4096];
+    __shared__ float red[kWarps];
+    for (int i = threadIdx.x; i < bins; i += kThreads) hist[i] = 0u;
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31;
+    const int tig = GROUP == 32 ? lane : static_cast<int>(threadIdx.x);
+    const long long group0 = GROUP == 32 ? static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5)
+                                         : static_cast<long long>(blockIdx.x);
+    const long long stride = GROUP == 32 ? static_cast<long long>(gridDim.x) * kWarps : static_cast<long long>(gridDim.x);
+    const float scale = 0.5f * static_cast<float>(bins);
+    unsigned long long since_flush = 0;
+
+    for (long long b = group0; b < num_blocks; b += stride) {
+        const S* gb = g + b * period;
+        const float absmax = block_absmax<S, GROUP>(gb, period, tig, red);
+        const long long rounds = (period + GROUP - 1) / GROUP;
+        for (long long r = 0; r < rounds; ++r) {
+            const long long i = r * GROUP + tig;
+            const bool active = i < period;
+            int bin = -1;
+            if (active) {
+                const float v = ScalarIO<S>::load(gb + i);
+                float x = 0.0f;
+                if (absmax > 0.0f) x = v / absmax;
+                bin = static_cast<int>(floorf((x + 1.0f) * scale));
+                bin = bin < 0 ? 0 : (bin >= bins ? bins - 1 : bin);
+            }
+            const unsigned int amask = __ballot_sync(0xffffffffu, active);
+            if (active) {
+                const unsigned int peers = __match_any_sync(amask, bin);
+                if (lane == (__ffs(peers) - 1)) atomicAdd(&hist[bin], static_cast<unsigned int>(__popc(peers)));
+            }
+        }
+        since_flush += static_cast<unsigned long long>(period);
+        if (GROUP > 32 && since_flush > 0x7fffffffull) {  // keep the 32-bit counters from wrapping
+            __syncthreads();
+            for (int i = threadIdx.x; i < bins; i += kThreads) {
+                if (hist[i]) { atomicAdd(&counts[i], static_cast<unsigned long long>(hist[i])); hist[i] = 0u; }
+            }
+            __syncthreads();
+            since_flush = 0;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < bins; i += kThreads) {
+        if (hist[i]) atomicAdd(&counts[i], static_cast<unsigned long long>(hist[i]));
+    }
+}
+
+// ------------------------------------------------------------------------------- period scores
+// Sum over one block of log(x + eps) in fp64, x = v*v in fp64 unless the input is already squared
+// (reference: period_variance_kernel.cu:124-139). `invalid` counts non-positive log inputs.
+template <typename S, bool SQUARED>
+__device__ __forceinline__ double log_term(const S* p, double eps, unsigned long long& invalid) {
+    const double raw = static_cast<double>(ScalarIO<S>::load(p));
+    const double x = (SQUARED ? raw : raw * raw) + eps;
+    if (x <= 0.0) { ++invalid; return 0.0; }
+    return log(x);
+}
+
+// period >= 64: one warp per block. period < 64: one thread per block.
+template <typename S, bool SQUARED>
+__global__ void __launch_bounds__(kThreads) block_logsum_kernel(const S* __restrict__ values, long long period,
+                                                                long long num_blocks, double eps,
+                                                                double* __restrict__ sums,
+                                                                unsigned long long* __restrict__ invalid_out) {
+    unsigned long long invalid = 0;
+    if (period >= 64) {
+        const int lane = threadIdx.x & 31;
+        const long long w0 = static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+        const long long stride = static_cast<long long>(gridDim.x) * kWarps;
+        for (long long b = w0; b < num_blocks; b += stride) {
+            const S* vb = values + b * period;
+            double acc = 0.0;
+            for (long long i = lane; i < period; i += 32) acc += log_term<S, SQUARED>(vb + i, eps, invalid);
+            acc = warp_sum(acc);
+            if (lane == 0) sums[b] = acc;
+        }
+    } else {
+        const long long t0 = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+        const long long stride = static_cast<long long>(gridDim.x) * kThreads;
+        for (long long b = t0; b < num_blocks; b += stride) {
+            const S* vb = values + b * period;
+            double acc = 0.0;
+            for (long long i = 0; i < period; ++i) acc += log_term<S, SQUARED>(vb + i, eps, invalid);
+            sums[b] = acc;
+        }
+    }
+    if (invalid) atomicAdd(invalid_out, invalid);
+}
+
+// partial[c] = sum over this CTA's slice of |S[j+1]/P - S[j]/P|, fixed order => reproducible.
+__global__ void __launch_bounds__(kThreads) adjacent_diff_partial_kernel(const double* __restrict__ sums,
+                                                                         long long num_pairs, double period,
+                                                                         double* __restrict__ partial) {
+    __shared__ double red[kWarps];
+    const long long per_cta = (num_pairs + gridDim.x - 1) / gridDim.x;
+    const long long begin = static_cast<long long>(blockIdx.x) * per_cta;
+    long long end = begin + per_cta;
+    if (end > num_pairs) end = num_pairs;
+    double acc = 0.0;
+    for (long long j = begin + threadIdx.x; j < end; j += kThreads) {
+        const double cur = sums[j] / period;
+        const double nxt = sums[j + 1] / period;
+        acc += fabs(nxt - cur);
+    }
+    acc = warp_sum(acc);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int w = 0; w < kWarps; ++w) t += red[w];
+        partial[blockIdx.x] = t;
+    }
+}
+
+__global__ void adjacent_diff_final_kernel(const double* __restrict__ partial, int n_partial, double num_pairs,
+                                           const unsigned long long* __restrict__ invalid,
+                                           double* __restrict__ stats) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        double t = 0.0;
+        for (int i = 0; i < n_partial; ++i) t += partial[i];
+        stats[0] = t / num_pairs;
+        stats[1] = static_cast<double>(*invalid);
+    }
+}
+
+// Mean within-block variance / coefficient of variation of x (= v or v*v), fp32 sums
+// (reference: period_variance_kernel.cu:13-106). One warp per block.
+template <typename S, bool SQUARED, bool COV>
+__global__ void __launch_bounds__(kThreads) block_moment_kernel(const S* __restrict__ values, long long period,
+                                                                long long num_blocks, double* __restrict__ stats) {
+    const int lane = threadIdx.x & 31;
+    const long long w0 = static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+    const long long stride = static_cast<long long>(gridDim.x) * kWarps;
+    for (long long b = w0; b < num_blocks; b += stride) {
+        const S* vb = values + b * period;
+        float sx = 0.0f, sx2 = 0.0f;
+        for (long long i = lane; i < period; i += 32) {
+            const float v = ScalarIO<S>::load(vb + i);
+            const float x = SQUARED ? v : v * v;
+            sx += x;
+            sx2 = fmaf(x, x, sx2);
+        }
+        sx = warp_sum(sx);
+        sx2 = warp_sum(sx2);
+        if (lane == 0) {
+            const float mean = sx / static_cast<float>(period);
+            float var = sx2 / static_cast<float>(period);
+            var -= mean * mean;
+            if (var < 0.0f) var = 0.0f;
+            if (!COV) {
+                atomicAdd(stats, static_cast<double>(var));
+            } else if (mean < 0.0f) {
+                atomicAdd(stats + 2, 1.0);
+            } else if (mean > 0.0f) {
+                atomicAdd(stats, static_cast<double>(sqrtf(var) / mean));
+                atomicAdd(stats + 1, 1.0);
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------- Lloyd-Max
+// E-step: per codebook entry, the sum of the normalised values assigned to it and their count
+// (reference: lloyd_max_fused_kernel.cu:50-118). Sums are fp32 atomics (order-dependent in the
+// reference too); counts are exact.
+template <typename S, int GROUP>
+__global__ void __launch_bounds__(kThreads) lloyd_accumulate_kernel(const S* __restrict__ g, long long period,
+                                                                    long long num_blocks, const unsigned char* ws,
+                                                                    int k, float* __restrict__ sums,
+                                                                    unsigned long long* __restrict__ counts) {
+    __shared__ float thr[kMaxCodebook];
+    __shared__ float ocb[kMaxCodebook];
+    __shared__ float ssum[kMaxCodebook];
+    __shared__ unsigned int scnt[kMaxCodebook];
+    __shared__ float red[kWarps];
+    thr[threadIdx.x] = reinterpret_cast<const float*>(ws + kWsThresholdOff)[threadIdx.x];
+    ocb[threadIdx.x] = reinterpret_cast<const float*>(ws + kWsCodebookOff)[threadIdx.x];
+    ssum[threadIdx.x] = 0.0f;
+    scnt[threadIdx.x] = 0u;
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int tig = GROUP == 32 ? lane : static_cast<int>(threadIdx.x);
+    const long long group0 = GROUP == 32 ? static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5)
+                                         : static_cast<long long>(blockIdx.x);
+    const long long stride = GROUP == 32 ? static_cast<long long>(gridDim.x) * kWarps : static_cast<long long>(gridDim.x);
+    unsigned long long since_flush = 0;
+    for (long long b = group0; b < num_blocks; b += stride) {
+        const S* gb = g + b * period;
+        const float absmax = block_absmax<S, GROUP>(gb, period, tig, red);
+        for (long long i = tig; i < period; i += GROUP) {
+            const float v = ScalarIO<S>::load(gb + i);
+            float x = 0.0f;
+            if (absmax > 0.0f) x = v / absmax;
+            const int e = entry_exact(x, thr, ocb, k);
+            atomicAdd(&ssum[e], x);
+            atomicAdd(&scnt[e], 1u);
+        }
+        since_flush += static_cast<unsigned long long>(period);
+        if (GROUP > 32 && since_flush > 0x7fffffffull) {
+            __syncthreads();
+            if (threadIdx.x < k && scnt[threadIdx.x]) {
+                atomicAdd(&counts[threadIdx.x], static_cast<unsigned long long>(scnt[threadIdx.x]));
+                scnt[threadIdx.x] = 0u;
+            }
+            __syncthreads();
+            since_flush = 0;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < k) {
+        atomicAdd(&sums[threadIdx.x], ssum[threadIdx.x]);
+        atomicAdd(&counts[threadIdx.x], static_cast<unsigned long long>(scnt[threadIdx.x]));
+    }
+}
+
+// Logging MSE of assigning with the old codebook and reconstructing with the new one
+// (reference: lloyd_max_fused_kernel.cu:120-195).
+template <typename S, int GROUP>
+__global__ void __launch_bounds__(kThreads) lloyd_mse_kernel(const S* __restrict__ g, long long period,
+                                                             long long num_blocks, const unsigned char* old_ws,
+                                                             const float* __restrict__ new_codebook, int k,
+                                                             float* __restrict__ mse_norm, float* __restrict__ mse_orig) {
+    __shared__ float thr[kMaxCodebook];
+    __shared__ float ncb[kMaxCodebook];
+    __shared__ float red[kWarps];
+    __shared__ float red2[2][kWarps];
+    __shared__ float ocb[kMaxCodebook];
+    thr[threadIdx.x] = reinterpret_cast<const float*>(old_ws + kWsThresholdOff)[threadIdx.x];
+    ocb[threadIdx.x] = reinterpret_cast<const float*>(old_ws + kWsCodebookOff)[threadIdx.x];
+    ncb[threadIdx.x] = new_codebook[threadIdx.x < k ? threadIdx.x : k - 1];
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int tig = GROUP == 32 ? lane : static_cast<int>(threadIdx.x);
+    const long long group0 = GROUP == 32 ? static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5)
+                                         : static_cast<long long>(blockIdx.x);
+    const long long stride = GROUP == 32 ? static_cast<long long>(gridDim.x) * kWarps : static_cast<long long>(gridDim.x);
+    float en = 0.0f, eo = 0.0f;
+    for (long long b = group0; b < num_blocks; b += stride) {
+        const S* gb = g + b * period;
+        const float absmax = block_absmax<S, GROUP>(gb, period, tig, red);
+        for (long long i = tig; i < period; i += GROUP) {
+            const float v = ScalarIO<S>::load(gb + i);
+            float x = 0.0f;
+            if (absmax > 0.0f) x = v / absmax;
+            const float err = x - ncb[entry_exact(x, thr, ocb, k)];
+            en = fmaf(err, err, en);
+            const float oe = err * absmax;
+            eo = fmaf(oe, oe, eo);
+        }
+    }
+    en = warp_sum(en);
+    eo = warp_sum(eo);
+    if (lane == 0) { red2[0][threadIdx.x >> 5] = en; red2[1][threadIdx.x >> 5] = eo; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float a = 0.0f, c = 0.0f;
+        for (int w = 0; w < kWarps; ++w) { a += red2[0][w]; c += red2[1][w]; }
+        atomicAdd(mse_norm, a);
+        atomicAdd(mse_orig, c);
+    }
+}
+
+// ------------------------------------------------------------------------------- host side
+static int check_flat(const void* values, int dtype, int64_t numel, int64_t period) {
+    GEFEN_CHECK_ARG(values != nullptr || numel == 0, "Expected a non-null tensor.");
+    GEFEN_CHECK_ARG(is_float_dtype(dtype), "Expected a floating-point tensor.");
+    GEFEN_CHECK_ARG(period > 0, "Expected a positive period.");
+    GEFEN_CHECK_ARG(numel >= 0 && numel % period == 0, "Expected tensor length to be divisible by period.");
+    return GEFEN_B200_OK;
+}
+
+#define GEFEN_DISPATCH_S(dtype, ...)                                                       \
+    switch (dtype) {                                                                       \
+        case GEFEN_B200_F32: { using S = float; __VA_ARGS__; } break;                      \
+        case GEFEN_B200_F16: { using S = __half; __VA_ARGS__; } break;                     \
+        case GEFEN_B200_BF16: { using S = __nv_bfloat16; __VA_ARGS__; } break;             \
+        default: { using S = double; __VA_ARGS__; } break;                                 \
+    }
+
+constexpr int kMaxPartials = 1024;
+
+static int adjacent_score(const void* values, int dtype, int64_t numel, int64_t period, bool squared, double eps,
+                          double* stats, double* block_sums, cudaStream_t stream) {
+    const int64_t nb = numel / period;
+    unsigned long long* invalid = reinterpret_cast<unsigned long long*>(block_sums + nb);
+    double* partial = block_sums + nb + 1;
+    GEFEN_CHECK_CUDA(cudaMemsetAsync(invalid, 0, sizeof(unsigned long long), stream));
+    const int grid = period >= 64 ? persistent_grid(nb, kWarps, 8) : persistent_grid(nb, kThreads, 8);
+    GEFEN_DISPATCH_S(dtype, {
+        if (squared)
+            block_logsum_kernel<S, true><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(values), period, nb, eps, block_sums, invalid);
+        else
+            block_logsum_kernel<S, false><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(values), period, nb, eps, block_sums, invalid);
+    });
+    GEFEN_CHECK_CUDA(cudaGetLastError());
+    const int64_t pairs = nb - 1;
+    int n_partial = static_cast<int>((pairs + 4095) / 4096);
+    if (n_partial > kMaxPartials) n_partial = kMaxPartials;
+    if (n_partial < 1) n_partial = 1;
+    adjacent_diff_partial_kernel<<<n_partial, kThreads, 0, stream>>>(block_sums, pairs, static_cast<double>(period), partial);
+    GEFEN_CHECK_CUDA(cudaGetLastError());
+    adjacent_diff_final_kernel<<<1, 32, 0, stream>>>(partial, n_partial, static_cast<double>(pairs), invalid, stats);
+    GEFEN_CHECK_CUDA(cudaGetLastError());
+    return GEFEN_B200_OK;
+}
+
+}  // namespace gefen
+
+using namespace gefen;
+
+extern "C" {
+
+int gefen_b200_exact_histogram(const void* grad_flat, int grad_dtype, int64_t numel, int64_t period,
+                               int64_t* bin_counts, int histogram_bins, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    GEFEN_CHECK_ARG(bin_counts != nullptr, "Expected a non-null bin_counts.");
+    GEFEN_CHECK_ARG(histogram_bins >= 1 && histogram_bins <= 4096, "Expected histogram size in [1, 4096].");
+    GEFEN_CHECK_ARG(period > 0, "Expected period to be positive.");
+    GEFEN_CHECK_ARG(grad_flat != nullptr || numel == 0, "Expected a non-null grad_flat.");
+    GEFEN_CHECK_ARG(is_float_dtype(grad_dtype), "Unsupported gradient dtype tag %d.", grad_dtype);
+    GEFEN_CHECK_ARG(numel >= 0 && numel % period == 0, "Expected grad_flat.numel() to be divisible by period.");
+    const int64_t nb = numel / period;
+    if (nb == 0) return GEFEN_B200_OK;
+    unsigned long long* counts = reinterpret_cast<unsigned long long*>(bin_counts);
+    if (period <= 8192) {
+        const int grid = persistent_grid(nb, kWarps, 4);
+        GEFEN_DISPATCH_S(grad_dtype, histogram_kernel<S, 32><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, histogram_bins, counts));
+    } else {
+        const int grid = persistent_grid(nb, 1, 4);
+        GEFEN_DISPATCH_S(grad_dtype, histogram_kernel<S, 256><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, histogram_bins, counts));
+    }
+    GEFEN_CHECK_CUDA(cudaGetLastError());
+    return GEFEN_B200_OK;
+}
+
+int gefen_b200_average_within_block_variance(const void* values, int dtype, int64_t numel, int64_t period,
+                                             int input_is_squared, double* stats, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int rc = check_flat(values, dtype, numel, period);
+    if (rc != GEFEN_B200_OK) return rc;
+    GEFEN_CHECK_ARG(stats != nullptr, "Expected a non-null stats buffer.");
+    GEFEN_CHECK_CUDA(cudaMemsetAsync(stats, 0, sizeof(double), stream));
+    const int64_t nb = numel / period;
+    if (nb == 0) return GEFEN_B200_OK;
+    const int grid = persistent_grid(nb, kWarps, 8);
+    GEFEN_DISPATCH_S(dtype, {
+        if (input_is_squared) block_moment_kernel<S, true, false><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(values), period, nb, stats);
+        else block_moment_kernel<S, false, false><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(values), period, nb, stats);
+    });
+    GEFEN_CHECK_CUDA(cudaGetLastError());
+    return GEFEN_B200_OK;
+}
+
+int gefen_b200_average_within_block_coefficient_of_variation(const void* values, int dtype, int64_t numel,
+                                                             int64_t period, int input_is_squared, double* stats,
+                                                             void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int rc = check_flat(values, dtype, numel, period);
+    if (rc != GEFEN_B200_OK) return rc;
+    GEFEN_CHECK_ARG(stats != nullptr, "Expected a non-null stats buffer.");
+    GEFEN_CHECK_CUDA(cudaMemsetAsync(stats, 0, 3 * sizeof(double), stream));
+    const int64_t nb = numel / period;
+    if (nb == 0) return GEFEN_B200_OK;
+    const int grid = persistent_grid(nb, kWarps, 8);
+    GEFEN_DISPATCH_S(dtype, {
+        if (input_is_squared) block_moment_kernel<S, true, true><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(values), period, nb, stats);
+        else block_moment_kernel<S, false, true><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(values), period, nb, stats);
+    });
+    GEFEN_CHECK_CUDA(cudaGetLastError());
+    return GEFEN_B200_OK;
+}
+
+int64_t gefen_b200_period_scratch_doubles(int64_t numel, int64_t period) {
+    if (period <= 0 || numel < 0) return 0;
+    return numel / period + 1 + kMaxPartials;
+}
+
+int gefen_b200_average_adjacent_log_block_mean_difference(const void* values, int dtype, int64_t numel,
+                                                          int64_t period, int input_is_squared, double epsilon,
+                                                          double* stats, double* block_sums, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int rc = check_flat(values, dtype, numel, period);
+    if (rc != GEFEN_B200_OK) return rc;
+    GEFEN_CHECK_ARG(epsilon > 0.0, "Expected a positive epsilon.");
+    GEFEN_CHECK_ARG(numel / period >= 2, "Expected at least two blocks to compare adjacent block means.");
+    GEFEN_CHECK_ARG(stats != nullptr && block_sums != nullptr, "Expected non-null stats and block_sums.");
+    return adjacent_score(values, dtype, numel, period, input_is_squared != 0, epsilon, stats, block_sums, stream);
+}
+
+int gefen_b200_period_scan(const void* values, int dtype, int64_t numel, int input_is_squared, double epsilon,
+                           const int64_t* host_periods, int n_periods, double* stats, double* block_sums,
+                           void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    GEFEN_CHECK_ARG(n_periods >= 0, "Expected a non-negative number of periods.");
+    if (n_periods == 0) return GEFEN_B200_OK;
+    GEFEN_CHECK_ARG(host_periods != nullptr && stats != nullptr && block_sums != nullptr,
+                    "Expected non-null periods, stats and block_sums.");
+    GEFEN_CHECK_ARG(epsilon > 0.0, "Expected a positive epsilon.");
+    for (int i = 0; i < n_periods; ++i) {
+        int rc = check_flat(values, dtype, numel, host_periods[i]);
+        if (rc != GEFEN_B200_OK) return rc;
+        GEFEN_CHECK_ARG(numel / host_periods[i] >= 2, "Expected at least two blocks for period %lld.",
+                        static_cast<long long>(host_periods[i]));
+    }
+    for (int i = 0; i < n_periods; ++i) {
+        int rc = adjacent_score(values, dtype, numel, host_periods[i], input_is_squared != 0, epsilon, stats + 2 * i,
+                                block_sums, stream);
+        if (rc != GEFEN_B200_OK) return rc;
+    }
+    return GEFEN_B200_OK;
+}
+
+int gefen_b200_lloyd_accumulate(const void* grad_flat, int grad_dtype, int64_t numel, int64_t period,
+                                const float* codebook, int codebook_size, const void* codebook_ws, float* sums,
+                                int64_t* counts, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int rc = check_flat(grad_flat, grad_dtype, numel, period);
+    if (rc != GEFEN_B200_OK) return rc;
+    GEFEN_CHECK_ARG(sums != nullptr && counts != nullptr, "Expected non-null sums and counts.");
+    const void* ws = nullptr;
+    rc = resolve_codebook_ws(codebook, codebook_size, codebook_ws, stream, &ws);
+    if (rc != GEFEN_B200_OK) return rc;
+    const int64_t nb = numel / period;
+    if (nb == 0) return GEFEN_B200_OK;
+    unsigned long long* cnt = reinterpret_cast<unsigned long long*>(counts);
+    const unsigned char* wsb = static_cast<const unsigned char*>(ws);
+    if (period <= 8192) {
+        const int grid = persistent_grid(nb, kWarps, 4);
+        GEFEN_DISPATCH_S(grad_dtype, lloyd_accumulate_kernel<S, 32><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, wsb, codebook_size, sums, cnt));
+    } else {
+        const int grid = persistent_grid(nb, 1, 4);
+        GEFEN_DISPATCH_S(grad_dtype, lloyd_accumulate_kernel<S, 256><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, wsb, codebook_size, sums, cnt));
+    }
+    GEFEN_CHECK_CUDA(cudaGetLastError());
+    return GEFEN_B200_OK;
+}
+
+int gefen_b200_lloyd_mse(const void* grad_flat, int grad_dtype, int64_t numel, int64_t period,
+                         const float* old_codebook, const float* new_codebook, int codebook_size,
+                         const void* old_codebook_ws, float* mse_normalized_sum, float* mse_original_sum,
+                         void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int rc = check_flat(grad_flat, grad_dtype, numel, period);
+    if (rc != GEFEN_B200_OK) return rc;
+    GEFEN_CHECK_ARG(new_codebook != nullptr && mse_normalized_sum != nullptr && mse_original_sum != nullptr,
+                    "Expected non-null new_codebook and outputs.");
+    const void* ws = nullptr;
+    rc = resolve_codebook_ws(old_codebook, codebook_size, old_codebook_ws, stream, &ws);
+    if (rc != GEFEN_B200_OK) return rc;
+    const int64_t nb = numel / period;
+    if (nb == 0) return GEFEN_B200_OK;
+    const unsigned char* wsb = static_cast<const unsigned char*>(ws);
+    if (period <= 8192) {
+        const int grid = persistent_grid(nb, kWarps, 4);
+        GEFEN_DISPATCH_S(grad_dtype, lloyd_mse_kernel<S, 32><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, wsb, new_codebook, codebook_size, mse_normalized_sum, mse_original_sum));
+    } else {
+        const int grid = persistent_grid(nb, 1, 4);
+        GEFEN_DISPATCH_S(grad_dtype, lloyd_mse_kernel<S, 256><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, wsb, new_codebook, codebook_size, mse_normalized_sum, mse_original_sum));
+    }
+    GEFEN_CHECK_CUDA(cudaGetLastError());
+    return GEFEN_B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,837 @@
+// The steady-state Gefen step on sm_100a.
+//
+// What one block (`period` consecutive elements sharing a magnitude and a second moment) goes
+// through, in the reference's arithmetic (kernels/automatic_gefen_fused_kernel.cu:239-318 for the
+// AdamW form, :320-407 for period 1, :169-237 for GefenMuon; kernels/automatic_vmean_kernel.cu:12-51
+// for the second moment; gefen.py:1280-1281 for the decoupled weight decay):
+//
+//   m_i   = beta1 * (mag * cb[code_i]) + (1 - beta1) * g_i              (fp32)
+//   mag'  = max_i |m_i|            stored rounded to the state dtype
+//   code' = nearest codebook entry of m_i / mag'   (IEEE divide by the un-rounded fp32 mag')
+//   p_i  -= cb[code'_i] * mag' * step * lr,   step = (1/bc1) / (sqrt(v/bc2) + eps)
+//
+// Two kernels:
+//  * step_vec_kernel  - the fast path. One warp owns one block and keeps its R*256 updated
+//    momenta in registers between the absmax reduction and the re-encode, so codes, gradients
+//    and params cross HBM exactly once (8 B/element in bf16, 14 B/element in fp32). 128-bit
+//    loads/stores; codebook, thresholds and the quantisation table arrive in shared memory by
+//    one bulk (TMA) copy; reductions are warp shuffles; no __syncthreads after set-up.
+//  * step_generic_kernel - any period, alignment and dtype (fp64 included): two passes with
+//    scalar accesses, the second pass re-reading from L1/L2.
+#include "common.cuh"
+
+namespace gefen {
+
+// fp32 contraction choices. They reproduce what nvcc emits for the reference source when it is
+// compiled with its own flags (-O3, fmad on): a*b + c*d becomes fma(a, b, c*d) and p - a*b becomes
+// fma(-a, b, p). The CPU oracle makes the same choices explicitly.
+__device__ __forceinline__ float ema_update(float beta, float cur, float omb, float g) {
+    return fmaf(beta, cur, omb * g);
+}
+
+struct StepLaunch {
+    const gefen_b200_step_tensor_t* table;  // device table, or nullptr: use `single`
+    int n_tensors;
+    long long total_blocks;
+    const unsigned char* ws;  // codebook workspace
+    const float* stepsize;    // optional precomputed per-block step (single tensor only)
+};
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kSmemWs = GEFEN_B200_CODEBOOK_WS_BYTES;
+constexpr int kSmemRep = 256 * 32 * 4;  // codebook replicated once per bank
+
+struct SmemView {
+    const float* cb;      // 256
+    const float* thr;     // 256
+    const uint32_t* lut;  // kLutWords
+    const float* rep;     // 256 x 32, entry e for lane l at rep[e*32 + l]
+    int k;                // true codebook size
+};
+
+// Stages the workspace with one bulk copy and builds the per-bank codebook copy.
+// Returns false (uniformly for the CTA) if the copy did not land in time.
+template <bool REP>
+__device__ __forceinline__ bool stage_tables(const unsigned char* ws, unsigned char* smem, SmemView& view) {
+    __shared__ uint64_t bar;
+    __shared__ int ok;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        mbar_expect_tx(&bar, kSmemWs);
+        bulk_copy_g2s(smem, ws, kSmemWs, &bar);
+        ok = mbar_wait_bounded(&bar, 0) ? 1 : 0;
+    }
+    __syncthreads();
+    view.cb = reinterpret_cast<const float*>(smem + kWsCodebookOff);
+    view.thr = reinterpret_cast<const float*>(smem + kWsThresholdOff);
+    view.lut = reinterpret_cast<const uint32_t*>(smem + kWsLutOff);
+    view.rep = nullptr;
+    view.k = 1;
+    if (!ok) return false;
+    view.k = static_cast<int>(view.lut[kLutSizeWord]);
+    if (REP) {
+        float* rep = reinterpret_cast<float*>(smem + kSmemWs);
+        for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) rep[i] = view.cb[i >> 5];
+        view.rep = rep;
+        __syncthreads();
+    }
+    return true;
+}
+
+template <bool REP>
+__device__ __forceinline__ float dequant(const SmemView& s, uint32_t code, int lane) {
+    return REP ? s.rep[code * 32 + lane] : s.cb[code];
+}
+
+__device__ __forceinline__ uint32_t quantize(const SmemView& s, float x) {
+    bool slow;
+    int e = lut_query(x, s.lut, &slow);
+    if (slow) e = entry_exact(x, s.thr, s.cb, s.k);
+    return static_cast<uint32_t>(e);
+}
+
+__device__ __forceinline__ float adam_step_size(float v, float bc1, float bc2, float eps) {
+    const float corrected = v / bc2;
+    return (1.0f / bc1) / (sqrtf(corrected) + eps);
+}
+
+// Finds the tensor that owns global block `gb` (table sorted by first_block).
+__device__ __forceinline__ int find_tensor(const gefen_b200_step_tensor_t* table, int n, long long gb) {
+    int lo = 0, hi = n - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (table[mid].first_block <= gb) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+
+// --------------------------------------------------------------------------- vector IO
+// A "chunk" is 8 consecutive elements: 8 code bytes, 16 B of bf16/f16 or 32 B of fp32.
+template <typename S> struct Chunk;
+template <> struct Chunk<__nv_bfloat16> {
+    uint4 raw;
+    __device__ __forceinline__ void load(const void* base, long long chunk) {
+        raw = reinterpret_cast<const uint4*>(base)[chunk];
+    }
+    __device__ __forceinline__ void store(void* base, long long chunk) const {
+        reinterpret_cast<uint4*>(base)[chunk] = raw;
+    }
+    __device__ __forceinline__ void unpack(float (&f)[8]) const {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+    }
+    __device__ __forceinline__ void pack(const float (&f)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        raw = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+template <> struct Chunk<__half> {
+    uint4 raw;
+    __device__ __forceinline__ void load(const void* base, long long chunk) {
+        raw = reinterpret_cast<const uint4*>(base)[chunk];
+    }
+    __device__ __forceinline__ void store(void* base, long long chunk) const {
+        reinterpret_cast<uint4*>(base)[chunk] = raw;
+    }
+    __device__ __forceinline__ void unpack(float (&f)[8]) const {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            f[2 * i] = v.x;
+            f[2 * i + 1] = v.y;
+        }
+    }
+    __device__ __forceinline__ void pack(const float (&f)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        raw = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+template <> struct Chunk<float> {
+    float4 lo, hi;
+    __device__ __forceinline__ void load(const void* base, long long chunk) {
+        lo = reinterpret_cast<const float4*>(base)[2 * chunk];
+        hi = reinterpret_cast<const float4*>(base)[2 * chunk + 1];
+    }
+    __device__ __forceinline__ void store(void* base, long long chunk) const {
+        reinterpret_cast<float4*>(base)[2 * chunk] = lo;
+        reinterpret_cast<float4*>(base)[2 * chunk + 1] = hi;
+    }
+    __device__ __forceinline__ void unpack(float (&f)[8]) const {
+        f[0] = lo.x; f[1] = lo.y; f[2] = lo.z; f[3] = lo.w;
+        f[4] = hi.x; f[5] = hi.y; f[6] = hi.z; f[7] = hi.w;
+    }
+    __device__ __forceinline__ void pack(const float (&f)[8]) {
+        lo = make_float4(f[0], f[1], f[2], f[3]);
+        hi = make_float4(f[4], f[5], f[6], f[7]);
+    }
+};
+
+// --------------------------------------------------------------------------- fast path
+// One warp, one block of t.period = 8 * nchunks elements, nchunks <= 32 * R.
+template <typename S, int R, bool REP>
+__device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& t, long long b, const float* stepsize,
+                                                const SmemView& s, int lane) {
+    const int nchunks = static_cast<int>(t.period >> 3);
+    const long long chunk0 = b * nchunks;  // chunk index of the block start, in units of 8 elements
+    const uint2* codes_in = reinterpret_cast<const uint2*>(t.codes) + chunk0;
+    uint2* codes_out = reinterpret_cast<uint2*>(t.codes) + chunk0;
+    const bool muon = (t.flags & GEFEN_B200_STEP_MUON) != 0;
+
+    const float beta1 = t.beta1;
+    const float omb1 = 1.0f - beta1;
+    const float old_mag = load_state(t.mag, b, t.mag_dtype);
+
+    float upd[R][8];
+    float absmax = 0.0f;
+    float sumsq = 0.0f;
+
+    // ---- pass over codes and gradients (the only read of both)
+    uint2 craw[R];
+    Chunk<S> graw[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int c = r * 32 + lane;
+        if (c < nchunks) {
+            craw[r] = codes_in[c];
+            graw[r].load(t.g, chunk0 + c);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int c = r * 32 + lane;
+        if (c < nchunks) {
+            float g[8];
+            graw[r].unpack(g);
+            const uint32_t cw[2] = {craw[r].x, craw[r].y};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t code = (cw[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+                const float cur = old_mag * dequant<REP>(s, code, lane);
+                const float u = ema_update(beta1, cur, omb1, g[i]);
+                upd[r][i] = u;
+                absmax = max_abs_nan(absmax, u);
+                sumsq = fmaf(g[i], g[i], sumsq);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) upd[r][i] = 0.0f;
+        }
+    }
+    absmax = warp_max_nan(absmax);
+
+    // ---- second moment (optionally fused) and the step size
+    float step = 0.0f;
+    if (!muon) {
+        if (stepsize != nullptr) {
+            step = stepsize[b];
+        } else {
+            float v;
+            if (t.flags & GEFEN_B200_STEP_FUSE_VMEAN) {
+                const float mean_sq = warp_sum(sumsq) / static_cast<float>(t.period);
+                const float prev = load_state(t.v, b, t.v_dtype);
+                const float nv = fmaf(t.beta2, prev, (1.0f - t.beta2) * mean_sq);
+                v = 0.0f;
+                if (lane == 0) v = store_state(t.v, b, t.v_dtype, nv);
+                v = __shfl_sync(0xffffffffu, v, 0);
+            } else {
+                v = load_state(t.v, b, t.v_dtype);
+            }
+            step = adam_step_size(v, t.bc1, t.bc2, t.eps);
+        }
+    }
+
+    // ---- rare: a NaN or Inf in the block. The reference's max ignores NaN; redo it that way and
+    // let the exact (threshold) quantiser handle non-finite quotients.
+    bool exact_path = false;
+    if (!(absmax <= 3.0e38f)) {
+        float m = 0.0f;
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(upd[r][i]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        absmax = m;
+        exact_path = true;
+    }
+    __syncwarp();  // every lane has read the old magnitude
+    if (lane == 0) store_state(t.mag, b, t.mag_dtype, absmax);
+
+    const bool nonzero = absmax > 0.0f;
+    const bool fastdiv = !exact_path && div_range_ok(absmax);
+    const float rinv = fastdiv ? 1.0f / absmax : 0.0f;
+    const bool do_update = muon || t.lr != 0.0f;
+    const bool wd = (t.flags & GEFEN_B200_STEP_WEIGHT_DECAY) != 0;
+    const bool nesterov = (t.flags & GEFEN_B200_STEP_NESTEROV) != 0;
+
+    // ---- re-encode and update
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int c = r * 32 + lane;
+        if (c < nchunks) {
+            Chunk<S> praw;
+            if (!muon && do_update) praw.load(t.p, chunk0 + c);
+            uint32_t cw[2] = {0u, 0u};
+            float q[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float u = upd[r][i];
+                float x = 0.0f;
+                if (nonzero) x = fastdiv ? div_by_block_constant(u, absmax, rinv) : u / absmax;
+                const uint32_t code = exact_path ? static_cast<uint32_t>(entry_exact(x, s.thr, s.cb, s.k))
+                                                 : quantize(s, x);
+                cw[i >> 2] |= code << (8 * (i & 3));
+                q[i] = dequant<REP>(s, code, lane) * absmax;
+            }
+            codes_out[c] = make_uint2(cw[0], cw[1]);
+            if (muon) {
+                if (nesterov) {
+                    // torch: m.mul_(momentum).add_(g, alpha=1-momentum) on the rounded momentum
+                    // (reference: gefen_muon.py:312-314); alpha travels in t.beta2.
+                    Chunk<S> g2;
+                    g2.load(t.g, chunk0 + c);
+                    float g[8];
+                    g2.unpack(g);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float m1 = ScalarIO<S>::round(ScalarIO<S>::round(q[i]) * beta1);
+                        q[i] = fmaf(t.beta2, g[i], m1);
+                    }
+                }
+                Chunk<S> out;
+                out.pack(q);
+                out.store(t.p, chunk0 + c);
+            } else if (do_update) {
+                float pv[8];
+                praw.unpack(pv);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float pi = pv[i];
+                    if (wd) pi = ScalarIO<S>::round(pi * t.wd_mul);
+                    pv[i] = fmaf(-(q[i] * step), t.lr, pi);
+                }
+                praw.pack(pv);
+                praw.store(t.p, chunk0 + c);
+            }
+        }
+    }
+}
+
+template <typename S, int R, bool REP>
+__global__ void __launch_bounds__(kThreads) step_vec_kernel(const __grid_constant__ StepLaunch L,
+                                                            const __grid_constant__ gefen_b200_step_tensor_t single) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    SmemView s;
+    if (!stage_tables<REP>(L.ws, smem, s)) return;
+
+    __shared__ gefen_b200_step_tensor_t wcache[kWarps];  // the tensor each warp is working on
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const long long warp_global = static_cast<long long>(blockIdx.x) * kWarps + warp;
+    const long long warp_stride = static_cast<long long>(gridDim.x) * kWarps;
+    long long cached_first = 0, cached_end = 0;
+    for (long long gb = warp_global; gb < L.total_blocks; gb += warp_stride) {
+        if (L.table == nullptr) {
+            warp_block_step<S, R, REP>(single, gb, L.stepsize, s, lane);
+        } else {
+            if (gb < cached_first || gb >= cached_end) {
+                const int ti = find_tensor(L.table, L.n_tensors, gb);
+                constexpr int kWords = sizeof(gefen_b200_step_tensor_t) / 4;
+                const uint32_t* src = reinterpret_cast<const uint32_t*>(L.table + ti);
+                uint32_t* dst = reinterpret_cast<uint32_t*>(&wcache[warp]);
+                __syncwarp();
+                if (lane < kWords) dst[lane] = src[lane];
+                __syncwarp();
+                cached_first = wcache[warp].first_block;
+                cached_end = cached_first + wcache[warp].num_blocks;
+            }
+            warp_block_step<S, R, REP>(wcache[warp], gb - cached_first, nullptr, s, lane);
+        }
+    }
+}
+
+// --------------------------------------------------------------------------- generic path
+// GROUP = 32: one warp per block; GROUP = 256: one CTA per block. Two passes, scalar accesses.
+template <typename S, int GROUP>
+__global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_constant__ StepLaunch L,
+                                                                const __grid_constant__ gefen_b200_step_tensor_t single) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ float red_max[kWarps];
+    __shared__ float red_sum[kWarps];
+    SmemView s;
+    if (!stage_tables<false>(L.ws, smem, s)) return;
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int tig = (GROUP == 32) ? lane : static_cast<int>(threadIdx.x);
+    const long long group_global = (GROUP == 32) ? static_cast<long long>(blockIdx.x) * kWarps + warp
+                                                 : static_cast<long long>(blockIdx.x);
+    const long long group_stride = (GROUP == 32) ? static_cast<long long>(gridDim.x) * kWarps
+                                                 : static_cast<long long>(gridDim.x);
+
+    for (long long gb = group_global; gb < L.total_blocks; gb += group_stride) {
+        gefen_b200_step_tensor_t t;
+        long long b;
+        if (L.table == nullptr) {
+            t = single;
+            b = gb;
+        } else {
+            t = L.table[find_tensor(L.table, L.n_tensors, gb)];
+            b = gb - t.first_block;
+        }
+        const long long start = b * t.period;
+        const int period = static_cast<int>(t.period);
+        const bool muon = (t.flags & GEFEN_B200_STEP_MUON) != 0;
+        const bool period1 = (t.flags & GEFEN_B200_STEP_PERIOD1) != 0;
+        const bool fuse_v = (t.flags & GEFEN_B200_STEP_FUSE_VMEAN) != 0;
+        const bool wd = (t.flags & GEFEN_B200_STEP_WEIGHT_DECAY) != 0;
+        const bool nesterov = (t.flags & GEFEN_B200_STEP_NESTEROV) != 0;
+        const S* g = static_cast<const S*>(t.g) + start;
+        S* p = static_cast<S*>(t.p) + start;
+        uint8_t* codes = t.codes + start;
+        const float beta1 = t.beta1;
+        const float omb1 = 1.0f - beta1;
+        const float beta2 = t.beta2;
+        const float omb2 = 1.0f - beta2;
+        const float old_mag = load_state(t.mag, b, t.mag_dtype);
+
+        // pass 1: NaN-ignoring absmax of the updated momentum (the reference's `>` test), sum g^2;
+        // period-1 tensors update their per-element second moment here
+        // (reference: automatic_gefen_fused_kernel.cu:350-366).
+        float absmax = 0.0f, sumsq = 0.0f;
+        for (int i = tig; i < period; i += GROUP) {
+            const float gi = ScalarIO<S>::load(g + i);
+            if (period1) {
+                const float prev = load_state(t.v, start + i, t.v_dtype);
+                store_state(t.v, start + i, t.v_dtype, fmaf(beta2, prev, (omb2 * gi) * gi));
+            }
+            const float cur = old_mag * s.cb[codes[i]];
+            const float u = ema_update(beta1, cur, omb1, gi);
+            absmax = fmaxf(absmax, fabsf(u));
+            sumsq = fmaf(gi, gi, sumsq);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) absmax = fmaxf(absmax, __shfl_xor_sync(0xffffffffu, absmax, o));
+        sumsq = warp_sum(sumsq);
+        if (GROUP > 32) {
+            __syncthreads();  // previous iteration's readers are done with red_*
+            if (lane == 0) { red_max[warp] = absmax; red_sum[warp] = sumsq; }
+            __syncthreads();
+            absmax = red_max[0];
+            sumsq = red_sum[0];
+#pragma unroll
+            for (int w = 1; w < kWarps; ++w) { absmax = fmaxf(absmax, red_max[w]); sumsq += red_sum[w]; }
+        }
+
+        float step = 0.0f;
+        if (!muon && !period1) {
+            if (L.stepsize != nullptr && L.table == nullptr) {
+                step = L.stepsize[b];
+            } else {
+                float v = load_state(t.v, b, t.v_dtype);
+                if (fuse_v) {
+                    const float mean_sq = sumsq / static_cast<float>(period);
+                    const float nv = fmaf(beta2, v, omb2 * mean_sq);
+                    // every thread computes the same rounded value; one thread stores it
+                    if (t.v_dtype == GEFEN_B200_F32) v = nv;
+                    else if (t.v_dtype == GEFEN_B200_BF16) v = __bfloat162float(__float2bfloat16_rn(nv));
+                    else v = __half2float(__float2half_rn(nv));
+                    if (tig == 0) store_state(t.v, b, t.v_dtype, nv);
+                }
+                step = adam_step_size(v, t.bc1, t.bc2, t.eps);
+            }
+        }
+        if (GROUP > 32) __syncthreads(); else __syncwarp();  // old magnitude was read by everyone
+        if (tig == 0) store_state(t.mag, b, t.mag_dtype, absmax);
+        const bool do_update = muon || period1 || t.lr != 0.0f;
+
+        // pass 2: re-encode and update
+        for (int i = tig; i < period; i += GROUP) {
+            const float gi = ScalarIO<S>::load(g + i);
+            const float cur = old_mag * s.cb[codes[i]];
+            const float u = ema_update(beta1, cur, omb1, gi);
+            float x = 0.0f;
+            if (absmax > 0.0f) x = u / absmax;
+            const uint32_t code = static_cast<uint32_t>(entry_exact(x, s.thr, s.cb, s.k));
+            codes[i] = static_cast<uint8_t>(code);
+            const float q = s.cb[code] * absmax;
+            if (muon) {
+                float out = q;
+                if (nesterov) out = fmaf(t.beta2, gi, ScalarIO<S>::round(ScalarIO<S>::round(q) * beta1));
+                ScalarIO<S>::store(p + i, out);
+            } else if (do_update) {
+                float st = step;
+                if (period1) st = adam_step_size(load_state(t.v, start + i, t.v_dtype), t.bc1, t.bc2, t.eps);
+                float pi = ScalarIO<S>::load(p + i);
+                if (wd) pi = ScalarIO<S>::round(pi * t.wd_mul);
+                ScalarIO<S>::store(p + i, fmaf(-(q * st), t.lr, pi));
+            }
+        }
+    }
+}
+
+// --------------------------------------------------------------------------- vmean only
+// vmean[b] = beta2*vmean[b] + (1-beta2)*mean(g[b,:]^2) (reference: automatic_vmean_kernel.cu:12-51).
+// One warp per block, fp32 accumulation.
+template <typename S>
+__global__ void __launch_bounds__(kThreads) vmean_kernel(void* __restrict__ vmean, int v_dtype, const S* __restrict__ g,
+                                                         long long num_blocks, long long period, float beta2) {
+    const int lane = threadIdx.x & 31;
+    const long long warp_global = static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+    const long long warp_stride = static_cast<long long>(gridDim.x) * kWarps;
+    const bool vec = (sizeof(S) == 2) && (period % 8 == 0) && ((reinterpret_cast<uintptr_t>(g) & 15u) == 0);
+    for (long long b = warp_global; b < num_blocks; b += warp_stride) {
+        const S* gb = g + b * period;
+        float sum = 0.0f;
+        if (vec) {
+            const uint4* g4 = reinterpret_cast<const uint4*>(gb);
+            for (long long c = lane; c < period / 8; c += 32) {
+                const uint4 raw = g4[c];
+                const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const S* h = reinterpret_cast<const S*>(&w[i]);
+                    const float a = ScalarIO<S>::load(h), c2 = ScalarIO<S>::load(h + 1);
+                    sum = fmaf(a, a, sum);
+                    sum = fmaf(c2, c2, sum);
+                }
+            }
+        } else {
+            for (long long i = lane; i < period; i += 32) {
+                const float a = ScalarIO<S>::load(gb + i);
+                sum = fmaf(a, a, sum);
+            }
+        }
+        sum = warp_sum(sum);
+        if (lane == 0) {
+            const float mean_sq = sum / static_cast<float>(period);
+            const float prev = load_state(vmean, b, v_dtype);
+            store_state(vmean, b, v_dtype, fmaf(beta2, prev, (1.0f - beta2) * mean_sq));
+        }
+    }
+}
+
+// --------------------------------------------------------------------------- host dispatch
+static int grid_for(long long groups_needed, int groups_per_cta, int ctas_per_sm) {
+    long long ctas = (groups_needed + groups_per_cta - 1) / groups_per_cta;
+    const long long cap = static_cast<long long>(sm_count()) * ctas_per_sm;
+    if (ctas > cap) ctas = cap;
+    if (ctas < 1) ctas = 1;
+    return static_cast<int>(ctas);
+}
+
+template <typename S, int R>
+static int launch_vec(const StepLaunch& L, const gefen_b200_step_tensor_t& single, cudaStream_t stream) {
+    constexpr bool REP = true;
+    constexpr int smem = kSmemWs + (REP ? kSmemRep : 0);
+    static bool configured[64];
+    int dev = 0;
+    GEFEN_CHECK_CUDA(cudaGetDevice(&dev));
+    auto kernel = step_vec_kernel<S, R, REP>;
+    if (dev < 64 && !configured[dev]) {
+        GEFEN_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured[dev] = true;
+    }
+    const int grid = grid_for(L.total_blocks, kWarps, R >= 6 ? 2 : 3);
+    kernel<<<grid, kThreads, smem, stream>>>(L, single);
+    GEFEN_CHECK_CUDA(cudaGetLastError());
+    return GEFEN_B200_OK;
+}
+
+template <typename S>
+static int launch_vec_r(int R, const StepLaunch& L, const gefen_b200_step_tensor_t& single, cudaStream_t stream) {
+    switch (R) {
+        case 1: return launch_vec<S, 1>(L, single, stream);
+        case 2: return launch_vec<S, 2>(L, single, stream);
+        case 3: return launch_vec<S, 3>(L, single, stream);
+        case 4: return launch_vec<S, 4>(L, single, stream);
+        case 5: return launch_vec<S, 5>(L, single, stream);
+        case 6: return launch_vec<S, 6>(L, single, stream);
+        case 7: return launch_vec<S, 7>(L, single, stream);
+        case 8: return launch_vec<S, 8>(L, single, stream);
+    }
+    return fail(GEFEN_B200_EINVAL, "internal: bad chunk count %d", R);
+}
+
+template <typename S>
+static int launch_generic(bool cta_per_block, const StepLaunch& L, const gefen_b200_step_tensor_t& single,
+                          cudaStream_t stream) {
+    constexpr int smem = kSmemWs;
+    static bool configured[64];
+    int dev = 0;
+    GEFEN_CHECK_CUDA(cudaGetDevice(&dev));
+    if (dev < 64 && !configured[dev]) {
+        GEFEN_CHECK_CUDA(cudaFuncSetAttribute(step_generic_kernel<S, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        GEFEN_CHECK_CUDA(cudaFuncSetAttribute(step_generic_kernel<S, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured[dev] = true;
+    }
+    if (cta_per_block) {
+        const int grid = grid_for(L.total_blocks, 1, 4);
+        step_generic_kernel<S, 256><<<grid, kThreads, smem, stream>>>(L, single);
+    } else {
+        const int grid = grid_for(L.total_blocks, kWarps, 4);
+        step_generic_kernel<S, 32><<<grid, kThreads, smem, stream>>>(L, single);
+    }
+    GEFEN_CHECK_CUDA(cudaGetLastError());
+    return GEFEN_B200_OK;
+}
+
+// Class of a tensor: 1..8 = fast path with that many chunks per lane, 0 = generic warp per block,
+// -1 = generic CTA per block.
+static int tensor_class(const gefen_b200_step_tensor_t& t, int dtype) {
+    const bool vec_dtype = dtype == GEFEN_B200_F32 || dtype == GEFEN_B200_BF16 || dtype == GEFEN_B200_F16;
+    const bool period1 = (t.flags & GEFEN_B200_STEP_PERIOD1) != 0;
+    if (vec_dtype && !period1 && t.period % 8 == 0 && t.period <= 2048 && aligned16(t.g) &&
+        (aligned16(t.p)) && (reinterpret_cast<uintptr_t>(t.codes) & 7u) == 0) {
+        return static_cast<int>((t.period + 255) / 256);
+    }
+    return t.period > 2048 ? -1 : 0;
+}
+
+static int launch_class(int cls, int dtype, const StepLaunch& L, const gefen_b200_step_tensor_t& single,
+                        cudaStream_t stream) {
+    if (cls >= 1) {
+        if (dtype == GEFEN_B200_BF16) return launch_vec_r<__nv_bfloat16>(cls, L, single, stream);
+        if (dtype == GEFEN_B200_F16) return launch_vec_r<__half>(cls, L, single, stream);
+        return launch_vec_r<float>(cls, L, single, stream);
+    }
+    const bool cta = cls < 0;
+    switch (dtype) {
+        case GEFEN_B200_F32: return launch_generic<float>(cta, L, single, stream);
+        case GEFEN_B200_F16: return launch_generic<__half>(cta, L, single, stream);
+        case GEFEN_B200_BF16: return launch_generic<__nv_bfloat16>(cta, L, single, stream);
+        case GEFEN_B200_F64: return launch_generic<double>(cta, L, single, stream);
+    }
+    return fail(GEFEN_B200_EINVAL, "Unsupported parameter dtype tag %d.", dtype);
+}
+
+static int check_common(const void* g, uint8_t* codes, void* mag, int mag_dtype, int param_dtype,
+                        int packed_indices, long long num_blocks, long long period) {
+    GEFEN_CHECK_ARG(g != nullptr && codes != nullptr && mag != nullptr, "Expected non-null tensor pointers.");
+    GEFEN_CHECK_ARG(is_float_dtype(param_dtype), "Unsupported parameter/gradient dtype tag %d.", param_dtype);
+    GEFEN_CHECK_ARG(is_state_dtype(mag_dtype),
+                    "Expected m_magnitude to have dtype float32, float16, or bfloat16.");
+    GEFEN_CHECK_ARG(num_blocks >= 0 && period > 0, "Expected a positive period and a non-negative block count.");
+    GEFEN_CHECK_ARG(period <= 0x7FFFFFFFLL, "Period %lld is too large.", period);
+    if (packed_indices) {
+        return fail(GEFEN_B200_EUNSUPPORTED,
+                    "packed_indices=True (4-bit codes) is not implemented; every caller in the optimizer "
+                    "passes False.");
+    }
+    return GEFEN_B200_OK;
+}
+
+static int run_single(gefen_b200_step_tensor_t& t, int param_dtype, const float* stepsize, const float* codebook,
+                      int codebook_size, const void* codebook_ws, cudaStream_t stream) {
+    if (t.num_blocks == 0) return GEFEN_B200_OK;
+    const void* ws = nullptr;
+    const int rc = resolve_codebook_ws(codebook, codebook_size, codebook_ws, stream, &ws);
+    if (rc != GEFEN_B200_OK) return rc;
+    t.first_block = 0;
+    StepLaunch L;
+    L.table = nullptr;
+    L.n_tensors = 1;
+    L.total_blocks = t.num_blocks;
+    L.ws = static_cast<const unsigned char*>(ws);
+    L.stepsize = stepsize;
+    return launch_class(tensor_class(t, param_dtype), param_dtype, L, t, stream);
+}
+
+}  // namespace gefen
+
+using namespace gefen;
+
+extern "C" {
+
+int gefen_b200_automatic_vmean_update(void* vmean, int vmean_dtype, const void* grad_view, int grad_dtype,
+                                      int64_t num_blocks, int64_t period, double beta2, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    GEFEN_CHECK_ARG(vmean != nullptr && grad_view != nullptr, "Expected non-null vmean and grad_view.");
+    GEFEN_CHECK_ARG(is_state_dtype(vmean_dtype), "Expected vmean to have dtype float32, float16, or bfloat16.");
+    GEFEN_CHECK_ARG(is_float_dtype(grad_dtype), "Unsupported gradient dtype tag %d.", grad_dtype);
+    GEFEN_CHECK_ARG(period > 0, "Expected grad_view to have a positive period.");
+    GEFEN_CHECK_ARG(num_blocks >= 0, "Expected a non-negative block count.");
+    if (num_blocks == 0) return GEFEN_B200_OK;
+    const int grid = grid_for(num_blocks, kWarps, 8);
+    const float b2 = static_cast<float>(beta2);
+    switch (grad_dtype) {
+        case GEFEN_B200_F32:
+            vmean_kernel<float><<<grid, kThreads, 0, stream>>>(vmean, vmean_dtype, static_cast<const float*>(grad_view), num_blocks, period, b2);
+            break;
+        case GEFEN_B200_F16:
+            vmean_kernel<__half><<<grid, kThreads, 0, stream>>>(vmean, vmean_dtype, static_cast<const __half*>(grad_view), num_blocks, period, b2);
+            break;
+        case GEFEN_B200_BF16:
+            vmean_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(vmean, vmean_dtype, static_cast<const __nv_bfloat16*>(grad_view), num_blocks, period, b2);
+            break;
+        default:
+            vmean_kernel<double><<<grid, kThreads, 0, stream>>>(vmean, vmean_dtype, static_cast<const double*>(grad_view), num_blocks, period, b2);
+            break;
+    }
+    GEFEN_CHECK_CUDA(cudaGetLastError());
+    return GEFEN_B200_OK;
+}
+
+int gefen_b200_automatic_gefen_fused_update_from_vmean(
+    void* p, const void* grad_view, int param_dtype, uint8_t* m_sign, void* m_magnitude, int magnitude_dtype,
+    const void* vmean, int vmean_dtype, const float* codebook, int codebook_size, const void* codebook_ws,
+    int packed_indices, int64_t num_blocks, int64_t period, double beta1, double lr, double bias_correction_1,
+    double bias_correction_2, double eps, void* stream) {
+    int rc = check_common(grad_view, m_sign, m_magnitude, magnitude_dtype, param_dtype, packed_indices, num_blocks, period);
+    if (rc != GEFEN_B200_OK) return rc;
+    GEFEN_CHECK_ARG(p != nullptr && vmean != nullptr, "Expected non-null p and vmean.");
+    GEFEN_CHECK_ARG(is_state_dtype(vmean_dtype), "Expected vmean to have dtype float32, float16, or bfloat16.");
+    GEFEN_CHECK_ARG(bias_correction_1 > 0.0, "Expected bias_correction_1 to be positive.");
+    GEFEN_CHECK_ARG(bias_correction_2 > 0.0, "Expected bias_correction_2 to be positive.");
+    GEFEN_CHECK_ARG(eps >= 0.0, "Expected eps to be non-negative.");
+    gefen_b200_step_tensor_t t = {};
+    t.p = p; t.g = grad_view; t.codes = m_sign; t.mag = m_magnitude; t.v = const_cast<void*>(vmean);
+    t.num_blocks = num_blocks; t.period = period;
+    t.beta1 = static_cast<float>(beta1); t.lr = static_cast<float>(lr);
+    t.bc1 = static_cast<float>(bias_correction_1); t.bc2 = static_cast<float>(bias_correction_2);
+    t.eps = static_cast<float>(eps); t.wd_mul = 1.0f; t.flags = 0;
+    t.mag_dtype = magnitude_dtype; t.v_dtype = vmean_dtype;
+    return run_single(t, param_dtype, nullptr, codebook, codebook_size, codebook_ws, static_cast<cudaStream_t>(stream));
+}
+
+int gefen_b200_automatic_gefen_fused_update(
+    void* p, const void* grad_view, int param_dtype, uint8_t* m_sign, void* m_magnitude, int magnitude_dtype,
+    const float* stepsize, const float* codebook, int codebook_size, const void* codebook_ws, int packed_indices,
+    int64_t num_blocks, int64_t period, double beta1, double lr, void* stream) {
+    int rc = check_common(grad_view, m_sign, m_magnitude, magnitude_dtype, param_dtype, packed_indices, num_blocks, period);
+    if (rc != GEFEN_B200_OK) return rc;
+    GEFEN_CHECK_ARG(p != nullptr && stepsize != nullptr, "Expected non-null p and stepsize.");
+    gefen_b200_step_tensor_t t = {};
+    t.p = p; t.g = grad_view; t.codes = m_sign; t.mag = m_magnitude; t.v = nullptr;
+    t.num_blocks = num_blocks; t.period = period;
+    t.beta1 = static_cast<float>(beta1); t.lr = static_cast<float>(lr);
+    t.bc1 = 1.0f; t.bc2 = 1.0f; t.eps = 0.0f; t.wd_mul = 1.0f; t.flags = 0;
+    t.mag_dtype = magnitude_dtype; t.v_dtype = GEFEN_B200_F32;
+    return run_single(t, param_dtype, stepsize, codebook, codebook_size, codebook_ws, static_cast<cudaStream_t>(stream));
+}
+
+int gefen_b200_automatic_gefen_period1_update(
+    void* p, const void* grad_flat, int param_dtype, uint8_t* m_sign, void* m_magnitude, int magnitude_dtype,
+    void* vmean, int vmean_dtype, const float* codebook, int codebook_size, const void* codebook_ws,
+    int64_t total_numel, int64_t period_one_divisor, double beta1, double beta2, double lr,
+    double bias_correction_1, double bias_correction_2, double eps, void* stream) {
+    GEFEN_CHECK_ARG(period_one_divisor > 0, "Expected period_one_divisor to be positive.");
+    GEFEN_CHECK_ARG(total_numel >= 0 && total_numel % period_one_divisor == 0,
+                    "Expected period_one_divisor to divide total_numel.");
+    const int64_t num_blocks = total_numel / period_one_divisor;
+    int rc = check_common(grad_flat, m_sign, m_magnitude, magnitude_dtype, param_dtype, 0, num_blocks, period_one_divisor);
+    if (rc != GEFEN_B200_OK) return rc;
+    GEFEN_CHECK_ARG(p != nullptr && vmean != nullptr, "Expected non-null p and vmean.");
+    GEFEN_CHECK_ARG(is_state_dtype(vmean_dtype), "Expected vmean to have dtype float32, float16, or bfloat16.");
+    GEFEN_CHECK_ARG(bias_correction_1 > 0.0, "Expected bias_correction_1 to be positive.");
+    GEFEN_CHECK_ARG(bias_correction_2 > 0.0, "Expected bias_correction_2 to be positive.");
+    GEFEN_CHECK_ARG(eps >= 0.0, "Expected eps to be non-negative.");
+    gefen_b200_step_tensor_t t = {};
+    t.p = p; t.g = grad_flat; t.codes = m_sign; t.mag = m_magnitude; t.v = vmean;
+    t.num_blocks = num_blocks; t.period = period_one_divisor;
+    t.beta1 = static_cast<float>(beta1); t.beta2 = static_cast<float>(beta2); t.lr = static_cast<float>(lr);
+    t.bc1 = static_cast<float>(bias_correction_1); t.bc2 = static_cast<float>(bias_correction_2);
+    t.eps = static_cast<float>(eps); t.wd_mul = 1.0f; t.flags = GEFEN_B200_STEP_PERIOD1;
+    t.mag_dtype = magnitude_dtype; t.v_dtype = vmean_dtype;
+    return run_single(t, param_dtype, nullptr, codebook, codebook_size, codebook_ws, static_cast<cudaStream_t>(stream));
+}
+
+int gefen_b200_automatic_gefen_muon_momentum(
+    const void* grad_view, int grad_dtype, uint8_t* m_sign, void* m_magnitude, int magnitude_dtype,
+    const float* codebook, int codebook_size, const void* codebook_ws, void* momentum_update, int packed_indices,
+    int64_t num_blocks, int64_t period, double beta1, void* stream) {
+    int rc = check_common(grad_view, m_sign, m_magnitude, magnitude_dtype, grad_dtype, packed_indices, num_blocks, period);
+    if (rc != GEFEN_B200_OK) return rc;
+    GEFEN_CHECK_ARG(momentum_update != nullptr, "Expected a non-null momentum_update.");
+    gefen_b200_step_tensor_t t = {};
+    t.p = momentum_update; t.g = grad_view; t.codes = m_sign; t.mag = m_magnitude; t.v = nullptr;
+    t.num_blocks = num_blocks; t.period = period;
+    t.beta1 = static_cast<float>(beta1); t.lr = 0.0f; t.bc1 = 1.0f; t.bc2 = 1.0f; t.wd_mul = 1.0f;
+    t.flags = GEFEN_B200_STEP_MUON;
+    t.mag_dtype = magnitude_dtype; t.v_dtype = GEFEN_B200_F32;
+    return run_single(t, grad_dtype, nullptr, codebook, codebook_size, codebook_ws, static_cast<cudaStream_t>(stream));
+}
+
+int gefen_b200_step_tensor_size(void) { return static_cast<int>(sizeof(gefen_b200_step_tensor_t)); }
+
+int gefen_b200_step_tensor_class(const gefen_b200_step_tensor_t* host_entry, int param_dtype) {
+    if (host_entry == nullptr) return -2;
+    return tensor_class(*host_entry, param_dtype);
+}
+
+int gefen_b200_multi_tensor_step(gefen_b200_step_tensor_t* host_table, void* device_table, int n_tensors,
+                                 int param_dtype, const void* codebook_ws, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    GEFEN_CHECK_ARG(n_tensors >= 0, "Expected a non-negative tensor count.");
+    if (n_tensors == 0) return GEFEN_B200_OK;
+    GEFEN_CHECK_ARG(host_table != nullptr && device_table != nullptr && codebook_ws != nullptr,
+                    "Expected non-null tables and codebook workspace.");
+    GEFEN_CHECK_ARG(aligned16(codebook_ws) && aligned16(device_table), "Expected 16-byte aligned workspace and table.");
+    GEFEN_CHECK_ARG(is_float_dtype(param_dtype), "Unsupported parameter dtype tag %d.", param_dtype);
+    // Tensors are launched in maximal runs of rows that share a kernel class (fast path with R
+    // chunks per lane, generic warp, generic CTA); callers that keep equal classes adjacent get one
+    // launch per class. Rows are never reordered.
+    for (int i = 0; i < n_tensors; ++i) {
+        gefen_b200_step_tensor_t& t = host_table[i];
+        GEFEN_CHECK_ARG(t.g != nullptr && t.codes != nullptr && t.mag != nullptr && t.p != nullptr,
+                        "Tensor %d of the table has a null pointer.", i);
+        GEFEN_CHECK_ARG(t.period > 0 && t.period <= 0x7FFFFFFFLL && t.num_blocks >= 0,
+                        "Tensor %d of the table has a bad period or block count.", i);
+        GEFEN_CHECK_ARG(is_state_dtype(t.mag_dtype) && is_state_dtype(t.v_dtype),
+                        "Tensor %d of the table has a bad state dtype.", i);
+        GEFEN_CHECK_ARG((t.flags & GEFEN_B200_STEP_MUON) || t.v != nullptr, "Tensor %d has a null vmean.", i);
+        t.reserved_[0] = tensor_class(t, param_dtype);
+    }
+    for (int begin = 0; begin < n_tensors;) {
+        int end = begin;
+        long long first = 0;
+        while (end < n_tensors && host_table[end].reserved_[0] == host_table[begin].reserved_[0]) {
+            host_table[end].first_block = first;
+            first += host_table[end].num_blocks;
+            ++end;
+        }
+        host_table[begin].reserved_[1] = end - begin;  // run length, read back below
+        begin = end;
+    }
+    GEFEN_CHECK_CUDA(cudaMemcpyAsync(device_table, host_table, sizeof(gefen_b200_step_tensor_t) * n_tensors,
+                                     cudaMemcpyHostToDevice, stream));
+    for (int begin = 0; begin < n_tensors;) {
+        const int run = host_table[begin].reserved_[1];
+        const gefen_b200_step_tensor_t& last = host_table[begin + run - 1];
+        const long long total = last.first_block + last.num_blocks;
+        if (total > 0) {
+            StepLaunch L;
+            L.table = static_cast<const gefen_b200_step_tensor_t*>(device_table) + begin;
+            L.n_tensors = run;
+            L.total_blocks = total;
+            L.ws = static_cast<const unsigned char*>(codebook_ws);
+            L.stepsize = nullptr;
+            const int rc = launch_class(host_table[begin].reserved_[0], param_dtype, L, host_table[begin], stream);
+            if (rc != GEFEN_B200_OK) return rc;
+        }
+        begin += run;
+    }
+    return GEFEN_B200_OK;
+}
+
+}  // extern "C"

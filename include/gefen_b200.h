@@ -1,0 +1,197 @@
+/*
+ * gefen_b200 — C ABI of the B200 (sm_100a) implementation of the Gefen optimizer-step hot path.
+ *
+ * This header is the drop-in boundary. It replaces the pybind11 module of the reference
+ * (kernels/gefen_cuda_binding.cpp:107-217, eleven functions taking at::Tensor) with plain
+ * `extern "C"` entry points taking raw device pointers, sizes, dtype tags and a CUDA stream.
+ *
+ * Conventions
+ *  - every pointer is a DEVICE pointer unless its name starts with `host_`;
+ *  - tensors are contiguous; the caller owns every buffer; in-place outputs as in the reference;
+ *  - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream, which is what the
+ *    reference launches on);
+ *  - work is enqueued on `stream` for the CURRENT device; nothing synchronises unless stated;
+ *  - return value: 0 on success, a negative GEFEN_B200_E* code otherwise; the text of the last
+ *    error of the calling thread is available from gefen_b200_last_error();
+ *  - nothing throws, nothing falls back to the CPU.
+ */
+#ifndef GEFEN_B200_H_
+#define GEFEN_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* dtype tags (params/grads accept all four, optimizer-state scalars the first three) */
+#define GEFEN_B200_F32 0
+#define GEFEN_B200_F16 1
+#define GEFEN_B200_BF16 2
+#define GEFEN_B200_F64 3
+
+#define GEFEN_B200_OK 0
+#define GEFEN_B200_EINVAL (-1)   /* bad argument (reference: std::invalid_argument -> ValueError) */
+#define GEFEN_B200_ECUDA (-2)    /* CUDA runtime error (reference: C10_CUDA_KERNEL_LAUNCH_CHECK) */
+#define GEFEN_B200_ERUNTIME (-3) /* data-dependent failure (reference: std::runtime_error) */
+#define GEFEN_B200_EUNSUPPORTED (-4)
+
+/* Bytes of the per-codebook workspace filled by gefen_b200_codebook_prepare:
+ * 256 padded codebook floats, 256 decision thresholds, 8196 lookup-table words. */
+#define GEFEN_B200_CODEBOOK_WS_BYTES 34832
+
+/* flags of gefen_b200_step_tensor_t.flags */
+#define GEFEN_B200_STEP_FUSE_VMEAN 1u   /* update vmean from the gradient inside the step kernel */
+#define GEFEN_B200_STEP_WEIGHT_DECAY 2u /* p <- round(p * wd_mul) before the update */
+#define GEFEN_B200_STEP_PERIOD1 4u      /* per-element vmean; `period` is the magnitude block */
+#define GEFEN_B200_STEP_MUON 8u         /* write the dequantised momentum to `p`, no Adam update */
+#define GEFEN_B200_STEP_NESTEROV 16u    /* with MUON: p <- round(round(m*beta1) + (1-beta1)*g) */
+
+const char* gefen_b200_last_error(void);
+int gefen_b200_version(void);
+
+/* Derives from a sorted codebook (<= 256 floats) the tables the kernels stage into shared
+ * memory. Must be re-run when the codebook contents change. `workspace` holds
+ * GEFEN_B200_CODEBOOK_WS_BYTES, 16-byte aligned. No counterpart in the reference, whose kernels
+ * binary-search the codebook in global memory (automatic_gefen_fused_kernel.cu:59-90). */
+int gefen_b200_codebook_prepare(const float* codebook, int codebook_size, void* workspace,
+                                void* stream);
+
+/* Replaces automatic_vmean_update_cuda (gefen_cuda_binding.cpp:59-63;
+ * automatic_vmean_kernel.cu:66-158): vmean[b] = beta2*vmean[b] + (1-beta2)*mean(grad[b,:]^2). */
+int gefen_b200_automatic_vmean_update(void* vmean, int vmean_dtype, const void* grad_view,
+                                      int grad_dtype, int64_t num_blocks, int64_t period,
+                                      double beta2, void* stream);
+
+/* Replaces automatic_gefen_fused_update_from_vmean_cuda (gefen_cuda_binding.cpp:18-31;
+ * automatic_gefen_fused_kernel.cu:676-833). `codebook_ws` may be NULL, in which case a
+ * library-owned per-device workspace is (re)built on `stream` before the step. */
+int gefen_b200_automatic_gefen_fused_update_from_vmean(
+    void* p, const void* grad_view, int param_dtype, uint8_t* m_sign, void* m_magnitude,
+    int magnitude_dtype, const void* vmean, int vmean_dtype, const float* codebook,
+    int codebook_size, const void* codebook_ws, int packed_indices, int64_t num_blocks,
+    int64_t period, double beta1, double lr, double bias_correction_1, double bias_correction_2,
+    double eps, void* stream);
+
+/* Replaces automatic_gefen_fused_update_cuda (gefen_cuda_binding.cpp:6-16;
+ * automatic_gefen_fused_kernel.cu:556-674): same as above with a precomputed fp32 stepsize[nb]. */
+int gefen_b200_automatic_gefen_fused_update(
+    void* p, const void* grad_view, int param_dtype, uint8_t* m_sign, void* m_magnitude,
+    int magnitude_dtype, const float* stepsize, const float* codebook, int codebook_size,
+    const void* codebook_ws, int packed_indices, int64_t num_blocks, int64_t period, double beta1,
+    double lr, void* stream);
+
+/* Replaces automatic_gefen_period1_update_cuda (gefen_cuda_binding.cpp:33-47;
+ * automatic_gefen_fused_kernel.cu:835-1000): per-element vmean, one magnitude per
+ * `period_one_divisor` elements. */
+int gefen_b200_automatic_gefen_period1_update(
+    void* p, const void* grad_flat, int param_dtype, uint8_t* m_sign, void* m_magnitude,
+    int magnitude_dtype, void* vmean, int vmean_dtype, const float* codebook, int codebook_size,
+    const void* codebook_ws, int64_t total_numel, int64_t period_one_divisor, double beta1,
+    double beta2, double lr, double bias_correction_1, double bias_correction_2, double eps,
+    void* stream);
+
+/* Replaces automatic_gefen_muon_momentum_cuda (gefen_cuda_binding.cpp:49-57;
+ * automatic_gefen_fused_kernel.cu:1002-1103): momentum_update <- dequantised new momentum. */
+int gefen_b200_automatic_gefen_muon_momentum(
+    const void* grad_view, int grad_dtype, uint8_t* m_sign, void* m_magnitude, int magnitude_dtype,
+    const float* codebook, int codebook_size, const void* codebook_ws, void* momentum_update,
+    int packed_indices, int64_t num_blocks, int64_t period, double beta1, void* stream);
+
+/* One launch for many tensors (no counterpart in the reference, which launches 2-3 kernels per
+ * tensor from Python, gefen.py:1208-1333). The host table is copied into `device_table`
+ * (n_tensors * sizeof(gefen_b200_step_tensor_t) bytes, caller-owned) on `stream`. Keep
+ * host_table in pageable memory, or do not touch a pinned one until the copy has run: the
+ * library writes first_block and reserved_ into it and the copy reads it later. All tensors of
+ * one call share param_dtype. Fuses the vmean update, the weight-decay pre-multiply and the
+ * step. */
+typedef struct gefen_b200_step_tensor {
+    void* p;            /* params, or the dense momentum output with GEFEN_B200_STEP_MUON */
+    const void* g;      /* gradients, same dtype as p */
+    uint8_t* codes;     /* m_codebook, one uint8 per element */
+    void* mag;          /* m_magnitude [num_blocks] */
+    void* v;            /* vmean [num_blocks] (per element with GEFEN_B200_STEP_PERIOD1) */
+    int64_t first_block; /* filled by the library */
+    int64_t num_blocks;
+    int64_t period;     /* elements per magnitude block */
+    float beta1, beta2, lr, bc1, bc2, eps, wd_mul; /* already rounded to float as the reference does */
+    uint32_t flags;
+    int32_t mag_dtype, v_dtype;
+    int32_t reserved_[2];
+} gefen_b200_step_tensor_t;
+
+int gefen_b200_multi_tensor_step(gefen_b200_step_tensor_t* host_table, void* device_table,
+                                 int n_tensors, int param_dtype, const void* codebook_ws,
+                                 void* stream);
+/* sizeof(gefen_b200_step_tensor_t) as compiled, for binding-side layout checks. */
+int gefen_b200_step_tensor_size(void);
+/* Kernel class the library would use for one table entry: 1..8 = vectorised path with that many
+ * 8-element chunks per lane, 0 = generic warp-per-block, -1 = generic CTA-per-block. Rows of equal
+ * class that are adjacent in the table share one launch. */
+int gefen_b200_step_tensor_class(const gefen_b200_step_tensor_t* host_entry, int param_dtype);
+
+/* Replaces gefen_exact_histogram_cuda (gefen_cuda_binding.cpp:65-69;
+ * exact_histogram_fused_kernel.cu:131-160): bin_counts[bin] += #elements, int64, exact. */
+int gefen_b200_exact_histogram(const void* grad_flat, int grad_dtype, int64_t numel,
+                               int64_t period, int64_t* bin_counts, int histogram_bins,
+                               void* stream);
+
+/* Replace average_within_block_variance_cuda, average_within_block_coefficient_of_variation_cuda
+ * and average_adjacent_log_block_mean_difference_cuda (gefen_cuda_binding.cpp:71-88;
+ * period_variance_kernel.cu:178-396). The reference allocates and returns a device double and
+ * synchronises to raise its data-dependent errors; here the raw accumulators go to caller-owned
+ * device memory (zeroed by the call) and the Python wrapper applies the reference's post-ops
+ * after its single device-to-host read:
+ *   variance: stats[0] = sum over blocks of the block variance      -> sqrt(stats[0] / nb)
+ *   cov     : stats[0] = sum of sqrt(var)/mean, stats[1] = #blocks with mean > 0,
+ *             stats[2] = #blocks with mean < 0                       -> stats[0] / stats[1]
+ *   adjacent: stats[0] = mean over adjacent block pairs of |mean log difference| (already
+ *             divided by nb-1), stats[1] = number of elements whose log input was <= 0
+ * `block_sums` is device scratch of gefen_b200_period_scratch_doubles(numel, period) doubles. */
+int gefen_b200_average_within_block_variance(const void* values, int dtype, int64_t numel,
+                                             int64_t period, int input_is_squared, double* stats,
+                                             void* stream);
+int gefen_b200_average_within_block_coefficient_of_variation(const void* values, int dtype,
+                                                             int64_t numel, int64_t period,
+                                                             int input_is_squared, double* stats,
+                                                             void* stream);
+int64_t gefen_b200_period_scratch_doubles(int64_t numel, int64_t period);
+int gefen_b200_average_adjacent_log_block_mean_difference(const void* values, int dtype,
+                                                          int64_t numel, int64_t period,
+                                                          int input_is_squared, double epsilon,
+                                                          double* stats, double* block_sums,
+                                                          void* stream);
+
+/* All candidate periods of one tensor in one call with no host synchronisation in between
+ * (replaces the per-divisor launch + .item() loop of partitioning.py:259-268). stats holds
+ * 2 * n_periods doubles: stats[2*i] = score of host_periods[i], stats[2*i+1] = its invalid
+ * count. `block_sums` must hold gefen_b200_period_scratch_doubles(numel, smallest period). */
+int gefen_b200_period_scan(const void* values, int dtype, int64_t numel, int input_is_squared,
+                           double epsilon, const int64_t* host_periods, int n_periods,
+                           double* stats, double* block_sums, void* stream);
+
+/* Replace gefen_lloyd_accumulate_cuda and gefen_lloyd_mse_cuda (gefen_cuda_binding.cpp:90-105;
+ * lloyd_max_fused_kernel.cu:244-356). */
+int gefen_b200_lloyd_accumulate(const void* grad_flat, int grad_dtype, int64_t numel,
+                                int64_t period, const float* codebook, int codebook_size,
+                                const void* codebook_ws, float* sums, int64_t* counts,
+                                void* stream);
+int gefen_b200_lloyd_mse(const void* grad_flat, int grad_dtype, int64_t numel, int64_t period,
+                         const float* old_codebook, const float* new_codebook, int codebook_size,
+                         const void* old_codebook_ws, float* mse_normalized_sum,
+                         float* mse_original_sum, void* stream);
+
+/* Exact 1-D k-means dynamic programme on the device in fp64 (replaces the numba kernel of
+ * quantization.py:92-145). prefix_* are device arrays of num_points+1 doubles (prefix sums of
+ * w, w*x, w*x^2 in the reference's order). `dp_scratch` holds
+ * gefen_b200_exact_dp_scratch_bytes(num_points, num_codebooks) bytes. Writes num_codebooks
+ * UNSORTED float32 centres to `codebook_out` (the caller sorts, as quantization.py:257 does). */
+int64_t gefen_b200_exact_dp_scratch_bytes(int num_points, int num_codebooks);
+int gefen_b200_exact_dp(const double* prefix_w, const double* prefix_wx, const double* prefix_wx2,
+                        int num_points, int num_codebooks, int force_endpoints, void* dp_scratch,
+                        float* codebook_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GEFEN_B200_H_ */
