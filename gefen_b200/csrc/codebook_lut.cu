@@ -3,7 +3,7 @@
 // The workspace turns "nearest codebook entry, left on ties" (reference:
 // kernels/automatic_gefen_fused_kernel.cu:59-90) into data the step kernels can stage into
 // shared memory with one bulk copy: the padded codebook, the 255 exact decision thresholds and
-// an 8193-cell table over [-1, 1] that resolves an element with a single word read.
+// an 8193-cell table over [-1, 1] that resolves an element with one 8-byte read and one compare.
 #include "common.cuh"
 
 #include <mutex>
@@ -52,21 +52,35 @@ __global__ void __launch_bounds__(256) codebook_prepare_kernel(const float* __re
     __shared__ float cb[kMaxCodebook];
     __shared__ float thr[kMaxCodebook];
     __shared__ int tcell[kMaxCodebook];
-    __shared__ uint32_t toff[kMaxCodebook];
+    __shared__ int any_slow;
     const int t = threadIdx.x;
+    if (t == 0) any_slow = 0;
     cb[t] = codebook[t < k ? t : k - 1];
     __syncthreads();
     thr[t] = (t < k - 1) ? entry_threshold(t, cb, k) : INFINITY;
-    tcell[t] = lut_threshold_cell(thr[t], &toff[t]);
+    tcell[t] = lut_threshold_cell(thr[t]);
     __syncthreads();
     float* ws_cb = reinterpret_cast<float*>(ws + kWsCodebookOff);
     float* ws_thr = reinterpret_cast<float*>(ws + kWsThresholdOff);
     uint32_t* ws_lut = reinterpret_cast<uint32_t*>(ws + kWsLutOff);
     ws_cb[t] = cb[t];
     ws_thr[t] = thr[t];
-    for (int cell = t; cell < kLutWords; cell += blockDim.x) {
-        ws_lut[cell] = (cell <= kLutCells) ? lut_build_cell(cell, tcell, toff, k - 1, cb[k - 1])
-                                           : (cell == kLutSizeWord ? static_cast<uint32_t>(k) : 0u);
+    bool slow = false;
+    for (int cell = t; cell < kLutBytes / 8; cell += blockDim.x) {
+        uint32_t w0 = 0x7f800000u, w1 = 0u;  // padding entries: +inf threshold, nothing below
+        if (cell <= kLutCells) lut_build_cell(cell, tcell, thr, k - 1, cb[k - 1], &w0, &w1);
+        ws_lut[2 * cell] = w0;
+        ws_lut[2 * cell + 1] = w1;
+        slow = slow || (w1 & kLutSlowBit);
+    }
+    if (slow) atomicOr(&any_slow, 1);
+    __syncthreads();
+    if (t == 0) {
+        int* meta = reinterpret_cast<int*>(ws + kWsMetaOff);
+        meta[0] = k;
+        meta[1] = any_slow;
+        meta[2] = 0;
+        meta[3] = 0;
     }
 }
 

@@ -43,8 +43,9 @@ int sm_count();  // SMs of the current device (cached per device)
 // Layout of the per-codebook workspace (GEFEN_B200_CODEBOOK_WS_BYTES).
 constexpr int kWsCodebookOff = 0;      // 256 floats, tail padded with the last entry
 constexpr int kWsThresholdOff = 1024;  // 256 floats, tail padded with +inf
-constexpr int kWsLutOff = 2048;        // kLutWords uint32
-static_assert(kWsLutOff + kLutWords * 4 == GEFEN_B200_CODEBOOK_WS_BYTES, "workspace size");
+constexpr int kWsMetaOff = 2048;       // 4 ints: codebook size, 1 if any table cell is undecidable, 0, 0
+constexpr int kWsLutOff = 2064;        // kLutBytes of 8-byte entries
+static_assert(kWsLutOff + kLutBytes == GEFEN_B200_CODEBOOK_WS_BYTES, "workspace size");
 
 // Returns a workspace for `codebook`: the caller's if given, else the library-owned one of the
 // current device, rebuilt on `stream` (see codebook_lut.cu).

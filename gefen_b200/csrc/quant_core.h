@@ -22,12 +22,11 @@
 namespace gefen {
 
 constexpr int kMaxCodebook = 256;          // reference: at most 256 entries (uint8 codes)
-constexpr int kLutCellShift = 18;          // key bits below the cell index
 constexpr int kLutCells = 8192;            // cells over [-1, 1); one more cell for x == 1
-constexpr int kLutWords = 8196;            // 8193 cells, word 8193 = codebook size, padded to 16 bytes
-constexpr int kLutSizeWord = 8193;
-constexpr uint32_t kLutNoThreshold = 0x80000u;   // larger than any in-cell offset
-constexpr uint32_t kLutSlowBit = 0x80000000u;    // cell holds two or more thresholds
+constexpr int kLutBytes = 65552;           // 8193 entries of 8 bytes, padded to a multiple of 16
+constexpr uint32_t kLutSlowBit = 0x80000000u;    // cell cannot be decided by one comparison
+
+struct alignas(8) uint2v { uint32_t x, y; };   // 8-byte table entry, read with one 64-bit load
 
 // ---------------------------------------------------------------------------------------------
 // The reference rule, verbatim in behaviour. NaN maps to entry 0 (every comparison is false).
@@ -98,54 +97,56 @@ GEFEN_HD int entry_exact(float x, const float* thr, const float* cb, int k) {
     return entry_by_thresholds(x, thr);
 }
 
-// Fixed-point key of a normalised value x in [-1, 1]: round(x * 2^30) + 2^30, in [0, 2^31].
-// Exact (no rounding) whenever |x| >= 2^-7, because then ulp(x) >= 2^-30.
-GEFEN_HD uint32_t lut_key(float x) {
-#if defined(__CUDA_ARCH__)
-    return static_cast<uint32_t>(__float2int_rn(x * 1073741824.0f)) + 0x40000000u;
-#else
-    return static_cast<uint32_t>(static_cast<int32_t>(nearbyintf(x * 1073741824.0f))) + 0x40000000u;
-#endif
+// ---------------------------------------------------------------------------------------------
+// Uniform-grid lookup table over x in [-1, 1]: 8192 cells of width 2^-12 (one more for x == 1).
+// Cell of x: the integer part of fma(x, 32768, magic) keeps round(x * 32768) + 32768 in its low
+// mantissa bits; masking the low three bits gives the BYTE offset of the 8-byte table entry. The
+// map is monotone in x, which is all the table needs: every threshold in a lower cell is below x,
+// every threshold in a higher cell is above it, and the one threshold that may share x's cell is
+// compared exactly in float. entry(x) = below(cell) + (x > threshold(cell)).
+// Entry layout: word 0 = float bits of the cell's threshold (+inf if none), word 1 = number of
+// thresholds below the cell, bit 31 set when the cell cannot be decided this way (two or more
+// thresholds inside, or values above the last codebook entry): such codebooks use entry_exact.
+GEFEN_HD uint32_t lut_byte_offset(float x) {
+    union { float f; uint32_t u; } c;
+    c.f = fmaf(x, 32768.0f, 12582912.0f + 32768.0f);
+    return c.u & 0x1FFF8u;
 }
+GEFEN_HD int lut_cell(float x) { return static_cast<int>(lut_byte_offset(x) >> 3); }
 
-// One table word per cell: bits 0-7 = number of thresholds below the cell, bits 8-27 = offset of
-// the single threshold inside the cell (kLutNoThreshold if none), bit 31 = two or more thresholds.
-//
-// Step 1, per threshold: the cell it falls in. -1 for thresholds below -1 (always exceeded),
-// kLutCells + 1 for thresholds that x <= 1 can never exceed (also the +inf padding).
-GEFEN_HD int lut_threshold_cell(float t, uint32_t* offset) {
-    *offset = kLutNoThreshold;
+// Step 1, per threshold: its cell. -1 for thresholds below -1 (always exceeded), kLutCells + 1 for
+// thresholds that x <= 1 can never exceed (also the +inf padding).
+GEFEN_HD int lut_threshold_cell(float t) {
     if (t < -1.0f) return -1;
     if (!(t < 1.0f)) return kLutCells + 1;
-    const uint32_t key = lut_key(t);
-    *offset = key & ((1u << kLutCellShift) - 1u);
-    return static_cast<int>(key >> kLutCellShift);
+    return lut_cell(t);
 }
-// Step 2, per cell: tcell[] is non-decreasing (thresholds are sorted), so two binary searches
-// give the number of thresholds below the cell and inside it.
-GEFEN_HD uint32_t lut_build_cell(int cell, const int* tcell, const uint32_t* toff, int nthr, float cb_last) {
-    // cells that contain values above the last codebook entry go to the exact path
-    if (cb_last < 1.0f && (cb_last < -1.0f || cell >= static_cast<int>(lut_key(cb_last) >> kLutCellShift)))
-        return (kLutNoThreshold << 8) | kLutSlowBit;
+// Step 2, per cell: tcell[] is non-decreasing (thresholds are sorted), so two binary searches give
+// the number of thresholds below the cell and inside it.
+GEFEN_HD void lut_build_cell(int cell, const int* tcell, const float* thr, int nthr, float cb_last,
+                             uint32_t* word_threshold, uint32_t* word_below) {
     int lo = 0, hi = nthr;
     while (lo < hi) { const int mid = (lo + hi) >> 1; if (tcell[mid] < cell) lo = mid + 1; else hi = mid; }
     const int below = lo;
     hi = nthr;
     while (lo < hi) { const int mid = (lo + hi) >> 1; if (tcell[mid] <= cell) lo = mid + 1; else hi = mid; }
     const int inside = lo - below;
-    if (inside == 0) return static_cast<uint32_t>(below) | (kLutNoThreshold << 8);
-    if (inside == 1) return static_cast<uint32_t>(below) | (toff[below] << 8);
-    return static_cast<uint32_t>(below) | (kLutNoThreshold << 8) | kLutSlowBit;
+    union { float f; uint32_t u; } c;
+    c.f = inside >= 1 ? thr[below] : INFINITY;
+    bool undecidable = inside >= 2;
+    // cells that contain values above the last codebook entry need the non-monotone rule
+    if (cb_last < 1.0f && (cb_last < -1.0f || cell >= lut_cell(cb_last))) undecidable = true;
+    *word_threshold = c.u;
+    *word_below = static_cast<uint32_t>(below) | (undecidable ? kLutSlowBit : 0u);
 }
 
-// The fast query. `slow` is set when the table cannot decide and entry_by_thresholds must be used.
-GEFEN_HD int lut_query(float x, const uint32_t* lut, bool* slow) {
-    const uint32_t key = lut_key(x);
-    const uint32_t w = lut[key >> kLutCellShift];
-    const uint32_t off = key & ((1u << kLutCellShift) - 1u);
-    const uint32_t toff = (w >> 8) & 0xFFFFFu;
-    *slow = (off == toff) || (w & kLutSlowBit);
-    return static_cast<int>(w & 0xFFu) + (off > toff ? 1 : 0);
+// The fast query; valid when no cell of the table carries kLutSlowBit.
+GEFEN_HD int lut_query(float x, const unsigned char* lut_bytes, bool* slow) {
+    const uint2v e = *reinterpret_cast<const uint2v*>(lut_bytes + lut_byte_offset(x));
+    union { float f; uint32_t u; } c;
+    c.u = e.x;
+    *slow = (e.y & kLutSlowBit) != 0u;
+    return static_cast<int>(e.y & 0xFFu) + (x > c.f ? 1 : 0);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -11,48 +11,51 @@
 //   p_i  -= cb[code'_i] * mag' * step * lr,   step = (1/bc1) / (sqrt(v/bc2) + eps)
 //
 // Two kernels:
-//  * step_vec_kernel  - the fast path. One warp owns one block and keeps its R*256 updated
-//    momenta in registers between the absmax reduction and the re-encode, so codes, gradients
-//    and params cross HBM exactly once (8 B/element in bf16, 14 B/element in fp32). 128-bit
-//    loads/stores; codebook, thresholds and the quantisation table arrive in shared memory by
-//    one bulk (TMA) copy; reductions are warp shuffles; no __syncthreads after set-up.
+//  * step_vec_kernel  - the fast path. One warp owns one block. Codes and gradients are read once
+//    (128-bit loads), the updated momenta wait in the warp's slice of shared memory while the
+//    block's absmax is reduced with shuffles, then they are re-encoded and the parameters updated:
+//    codes, gradients and params cross HBM exactly once (8 B/element in bf16, 14 B/element in
+//    fp32). Codebook, thresholds and the quantisation table arrive in shared memory by one bulk
+//    (TMA) copy per CTA. No __syncthreads after set-up; the loops are short so the code stays in
+//    the instruction cache.
 //  * step_generic_kernel - any period, alignment and dtype (fp64 included): two passes with
 //    scalar accesses, the second pass re-reading from L1/L2.
+// Both take their tensors from a descriptor table (one launch for many tensors); a single-tensor
+// call passes a one-row table inside the kernel parameters.
 #include "common.cuh"
 
 namespace gefen {
 
 // fp32 contraction choices. They reproduce what nvcc emits for the reference source when it is
 // compiled with its own flags (-O3, fmad on): a*b + c*d becomes fma(a, b, c*d) and p - a*b becomes
-// fma(-a, b, p). The CPU oracle makes the same choices explicitly.
+// fma(-a, b, p); checked on a B200 against the reference's own kernels. The CPU oracle makes the
+// same choices explicitly.
 __device__ __forceinline__ float ema_update(float beta, float cur, float omb, float g) {
     return fmaf(beta, cur, omb * g);
 }
 
 struct StepLaunch {
-    const gefen_b200_step_tensor_t* table;  // device table, or nullptr: use `single`
+    const gefen_b200_step_tensor_t* table;  // device table, or nullptr: the row in the kernel params
     int n_tensors;
+    int stage_floats;                       // fast path: floats of staging per warp (>= max period)
     long long total_blocks;
-    const unsigned char* ws;  // codebook workspace
-    const float* stepsize;    // optional precomputed per-block step (single tensor only)
+    const unsigned char* ws;                // codebook workspace
+    const float* stepsize;                  // optional precomputed per-block step (single tensor only)
 };
 
-constexpr int kThreads = 256;
-constexpr int kWarps = kThreads / 32;
 constexpr int kSmemWs = GEFEN_B200_CODEBOOK_WS_BYTES;
-constexpr int kSmemRep = 256 * 32 * 4;  // codebook replicated once per bank
+constexpr int kMaxSmem = 227 * 1024;
 
 struct SmemView {
-    const float* cb;      // 256
-    const float* thr;     // 256
-    const uint32_t* lut;  // kLutWords
-    const float* rep;     // 256 x 32, entry e for lane l at rep[e*32 + l]
-    int k;                // true codebook size
+    const float* cb;             // 256, padded with the last entry
+    const float* thr;            // 256, padded with +inf
+    const unsigned char* lut;    // kLutBytes
+    int k;                       // true codebook size
+    bool slow;                   // the table has undecidable cells: use entry_exact
 };
 
-// Stages the workspace with one bulk copy and builds the per-bank codebook copy.
-// Returns false (uniformly for the CTA) if the copy did not land in time.
-template <bool REP>
+// Stages the workspace with one bulk copy. Returns false (uniformly for the CTA) if the copy did
+// not land within the bounded wait.
 __device__ __forceinline__ bool stage_tables(const unsigned char* ws, unsigned char* smem, SmemView& view) {
     __shared__ uint64_t bar;
     __shared__ int ok;
@@ -69,30 +72,14 @@ __device__ __forceinline__ bool stage_tables(const unsigned char* ws, unsigned c
     __syncthreads();
     view.cb = reinterpret_cast<const float*>(smem + kWsCodebookOff);
     view.thr = reinterpret_cast<const float*>(smem + kWsThresholdOff);
-    view.lut = reinterpret_cast<const uint32_t*>(smem + kWsLutOff);
-    view.rep = nullptr;
+    view.lut = smem + kWsLutOff;
     view.k = 1;
+    view.slow = true;
     if (!ok) return false;
-    view.k = static_cast<int>(view.lut[kLutSizeWord]);
-    if (REP) {
-        float* rep = reinterpret_cast<float*>(smem + kSmemWs);
-        for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) rep[i] = view.cb[i >> 5];
-        view.rep = rep;
-        __syncthreads();
-    }
+    const int* meta = reinterpret_cast<const int*>(smem + kWsMetaOff);
+    view.k = meta[0];
+    view.slow = meta[1] != 0;
     return true;
-}
-
-template <bool REP>
-__device__ __forceinline__ float dequant(const SmemView& s, uint32_t code, int lane) {
-    return REP ? s.rep[code * 32 + lane] : s.cb[code];
-}
-
-__device__ __forceinline__ uint32_t quantize(const SmemView& s, float x) {
-    bool slow;
-    int e = lut_query(x, s.lut, &slow);
-    if (slow) e = entry_exact(x, s.thr, s.cb, s.k);
-    return static_cast<uint32_t>(e);
 }
 
 __device__ __forceinline__ float adam_step_size(float v, float bc1, float bc2, float eps) {
@@ -100,7 +87,7 @@ __device__ __forceinline__ float adam_step_size(float v, float bc1, float bc2, f
     return (1.0f / bc1) / (sqrtf(corrected) + eps);
 }
 
-// Finds the tensor that owns global block `gb` (table sorted by first_block).
+// Finds the row that owns global block `gb` (rows sorted by first_block).
 __device__ __forceinline__ int find_tensor(const gefen_b200_step_tensor_t* table, int n, long long gb) {
     int lo = 0, hi = n - 1;
     while (lo < hi) {
@@ -187,54 +174,58 @@ template <> struct Chunk<float> {
 };
 
 // --------------------------------------------------------------------------- fast path
-// One warp, one block of t.period = 8 * nchunks elements, nchunks <= 32 * R.
-template <typename S, int R, bool REP>
+// One warp, one block of t.period = 8 * nchunks elements. `stage` holds period floats for this warp:
+// the first halves of all chunks, then the second halves, so that every 128-bit shared access of
+// a warp is conflict-free.
+template <typename S>
 __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& t, long long b, const float* stepsize,
-                                                const SmemView& s, int lane) {
+                                                const SmemView& s, float* stage, int lane) {
     const int nchunks = static_cast<int>(t.period >> 3);
     const long long chunk0 = b * nchunks;  // chunk index of the block start, in units of 8 elements
     const uint2* codes_in = reinterpret_cast<const uint2*>(t.codes) + chunk0;
     uint2* codes_out = reinterpret_cast<uint2*>(t.codes) + chunk0;
-    const bool muon = (t.flags & GEFEN_B200_STEP_MUON) != 0;
+    const uint32_t flags = t.flags;
+    const bool muon = (flags & GEFEN_B200_STEP_MUON) != 0;
 
     const float beta1 = t.beta1;
     const float omb1 = 1.0f - beta1;
     const float old_mag = load_state(t.mag, b, t.mag_dtype);
-
-    float upd[R][8];
-    float absmax = 0.0f;
-    float sumsq = 0.0f;
+    float4* stage_a = reinterpret_cast<float4*>(stage);
+    float4* stage_b = stage_a + nchunks;
 
     // ---- pass over codes and gradients (the only read of both)
-    uint2 craw[R];
-    Chunk<S> graw[R];
+    float absmax = 0.0f;
+    float sumsq = 0.0f;
+    constexpr int U = 2;  // chunks in flight per lane
+    for (int c0 = lane; c0 < nchunks; c0 += 32 * U) {
+        uint2 craw[U];
+        Chunk<S> graw[U];
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int c = r * 32 + lane;
-        if (c < nchunks) {
-            craw[r] = codes_in[c];
-            graw[r].load(t.g, chunk0 + c);
-        }
-    }
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int c = r * 32 + lane;
-        if (c < nchunks) {
-            float g[8];
-            graw[r].unpack(g);
-            const uint32_t cw[2] = {craw[r].x, craw[r].y};
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const uint32_t code = (cw[i >> 2] >> (8 * (i & 3))) & 0xFFu;
-                const float cur = old_mag * dequant<REP>(s, code, lane);
-                const float u = ema_update(beta1, cur, omb1, g[i]);
-                upd[r][i] = u;
-                absmax = max_abs_nan(absmax, u);
-                sumsq = fmaf(g[i], g[i], sumsq);
+        for (int u = 0; u < U; ++u) {
+            const int c = c0 + 32 * u;
+            if (c < nchunks) {
+                craw[u] = codes_in[c];
+                graw[u].load(t.g, chunk0 + c);
             }
-        } else {
+        }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) upd[r][i] = 0.0f;
+        for (int u = 0; u < U; ++u) {
+            const int c = c0 + 32 * u;
+            if (c < nchunks) {
+                float g[8], m[8];
+                graw[u].unpack(g);
+                const uint32_t cw[2] = {craw[u].x, craw[u].y};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t code = (cw[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+                    const float cur = old_mag * s.cb[code];
+                    m[i] = ema_update(beta1, cur, omb1, g[i]);
+                    absmax = max_abs_nan(absmax, m[i]);
+                    sumsq = fmaf(g[i], g[i], sumsq);
+                }
+                stage_a[c] = make_float4(m[0], m[1], m[2], m[3]);
+                stage_b[c] = make_float4(m[4], m[5], m[6], m[7]);
+            }
         }
     }
     absmax = warp_max_nan(absmax);
@@ -246,7 +237,7 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
             step = stepsize[b];
         } else {
             float v;
-            if (t.flags & GEFEN_B200_STEP_FUSE_VMEAN) {
+            if (flags & GEFEN_B200_STEP_FUSE_VMEAN) {
                 const float mean_sq = warp_sum(sumsq) / static_cast<float>(t.period);
                 const float prev = load_state(t.v, b, t.v_dtype);
                 const float nv = fmaf(t.beta2, prev, (1.0f - t.beta2) * mean_sq);
@@ -259,119 +250,125 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
             step = adam_step_size(v, t.bc1, t.bc2, t.eps);
         }
     }
+    __syncwarp();  // staged momenta are visible to the whole warp; every lane has read the old magnitude
 
     // ---- rare: a NaN or Inf in the block. The reference's max ignores NaN; redo it that way and
     // let the exact (threshold) quantiser handle non-finite quotients.
-    bool exact_path = false;
+    bool exact_path = s.slow;
     if (!(absmax <= 3.0e38f)) {
-        float m = 0.0f;
+        float mx = 0.0f;
+        for (int c = lane; c < nchunks; c += 32) {
+            const float4 a = stage_a[c], d = stage_b[c];
+            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
+            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(d.x), fabsf(d.y)), fmaxf(fabsf(d.z), fabsf(d.w))));
+        }
 #pragma unroll
-        for (int r = 0; r < R; ++r)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(upd[r][i]));
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        absmax = m;
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        absmax = mx;
         exact_path = true;
     }
-    __syncwarp();  // every lane has read the old magnitude
     if (lane == 0) store_state(t.mag, b, t.mag_dtype, absmax);
 
     const bool nonzero = absmax > 0.0f;
     const bool fastdiv = !exact_path && div_range_ok(absmax);
     const float rinv = fastdiv ? 1.0f / absmax : 0.0f;
     const bool do_update = muon || t.lr != 0.0f;
-    const bool wd = (t.flags & GEFEN_B200_STEP_WEIGHT_DECAY) != 0;
-    const bool nesterov = (t.flags & GEFEN_B200_STEP_NESTEROV) != 0;
+    const bool wd = (flags & GEFEN_B200_STEP_WEIGHT_DECAY) != 0;
+    const bool nesterov = (flags & GEFEN_B200_STEP_NESTEROV) != 0;
+    const float lr = t.lr;
+    const float wd_mul = t.wd_mul;
 
     // ---- re-encode and update
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int c = r * 32 + lane;
-        if (c < nchunks) {
-            Chunk<S> praw;
-            if (!muon && do_update) praw.load(t.p, chunk0 + c);
-            uint32_t cw[2] = {0u, 0u};
-            float q[8];
+    for (int c = lane; c < nchunks; c += 32) {
+        Chunk<S> praw;
+        if (!muon && do_update) praw.load(t.p, chunk0 + c);
+        const float4 ma = stage_a[c], mb = stage_b[c];
+        const float m[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};
+        uint32_t cw[2] = {0u, 0u};
+        float q[8];
+        if (fastdiv) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const float u = upd[r][i];
-                float x = 0.0f;
-                if (nonzero) x = fastdiv ? div_by_block_constant(u, absmax, rinv) : u / absmax;
-                const uint32_t code = exact_path ? static_cast<uint32_t>(entry_exact(x, s.thr, s.cb, s.k))
-                                                 : quantize(s, x);
+                const float x = div_by_block_constant(m[i], absmax, rinv);
+                bool unused;
+                const uint32_t code = static_cast<uint32_t>(lut_query(x, s.lut, &unused));
                 cw[i >> 2] |= code << (8 * (i & 3));
-                q[i] = dequant<REP>(s, code, lane) * absmax;
+                q[i] = s.cb[code] * absmax;
             }
-            codes_out[c] = make_uint2(cw[0], cw[1]);
-            if (muon) {
-                if (nesterov) {
-                    // torch: m.mul_(momentum).add_(g, alpha=1-momentum) on the rounded momentum
-                    // (reference: gefen_muon.py:312-314); alpha travels in t.beta2.
-                    Chunk<S> g2;
-                    g2.load(t.g, chunk0 + c);
-                    float g[8];
-                    g2.unpack(g);
+        } else {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float m1 = ScalarIO<S>::round(ScalarIO<S>::round(q[i]) * beta1);
-                        q[i] = fmaf(t.beta2, g[i], m1);
-                    }
-                }
-                Chunk<S> out;
-                out.pack(q);
-                out.store(t.p, chunk0 + c);
-            } else if (do_update) {
-                float pv[8];
-                praw.unpack(pv);
+            for (int i = 0; i < 8; ++i) {
+                float x = 0.0f;
+                if (nonzero) x = m[i] / absmax;
+                const uint32_t code = static_cast<uint32_t>(entry_exact(x, s.thr, s.cb, s.k));
+                cw[i >> 2] |= code << (8 * (i & 3));
+                q[i] = s.cb[code] * absmax;
+            }
+        }
+        codes_out[c] = make_uint2(cw[0], cw[1]);
+        if (muon) {
+            if (nesterov) {
+                // torch: m.mul_(momentum).add_(g, alpha=1-momentum) on the rounded momentum
+                // (reference: gefen_muon.py:312-314); alpha travels in t.beta2.
+                Chunk<S> g2;
+                g2.load(t.g, chunk0 + c);
+                float g[8];
+                g2.unpack(g);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    float pi = pv[i];
-                    if (wd) pi = ScalarIO<S>::round(pi * t.wd_mul);
-                    pv[i] = fmaf(-(q[i] * step), t.lr, pi);
+                    const float m1 = ScalarIO<S>::round(ScalarIO<S>::round(q[i]) * beta1);
+                    q[i] = fmaf(t.beta2, g[i], m1);
                 }
-                praw.pack(pv);
-                praw.store(t.p, chunk0 + c);
             }
+            Chunk<S> out;
+            out.pack(q);
+            out.store(t.p, chunk0 + c);
+        } else if (do_update) {
+            float pv[8];
+            praw.unpack(pv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float pi = pv[i];
+                if (wd) pi = ScalarIO<S>::round(pi * wd_mul);
+                pv[i] = fmaf(-(q[i] * step), lr, pi);
+            }
+            praw.pack(pv);
+            praw.store(t.p, chunk0 + c);
         }
     }
+    __syncwarp();  // the staging slice is free for this warp's next block
 }
 
-template <typename S, int R, bool REP>
-__global__ void __launch_bounds__(kThreads) step_vec_kernel(const __grid_constant__ StepLaunch L,
-                                                            const __grid_constant__ gefen_b200_step_tensor_t single) {
+template <typename S>
+__global__ void __launch_bounds__(512) step_vec_kernel(const __grid_constant__ StepLaunch L,
+                                                           const __grid_constant__ gefen_b200_step_tensor_t single) {
     extern __shared__ __align__(128) unsigned char smem[];
     SmemView s;
-    if (!stage_tables<REP>(L.ws, smem, s)) return;
+    if (!stage_tables(L.ws, smem, s)) return;
+    const gefen_b200_step_tensor_t* table = L.table != nullptr ? L.table : &single;
 
-    __shared__ gefen_b200_step_tensor_t wcache[kWarps];  // the tensor each warp is working on
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    const long long warp_global = static_cast<long long>(blockIdx.x) * kWarps + warp;
-    const long long warp_stride = static_cast<long long>(gridDim.x) * kWarps;
-    long long cached_first = 0, cached_end = 0;
+    const int warps = blockDim.x >> 5;
+    float* stage = reinterpret_cast<float*>(smem + kSmemWs) + static_cast<size_t>(warp) * L.stage_floats;
+    const long long warp_global = static_cast<long long>(blockIdx.x) * warps + warp;
+    const long long warp_stride = static_cast<long long>(gridDim.x) * warps;
+    int ti = 0;
+    gefen_b200_step_tensor_t t = table[0];
     for (long long gb = warp_global; gb < L.total_blocks; gb += warp_stride) {
-        if (L.table == nullptr) {
-            warp_block_step<S, R, REP>(single, gb, L.stepsize, s, lane);
-        } else {
-            if (gb < cached_first || gb >= cached_end) {
-                const int ti = find_tensor(L.table, L.n_tensors, gb);
-                constexpr int kWords = sizeof(gefen_b200_step_tensor_t) / 4;
-                const uint32_t* src = reinterpret_cast<const uint32_t*>(L.table + ti);
-                uint32_t* dst = reinterpret_cast<uint32_t*>(&wcache[warp]);
-                __syncwarp();
-                if (lane < kWords) dst[lane] = src[lane];
-                __syncwarp();
-                cached_first = wcache[warp].first_block;
-                cached_end = cached_first + wcache[warp].num_blocks;
-            }
-            warp_block_step<S, R, REP>(wcache[warp], gb - cached_first, nullptr, s, lane);
+        if (gb < t.first_block || gb >= t.first_block + t.num_blocks) {
+            ti = find_tensor(table, L.n_tensors, gb);
+            t = table[ti];
         }
+        warp_block_step<S>(t, gb - t.first_block, L.stepsize, s, stage, lane);
     }
 }
 
 // --------------------------------------------------------------------------- generic path
 // GROUP = 32: one warp per block; GROUP = 256: one CTA per block. Two passes, scalar accesses.
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
 template <typename S, int GROUP>
 __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_constant__ StepLaunch L,
                                                                 const __grid_constant__ gefen_b200_step_tensor_t single) {
@@ -379,7 +376,8 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
     __shared__ float red_max[kWarps];
     __shared__ float red_sum[kWarps];
     SmemView s;
-    if (!stage_tables<false>(L.ws, smem, s)) return;
+    if (!stage_tables(L.ws, smem, s)) return;
+    const gefen_b200_step_tensor_t* table = L.table != nullptr ? L.table : &single;
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -390,30 +388,28 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
                                                  : static_cast<long long>(gridDim.x);
 
     for (long long gb = group_global; gb < L.total_blocks; gb += group_stride) {
-        gefen_b200_step_tensor_t t;
-        long long b;
-        if (L.table == nullptr) {
-            t = single;
-            b = gb;
-        } else {
-            t = L.table[find_tensor(L.table, L.n_tensors, gb)];
-            b = gb - t.first_block;
-        }
-        const long long start = b * t.period;
-        const int period = static_cast<int>(t.period);
-        const bool muon = (t.flags & GEFEN_B200_STEP_MUON) != 0;
-        const bool period1 = (t.flags & GEFEN_B200_STEP_PERIOD1) != 0;
-        const bool fuse_v = (t.flags & GEFEN_B200_STEP_FUSE_VMEAN) != 0;
-        const bool wd = (t.flags & GEFEN_B200_STEP_WEIGHT_DECAY) != 0;
-        const bool nesterov = (t.flags & GEFEN_B200_STEP_NESTEROV) != 0;
-        const S* g = static_cast<const S*>(t.g) + start;
-        S* p = static_cast<S*>(t.p) + start;
-        uint8_t* codes = t.codes + start;
-        const float beta1 = t.beta1;
+        const gefen_b200_step_tensor_t* tp = table + find_tensor(table, L.n_tensors, gb);
+        const long long b = gb - tp->first_block;
+        const int period = static_cast<int>(tp->period);
+        const long long start = b * period;
+        const uint32_t flags = tp->flags;
+        const bool muon = (flags & GEFEN_B200_STEP_MUON) != 0;
+        const bool period1 = (flags & GEFEN_B200_STEP_PERIOD1) != 0;
+        const bool fuse_v = (flags & GEFEN_B200_STEP_FUSE_VMEAN) != 0;
+        const bool wd = (flags & GEFEN_B200_STEP_WEIGHT_DECAY) != 0;
+        const bool nesterov = (flags & GEFEN_B200_STEP_NESTEROV) != 0;
+        const S* g = static_cast<const S*>(tp->g) + start;
+        S* prm = static_cast<S*>(tp->p) + start;
+        uint8_t* codes = tp->codes + start;
+        void* mag_ptr = tp->mag;
+        void* v_ptr = tp->v;
+        const int mag_dtype = tp->mag_dtype, v_dtype = tp->v_dtype;
+        const float beta1 = tp->beta1;
         const float omb1 = 1.0f - beta1;
-        const float beta2 = t.beta2;
+        const float beta2 = tp->beta2;
         const float omb2 = 1.0f - beta2;
-        const float old_mag = load_state(t.mag, b, t.mag_dtype);
+        const float lr = tp->lr, bc1 = tp->bc1, bc2 = tp->bc2, eps = tp->eps, wd_mul = tp->wd_mul;
+        const float old_mag = load_state(mag_ptr, b, mag_dtype);
 
         // pass 1: NaN-ignoring absmax of the updated momentum (the reference's `>` test), sum g^2;
         // period-1 tensors update their per-element second moment here
@@ -422,8 +418,8 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
         for (int i = tig; i < period; i += GROUP) {
             const float gi = ScalarIO<S>::load(g + i);
             if (period1) {
-                const float prev = load_state(t.v, start + i, t.v_dtype);
-                store_state(t.v, start + i, t.v_dtype, fmaf(beta2, prev, (omb2 * gi) * gi));
+                const float prev = load_state(v_ptr, start + i, v_dtype);
+                store_state(v_ptr, start + i, v_dtype, fmaf(beta2, prev, (omb2 * gi) * gi));
             }
             const float cur = old_mag * s.cb[codes[i]];
             const float u = ema_update(beta1, cur, omb1, gi);
@@ -445,25 +441,28 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
 
         float step = 0.0f;
         if (!muon && !period1) {
-            if (L.stepsize != nullptr && L.table == nullptr) {
+            if (L.stepsize != nullptr) {
                 step = L.stepsize[b];
             } else {
-                float v = load_state(t.v, b, t.v_dtype);
+                float v = load_state(v_ptr, b, v_dtype);
+                float nv = 0.0f;
                 if (fuse_v) {
-                    const float mean_sq = sumsq / static_cast<float>(period);
-                    const float nv = fmaf(beta2, v, omb2 * mean_sq);
-                    // every thread computes the same rounded value; one thread stores it
-                    if (t.v_dtype == GEFEN_B200_F32) v = nv;
-                    else if (t.v_dtype == GEFEN_B200_BF16) v = __bfloat162float(__float2bfloat16_rn(nv));
+                    nv = fmaf(beta2, v, omb2 * (sumsq / static_cast<float>(period)));
+                    // every thread computes the same rounded value; one thread stores it below
+                    if (v_dtype == GEFEN_B200_F32) v = nv;
+                    else if (v_dtype == GEFEN_B200_BF16) v = __bfloat162float(__float2bfloat16_rn(nv));
                     else v = __half2float(__float2half_rn(nv));
-                    if (tig == 0) store_state(t.v, b, t.v_dtype, nv);
                 }
-                step = adam_step_size(v, t.bc1, t.bc2, t.eps);
+                step = adam_step_size(v, bc1, bc2, eps);
+                if (fuse_v) {
+                    if (GROUP > 32) __syncthreads(); else __syncwarp();  // everyone has read the old vmean
+                    if (tig == 0) store_state(v_ptr, b, v_dtype, nv);
+                }
             }
         }
         if (GROUP > 32) __syncthreads(); else __syncwarp();  // old magnitude was read by everyone
-        if (tig == 0) store_state(t.mag, b, t.mag_dtype, absmax);
-        const bool do_update = muon || period1 || t.lr != 0.0f;
+        if (tig == 0) store_state(mag_ptr, b, mag_dtype, absmax);
+        const bool do_update = muon || period1 || lr != 0.0f;
 
         // pass 2: re-encode and update
         for (int i = tig; i < period; i += GROUP) {
@@ -477,14 +476,14 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
             const float q = s.cb[code] * absmax;
             if (muon) {
                 float out = q;
-                if (nesterov) out = fmaf(t.beta2, gi, ScalarIO<S>::round(ScalarIO<S>::round(q) * beta1));
-                ScalarIO<S>::store(p + i, out);
+                if (nesterov) out = fmaf(beta2, gi, ScalarIO<S>::round(ScalarIO<S>::round(q) * beta1));
+                ScalarIO<S>::store(prm + i, out);
             } else if (do_update) {
                 float st = step;
-                if (period1) st = adam_step_size(load_state(t.v, start + i, t.v_dtype), t.bc1, t.bc2, t.eps);
-                float pi = ScalarIO<S>::load(p + i);
-                if (wd) pi = ScalarIO<S>::round(pi * t.wd_mul);
-                ScalarIO<S>::store(p + i, fmaf(-(q * st), t.lr, pi));
+                if (period1) st = adam_step_size(load_state(v_ptr, start + i, v_dtype), bc1, bc2, eps);
+                float pi = ScalarIO<S>::load(prm + i);
+                if (wd) pi = ScalarIO<S>::round(pi * wd_mul);
+                ScalarIO<S>::store(prm + i, fmaf(-(q * st), lr, pi));
             }
         }
     }
@@ -540,37 +539,34 @@ static int grid_for(long long groups_needed, int groups_per_cta, int ctas_per_sm
     return static_cast<int>(ctas);
 }
 
-template <typename S, int R>
-static int launch_vec(const StepLaunch& L, const gefen_b200_step_tensor_t& single, cudaStream_t stream) {
-    constexpr bool REP = true;
-    constexpr int smem = kSmemWs + (REP ? kSmemRep : 0);
+constexpr int kFastMaxPeriod = 8192;
+constexpr int kFastMaxWarps = 16;
+constexpr int kStaticSmemSlack = 1024;  // static __shared__ of the kernels plus the per-CTA reservation
+
+template <typename S>
+static int launch_vec(StepLaunch L, const gefen_b200_step_tensor_t& single, long long max_period, cudaStream_t stream) {
     static bool configured[64];
     int dev = 0;
     GEFEN_CHECK_CUDA(cudaGetDevice(&dev));
-    auto kernel = step_vec_kernel<S, R, REP>;
+    auto kernel = step_vec_kernel<S>;
     if (dev < 64 && !configured[dev]) {
-        GEFEN_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        GEFEN_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem - kStaticSmemSlack));
         configured[dev] = true;
     }
-    const int grid = grid_for(L.total_blocks, kWarps, R >= 6 ? 2 : 3);
-    kernel<<<grid, kThreads, smem, stream>>>(L, single);
+    const long long stage_bytes = max_period * 4;
+    int warps = static_cast<int>((kMaxSmem - kStaticSmemSlack - kSmemWs) / stage_bytes);
+    if (warps > kFastMaxWarps) warps = kFastMaxWarps;
+    if (warps < 1) return fail(GEFEN_B200_EINVAL, "internal: period %lld too large for the staged path", max_period);
+    if (L.total_blocks < warps) warps = static_cast<int>(L.total_blocks);
+    const int smem = kSmemWs + static_cast<int>(stage_bytes) * warps;
+    int ctas_per_sm = (kMaxSmem - kStaticSmemSlack) / (smem + kStaticSmemSlack);
+    if (ctas_per_sm > 2) ctas_per_sm = 2;
+    if (ctas_per_sm < 1) ctas_per_sm = 1;
+    L.stage_floats = static_cast<int>(max_period);
+    const int grid = grid_for(L.total_blocks, warps, ctas_per_sm);
+    kernel<<<grid, warps * 32, smem, stream>>>(L, single);
     GEFEN_CHECK_CUDA(cudaGetLastError());
     return GEFEN_B200_OK;
-}
-
-template <typename S>
-static int launch_vec_r(int R, const StepLaunch& L, const gefen_b200_step_tensor_t& single, cudaStream_t stream) {
-    switch (R) {
-        case 1: return launch_vec<S, 1>(L, single, stream);
-        case 2: return launch_vec<S, 2>(L, single, stream);
-        case 3: return launch_vec<S, 3>(L, single, stream);
-        case 4: return launch_vec<S, 4>(L, single, stream);
-        case 5: return launch_vec<S, 5>(L, single, stream);
-        case 6: return launch_vec<S, 6>(L, single, stream);
-        case 7: return launch_vec<S, 7>(L, single, stream);
-        case 8: return launch_vec<S, 8>(L, single, stream);
-    }
-    return fail(GEFEN_B200_EINVAL, "internal: bad chunk count %d", R);
 }
 
 template <typename S>
@@ -586,34 +582,33 @@ static int launch_generic(bool cta_per_block, const StepLaunch& L, const gefen_b
         configured[dev] = true;
     }
     if (cta_per_block) {
-        const int grid = grid_for(L.total_blocks, 1, 4);
+        const int grid = grid_for(L.total_blocks, 1, 3);
         step_generic_kernel<S, 256><<<grid, kThreads, smem, stream>>>(L, single);
     } else {
-        const int grid = grid_for(L.total_blocks, kWarps, 4);
+        const int grid = grid_for(L.total_blocks, kWarps, 3);
         step_generic_kernel<S, 32><<<grid, kThreads, smem, stream>>>(L, single);
     }
     GEFEN_CHECK_CUDA(cudaGetLastError());
     return GEFEN_B200_OK;
 }
 
-// Class of a tensor: 1..8 = fast path with that many chunks per lane, 0 = generic warp per block,
-// -1 = generic CTA per block.
+// Class of a tensor: 1 = vectorised staged path, 0 = generic warp per block, -1 = generic CTA per block.
 static int tensor_class(const gefen_b200_step_tensor_t& t, int dtype) {
     const bool vec_dtype = dtype == GEFEN_B200_F32 || dtype == GEFEN_B200_BF16 || dtype == GEFEN_B200_F16;
     const bool period1 = (t.flags & GEFEN_B200_STEP_PERIOD1) != 0;
-    if (vec_dtype && !period1 && t.period % 8 == 0 && t.period <= 2048 && aligned16(t.g) &&
-        (aligned16(t.p)) && (reinterpret_cast<uintptr_t>(t.codes) & 7u) == 0) {
-        return static_cast<int>((t.period + 255) / 256);
+    if (vec_dtype && !period1 && t.period % 8 == 0 && t.period <= kFastMaxPeriod && aligned16(t.g) && aligned16(t.p) &&
+        (reinterpret_cast<uintptr_t>(t.codes) & 7u) == 0) {
+        return 1;
     }
     return t.period > 2048 ? -1 : 0;
 }
 
 static int launch_class(int cls, int dtype, const StepLaunch& L, const gefen_b200_step_tensor_t& single,
-                        cudaStream_t stream) {
+                        long long max_period, cudaStream_t stream) {
     if (cls >= 1) {
-        if (dtype == GEFEN_B200_BF16) return launch_vec_r<__nv_bfloat16>(cls, L, single, stream);
-        if (dtype == GEFEN_B200_F16) return launch_vec_r<__half>(cls, L, single, stream);
-        return launch_vec_r<float>(cls, L, single, stream);
+        if (dtype == GEFEN_B200_BF16) return launch_vec<__nv_bfloat16>(L, single, max_period, stream);
+        if (dtype == GEFEN_B200_F16) return launch_vec<__half>(L, single, max_period, stream);
+        return launch_vec<float>(L, single, max_period, stream);
     }
     const bool cta = cls < 0;
     switch (dtype) {
@@ -651,10 +646,11 @@ static int run_single(gefen_b200_step_tensor_t& t, int param_dtype, const float*
     StepLaunch L;
     L.table = nullptr;
     L.n_tensors = 1;
+    L.stage_floats = 0;
     L.total_blocks = t.num_blocks;
     L.ws = static_cast<const unsigned char*>(ws);
     L.stepsize = stepsize;
-    return launch_class(tensor_class(t, param_dtype), param_dtype, L, t, stream);
+    return launch_class(tensor_class(t, param_dtype), param_dtype, L, t, t.period, stream);
 }
 
 }  // namespace gefen
@@ -788,9 +784,9 @@ int gefen_b200_multi_tensor_step(gefen_b200_step_tensor_t* host_table, void* dev
                     "Expected non-null tables and codebook workspace.");
     GEFEN_CHECK_ARG(aligned16(codebook_ws) && aligned16(device_table), "Expected 16-byte aligned workspace and table.");
     GEFEN_CHECK_ARG(is_float_dtype(param_dtype), "Unsupported parameter dtype tag %d.", param_dtype);
-    // Tensors are launched in maximal runs of rows that share a kernel class (fast path with R
-    // chunks per lane, generic warp, generic CTA); callers that keep equal classes adjacent get one
-    // launch per class. Rows are never reordered.
+    // Tensors are launched in maximal runs of rows that share a kernel class (staged vector path,
+    // generic warp, generic CTA); callers that keep equal classes adjacent get one launch per
+    // class. Rows are never reordered.
     for (int i = 0; i < n_tensors; ++i) {
         gefen_b200_step_tensor_t& t = host_table[i];
         GEFEN_CHECK_ARG(t.g != nullptr && t.codes != nullptr && t.mag != nullptr && t.p != nullptr,
@@ -819,14 +815,17 @@ int gefen_b200_multi_tensor_step(gefen_b200_step_tensor_t* host_table, void* dev
         const int run = host_table[begin].reserved_[1];
         const gefen_b200_step_tensor_t& last = host_table[begin + run - 1];
         const long long total = last.first_block + last.num_blocks;
+        long long max_period = 0;
+        for (int i = begin; i < begin + run; ++i) max_period = host_table[i].period > max_period ? host_table[i].period : max_period;
         if (total > 0) {
             StepLaunch L;
             L.table = static_cast<const gefen_b200_step_tensor_t*>(device_table) + begin;
             L.n_tensors = run;
+            L.stage_floats = 0;
             L.total_blocks = total;
             L.ws = static_cast<const unsigned char*>(codebook_ws);
             L.stepsize = nullptr;
-            const int rc = launch_class(host_table[begin].reserved_[0], param_dtype, L, host_table[begin], stream);
+            const int rc = launch_class(host_table[begin].reserved_[0], param_dtype, L, host_table[begin], max_period, stream);
             if (rc != GEFEN_B200_OK) return rc;
         }
         begin += run;

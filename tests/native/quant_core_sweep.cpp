@@ -26,13 +26,14 @@ int main(int argc, char** argv) {
     std::vector<float> pad(256), thr(256);
     for (int i = 0; i < 256; ++i) pad[i] = cb[i < k ? i : k - 1];
     std::vector<int> tcell(256);
-    std::vector<uint32_t> toff(256);
     for (int i = 0; i < 256; ++i) {
         thr[i] = (i < k - 1) ? entry_threshold(i, pad.data(), k) : INFINITY;
-        tcell[i] = lut_threshold_cell(thr[i], &toff[i]);
+        tcell[i] = lut_threshold_cell(thr[i]);
     }
-    std::vector<uint32_t> lut(kLutWords, 0u);
-    for (int c = 0; c <= kLutCells; ++c) lut[c] = lut_build_cell(c, tcell.data(), toff.data(), k - 1, pad[k - 1]);
+    std::vector<uint32_t> lut(kLutBytes / 4, 0u);
+    for (int c = 0; c <= kLutCells; ++c)
+        lut_build_cell(c, tcell.data(), thr.data(), k - 1, pad[k - 1], &lut[2 * c], &lut[2 * c + 1]);
+    const unsigned char* lut_bytes = reinterpret_cast<const unsigned char*>(lut.data());
 
     unsigned long long bad_lut = 0, bad_thr = 0, slow_hits = 0, checked = 0;
     const uint32_t lo = float_to_ordered(-1.0f), hi = float_to_ordered(1.0f);
@@ -42,7 +43,7 @@ int main(int argc, char** argv) {
         const float x = ordered_to_float(static_cast<uint32_t>(o));
         const int want = nearest_entry_reference(x, pad.data(), k);
         bool slow;
-        int got = lut_query(x, lut.data(), &slow);
+        int got = lut_query(x, lut_bytes, &slow);
         if (slow) { ++slow_hits; got = entry_exact(x, thr.data(), pad.data(), k); }
         if (got != want) ++bad_lut;
         if (entry_exact(x, thr.data(), pad.data(), k) != want) ++bad_thr;

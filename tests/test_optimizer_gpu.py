@@ -1,0 +1,113 @@
+"""End-to-end: the `Gefen` optimizer on the GPU against the oracle's restatement of the reference
+loop, on a small transformer-shaped parameter set with the benchmark's gradient distribution."""
+import copy
+
+import pytest
+import torch
+
+from tests.util import make_grad, make_param, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(96, 64), (64,), (64, 192), (192,), (64, 256), (256, 64), (64,), (1,), (40, 36)]
+
+
+def _setup(dtype, device):
+    params_cpu = [make_param(s, 0, i, dtype) if len(s) == 2 else torch.ones(s, dtype=dtype) for i, s in enumerate(SHAPES)]
+    params_gpu = [torch.nn.Parameter(p.clone().to(device)) for p in params_cpu]
+    return params_cpu, params_gpu
+
+
+def _grads(step, dtype):
+    return [make_grad(s, 0, i, step, dtype) for i, s in enumerate(SHAPES)]
+
+
+@pytest.mark.parametrize("dtype,wd,fused", [(torch.float32, 0.0, True), (torch.float32, 0.0, False),
+                                            (torch.bfloat16, 0.1, True), (torch.bfloat16, 0.1, False),
+                                            (torch.float16, 0.01, True)])
+def test_ten_steps_match_oracle(oracle, cuda_device, dtype, wd, fused):
+    from gefen_b200 import Gefen
+    from oracle.ref_loop import OracleGefen
+
+    params_cpu, params_gpu = _setup(dtype, cuda_device)
+    ref = OracleGefen(params_cpu, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=wd)
+    opt = Gefen([("p{}".format(i), p) for i, p in enumerate(params_gpu)], lr=1e-3, betas=(0.9, 0.999), eps=1e-8,
+                weight_decay=wd, fused=fused)
+    for step in range(10):
+        grads = _grads(step, dtype)
+        for p, g in zip(params_gpu, grads):
+            p.grad = g.to(cuda_device)
+        opt.step()
+        ref.step(grads)
+        if step == 0:
+            # calibration: partition assignments and the codebook are bit-exact
+            for p, st in zip(params_gpu, ref.state):
+                assert opt.state[p]["automatic_period"] == st["automatic_period"]
+            assert torch.equal(opt._gefen_codebook.cpu(), ref.codebook)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    for p, pc, st in zip(params_gpu, params_cpu, ref.state):
+        codes = opt.state[p]["m_codebook"].cpu().int()
+        diff = (codes - st["m_codebook"].int()).abs()
+        assert float((diff == 0).float().mean()) >= 0.9999 and int(diff.max()) <= 1
+        assert rel_l2(p.detach().cpu(), pc) <= tol
+        assert rel_l2(opt.state[p]["vmean"].cpu().float(), st["vmean"].float()) <= (1e-5 if dtype == torch.float32 else 1e-2)
+        assert opt.state[p]["m_magnitude"].dtype == st["m_magnitude"].dtype
+        assert opt.state[p]["step"] == 10
+
+
+def test_state_dict_round_trip(cuda_device):
+    from gefen_b200 import Gefen
+
+    dtype = torch.bfloat16
+    _, params = _setup(dtype, cuda_device)
+    opt = Gefen(params, lr=1e-3, weight_decay=0.1)
+    for step in range(2):
+        for p, g in zip(params, _grads(step, dtype)):
+            p.grad = g.to(cuda_device)
+        opt.step()
+    sd = copy.deepcopy(opt.state_dict())
+    assert sd["gefen_global_step"] == 2 and sd["gefen_codebook"].numel() == 256
+    keys = set(sd["state"][0].keys())
+    assert {"automatic_period", "step", "m_codebook_shape", "m_codebook", "m_magnitude", "vmean"} <= keys
+
+    params2 = [torch.nn.Parameter(p.detach().clone()) for p in params]
+    opt2 = Gefen(params2, lr=1e-3, weight_decay=0.1)
+    opt2.load_state_dict(sd)
+    assert opt2.state[params2[0]]["m_codebook"].dtype == torch.uint8  # torch's cast was undone
+    assert opt2.state[params2[0]]["vmean"].dtype == dtype
+    grads = _grads(2, dtype)
+    for p, p2, g in zip(params, params2, grads):
+        p.grad = g.to(cuda_device)
+        p2.grad = g.to(cuda_device)
+    opt.step()
+    opt2.step()
+    for p, p2 in zip(params, params2):
+        assert torch.equal(p.detach(), p2.detach())
+        assert torch.equal(opt.state[p]["m_codebook"], opt2.state[p2]["m_codebook"])
+
+
+def test_codebook_relearned_from_restored_periods(cuda_device):
+    from gefen_b200 import Gefen
+
+    _, params = _setup(torch.float32, cuda_device)
+    opt = Gefen(params, lr=1e-3)
+    for p, g in zip(params, _grads(0, torch.float32)):
+        p.grad = g.to(cuda_device)
+    opt.step()
+    sd = copy.deepcopy(opt.state_dict())
+    sd["gefen_codebook"] = None
+    opt2 = Gefen([torch.nn.Parameter(p.detach().clone()) for p in params], lr=1e-3)
+    opt2.load_state_dict(sd)
+    for p, g in zip(opt2.param_groups, _grads(0, torch.float32)):
+        p["params"][0].grad = g.to(cuda_device)
+    opt2.step()
+    assert torch.equal(opt2._gefen_codebook, opt._gefen_codebook)
+
+
+def test_missing_library_is_loud(monkeypatch, cuda_device, tmp_path):
+    from gefen_b200 import _lib
+
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "nope.so")
+    with pytest.raises(_lib.GefenB200Error):
+        _lib.load()
