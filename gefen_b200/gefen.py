@@ -479,6 +479,7 @@ class Gefen(torch.optim.Optimizer):
                 "rows": rows,
                 "static_flags": rows["flags"].copy(),
                 "entries": [idxs[r] for r in order],
+                "classes": [classes[r] for r in order],
                 "device_table": torch.empty(rows.nbytes, dtype=torch.uint8, device=device),
             })
         plan.key = key

@@ -1,0 +1,348 @@
+"""ZeRO-1 style data parallelism around the Gefen step: every rank keeps the full parameters, owns
+the optimizer state of one contiguous segment of a flat layout, and a step is
+
+    reduce-scatter(gradients)  ->  Gefen step on the owned segment  ->  all-gather(parameters).
+
+The reference has no communication code at all (its only distributed awareness is unwrapping
+DTensor shards, gefen.py:692-706); this module is the exchange step the data-parallel use of the
+optimizer needs. Two properties are kept so that N ranks reproduce one rank bit for bit:
+  * segments are cut at ROW boundaries of the 2-D tensors, so every partition block of the
+    optimizer (a run of `period` elements inside a row) lives on exactly one rank;
+  * the codebook is fitted from the histogram of ALL tensors: per-piece int64 histograms are
+    gathered, pieces of one tensor are added exactly, and tensors are accumulated in float32 in
+    parameter order, which is the single-process arithmetic (reference: gefen.py:331-347).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+ALIGN = 8  # elements; keeps every piece 16-byte aligned for 2-byte dtypes
+
+
+@dataclass
+class Piece:
+    tensor: int      # index into the parameter list
+    row0: int        # first row of the tensor held by this piece (0 for 1-D tensors)
+    rows: int        # number of rows (1 for 1-D tensors)
+    cols: int        # elements per row (numel for 1-D tensors)
+    rank: int        # owner
+    offset: int      # element offset in the flat buffer
+
+    @property
+    def numel(self) -> int:
+        return self.rows * self.cols
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class FlatLayout:
+    """Places tensors, in order, into `world` equal segments of one flat buffer. A tensor that does
+    not fit in the rest of a segment is split between rows: its first piece is pushed against the
+    end of the segment and the next piece starts the following segment, so the tensor stays one
+    contiguous range of the buffer (the model's parameter is a plain view of it)."""
+
+    def __init__(self, shapes: Sequence[Tuple[int, ...]], world: int):
+        self.world = world
+        self.shapes = [tuple(s) for s in shapes]
+        dims = [(s[0], int(math.prod(s[1:]))) if len(s) >= 2 else (1, int(math.prod(s)) if len(s) else 1)
+                for s in self.shapes]
+        total = sum(r * c for r, c in dims)
+        unit = ALIGN
+        for r, c in dims:
+            if r > 1 and r * c > total // max(world, 1):  # may cover a whole segment: rows must tile it
+                unit = unit * c // math.gcd(unit, c)
+        seg = _round_up(max(-(-total // world), 1), unit)
+        while True:
+            pieces = self._fill(dims, seg)
+            if pieces is not None:
+                break
+            seg += unit
+        self.segment = seg
+        self.total = seg * world
+        self.pieces: List[Piece] = pieces
+        self.tensor_offset = [min(p.offset for p in pieces if p.tensor == t) for t in range(len(dims))]
+
+    def _fill(self, dims, seg) -> Optional[List[Piece]]:
+        """Sequential fill; returns None when `seg` is too small (the caller grows it)."""
+        pieces, rank, fill = [], 0, 0
+        for t, (rows, cols) in enumerate(dims):
+            n = rows * cols
+            start = _round_up(fill, ALIGN)
+            if start + n <= seg:
+                pieces.append(Piece(t, 0, rows, cols, rank, rank * seg + start))
+                fill = start + n
+                continue
+            fit_rows = (seg - start) // cols if rows > 1 and start < seg else 0
+            if fit_rows == 0:  # nothing of this tensor fits here: open the next segment
+                rank, fill = rank + 1, 0
+                if rank >= self.world:
+                    return None
+                if n <= seg:
+                    pieces.append(Piece(t, 0, rows, cols, rank, rank * seg))
+                    fill = n
+                    continue
+                if rows == 1:
+                    return None
+                fit_rows = seg // cols
+                if fit_rows == 0:
+                    return None
+            # split between rows: the first piece is pushed against the end of this segment, middle
+            # pieces fill their segments exactly, the last piece starts its segment
+            pieces.append(Piece(t, 0, fit_rows, cols, rank, rank * seg + seg - fit_rows * cols))
+            row0, left = fit_rows, rows - fit_rows
+            while left > 0:
+                rank += 1
+                if rank >= self.world:
+                    return None
+                fit = seg // cols
+                if left <= fit:
+                    pieces.append(Piece(t, row0, left, cols, rank, rank * seg))
+                    fill = left * cols
+                    left = 0
+                else:
+                    if seg % cols != 0:
+                        return None
+                    pieces.append(Piece(t, row0, fit, cols, rank, rank * seg))
+                    row0 += fit
+                    left -= fit
+        return pieces
+
+    def owned(self, rank: int) -> List[Piece]:
+        return [p for p in self.pieces if p.rank == rank]
+
+
+class GpuOps:
+    """Device work of the calibration, on the library's kernels."""
+
+    def predict_periods(self, grads: List[torch.Tensor]) -> List[int]:
+        from . import partitioning
+
+        launched = [partitioning.launch_period_scores(g, input_is_squared=False) if g.numel() > 1 else (1, [], None, False)
+                    for g in grads]
+        stats = [s for _, _, s, _ in launched if s is not None]
+        host = torch.cat(stats, 0).cpu() if stats else None
+        out, cur = [], 0
+        for n, cand, s, _ in launched:
+            if s is None:
+                out.append(1)
+            else:
+                out.append(partitioning.decide_period(n, cand, host[cur:cur + len(cand)]))
+                cur += len(cand)
+        return out
+
+    def histograms(self, flats_and_periods, bins: int) -> torch.Tensor:
+        from .kernels.exact_histogram_fused import gefen_exact_histogram_cuda
+
+        if not flats_and_periods:
+            return torch.zeros((0, bins), dtype=torch.int64)
+        rows = torch.zeros((len(flats_and_periods), bins), dtype=torch.int64, device=flats_and_periods[0][0].device)
+        for row, (flat, period) in zip(rows, flats_and_periods):
+            gefen_exact_histogram_cuda(flat, period, row)
+        return rows.cpu()
+
+    def fit_codebook(self, bin_counts: torch.Tensor, num_codebooks: int, device) -> torch.Tensor:
+        from . import quantization
+
+        bins = bin_counts.numel()
+        edges = torch.linspace(-1.0, 1.0, steps=bins + 1, dtype=torch.float32)
+        centers = 0.5 * (edges[:-1] + edges[1:])
+        active = bin_counts > 0
+        stats = {"active_centers": centers[active], "active_counts": bin_counts[active]}
+        return quantization.exact_dp(stats, num_codebooks, True, device=device).to(device)
+
+    def make_optimizer(self, named_pieces, **kwargs):
+        from .gefen import Gefen
+
+        return Gefen(named_pieces, **kwargs)
+
+
+class Zero1Gefen:
+    """Gefen over ZeRO-1 sharded optimizer state.
+
+    named_params: list of (name, Parameter) of ONE dtype and device. The parameters and their
+    `.grad` are re-pointed into two flat buffers (views, no copies per step). `step()` averages
+    the gradients over the ranks of `group` while scattering them, runs the Gefen step on the
+    pieces this rank owns and gathers the updated parameters.
+    """
+
+    def __init__(self, named_params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, *, group=None,
+                 ops=None, average_gradients: bool = True):
+        self.group = group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.ops = ops if ops is not None else GpuOps()
+        self.average = average_gradients
+        self.named = [(n, p) for n, p in named_params]
+        if not self.named:
+            raise ValueError("Zero1Gefen needs at least one parameter")
+        p0 = self.named[0][1]
+        self.dtype, self.device = p0.dtype, p0.device
+        for n, p in self.named:
+            if p.dtype != self.dtype or p.device != self.device:
+                raise ValueError("Zero1Gefen expects one dtype and device per instance, got {} for {}".format(p.dtype, n))
+        self.layout = FlatLayout([tuple(p.shape) for _, p in self.named], self.world)
+        self.flat_param = torch.zeros(self.layout.total, dtype=self.dtype, device=self.device)
+        self.flat_grad = torch.zeros(self.layout.total, dtype=self.dtype, device=self.device)
+        with torch.no_grad():
+            for t, (n, p) in enumerate(self.named):
+                off = self.layout.tensor_offset[t]
+                view = self.flat_param[off:off + p.numel()].view(p.shape)
+                view.copy_(p.data)
+                gview = self.flat_grad[off:off + p.numel()].view(p.shape)
+                if p.grad is not None:
+                    gview.copy_(p.grad)
+                p.data = view
+                p.grad = gview
+        seg = self.layout.segment
+        self.my_param = self.flat_param[self.rank * seg:(self.rank + 1) * seg]
+        self.my_grad = self.flat_grad[self.rank * seg:(self.rank + 1) * seg]
+        self.pieces = self.layout.owned(self.rank)
+        self.piece_params = []
+        named_pieces = []
+        for pc in self.pieces:
+            shape = (pc.rows, pc.cols) if len(self.named[pc.tensor][1].shape) >= 2 else (pc.cols,)
+            if len(self.named[pc.tensor][1].shape) > 2 and pc.rows == self.named[pc.tensor][1].shape[0]:
+                shape = tuple(self.named[pc.tensor][1].shape)
+            prm = torch.nn.Parameter(self.flat_param[pc.offset:pc.offset + pc.numel].view(shape))
+            prm.grad = self.flat_grad[pc.offset:pc.offset + pc.numel].view(shape)
+            self.piece_params.append(prm)
+            named_pieces.append(("{}#{}".format(self.named[pc.tensor][0], pc.row0), prm))
+        self.local = self.ops.make_optimizer(named_pieces, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay) \
+            if named_pieces else None
+        self.period_mismatches: List[Tuple[str, Dict[int, int]]] = []
+        self._events = None
+        self._calibrated = False
+
+    # ------------------------------------------------------------------ collectives
+    def _backend(self) -> str:
+        return dist.get_backend(self.group) if dist.is_initialized() else "none"
+
+    def _reduce_scatter(self) -> None:
+        if self.world == 1:
+            return
+        if self._backend() == "nccl":
+            op = dist.ReduceOp.AVG if self.average else dist.ReduceOp.SUM
+            dist.reduce_scatter_tensor(self.my_grad, self.flat_grad, op=op, group=self.group)
+        else:  # gloo has no reduce-scatter: reduce everything, keep the owned segment
+            dist.all_reduce(self.flat_grad, op=dist.ReduceOp.SUM, group=self.group)
+            if self.average:
+                self.my_grad.div_(self.world)
+
+    def _all_gather(self) -> None:
+        if self.world == 1:
+            return
+        if self._backend() == "nccl":
+            dist.all_gather_into_tensor(self.flat_param, self.my_param, group=self.group)
+        else:
+            seg = self.layout.segment
+            parts = [self.flat_param[r * seg:(r + 1) * seg] for r in range(self.world)]
+            gathered = [torch.empty_like(self.my_param) for _ in range(self.world)]
+            dist.all_gather(gathered, self.my_param.clone(), group=self.group)
+            for dst, src in zip(parts, gathered):
+                dst.copy_(src)
+
+    def _gather_objects(self, obj):
+        if self.world == 1:
+            return [obj]
+        out = [None] * self.world
+        dist.all_gather_object(out, obj, group=self.group)
+        return out
+
+    # ------------------------------------------------------------------ calibration
+    def _calibrate(self) -> None:
+        """Periods per piece, one period per tensor, global histogram, one codebook everywhere."""
+        from .gefen import HISTOGRAM_BINS, NUM_CODEBOOK_ENTRIES
+
+        grads = [prm.grad.detach() for prm in self.piece_params]
+        local_periods = self.ops.predict_periods(grads) if grads else []
+        mine = {(pc.tensor, pc.row0): (per, pc.numel) for pc, per in zip(self.pieces, local_periods)}
+        everyone: Dict[Tuple[int, int], Tuple[int, int]] = {}
+        for d in self._gather_objects(mine):
+            everyone.update(d)
+        # one period per tensor: the choice of its largest piece (first on ties); pieces normally agree
+        chosen: Dict[int, int] = {}
+        for t in range(len(self.named)):
+            votes = sorted(((numel, -row0, per) for (tt, row0), (per, numel) in everyone.items() if tt == t), reverse=True)
+            period = votes[0][2]
+            if any(v[2] != period for v in votes):
+                self.period_mismatches.append((self.named[t][0], {-v[1]: v[2] for v in votes}))
+                if any(v[0] % period for v in votes):
+                    period = math.gcd(*[v[2] for v in votes])
+            chosen[t] = period
+        flats = [(g.reshape(-1), chosen[pc.tensor]) for pc, g in zip(self.pieces, grads)]
+        hist = self.ops.histograms(flats, HISTOGRAM_BINS)
+        mine_h = {(pc.tensor, pc.row0): hist[i] for i, pc in enumerate(self.pieces)}
+        all_h: Dict[Tuple[int, int], torch.Tensor] = {}
+        for d in self._gather_objects(mine_h):
+            all_h.update(d)
+        bin_counts = torch.zeros(HISTOGRAM_BINS, dtype=torch.float32)
+        for t in range(len(self.named)):
+            rows = [h for (tt, _), h in sorted(all_h.items()) if tt == t]
+            if rows:
+                bin_counts.add_(torch.stack(rows).sum(0).to(torch.float32))   # int64 sum is exact
+        codebook = self.ops.fit_codebook(bin_counts, NUM_CODEBOOK_ENTRIES, self.device)
+        self.codebook = codebook
+        if self.local is not None:
+            for pc, prm in zip(self.pieces, self.piece_params):
+                self.local.state[prm]["automatic_period"] = chosen[pc.tensor]
+            self.local._gefen_codebook = codebook.contiguous()
+        self.periods = chosen
+        self._calibrated = True
+
+    # ------------------------------------------------------------------ step
+    def _mark(self):
+        if self.device.type != "cuda":
+            return None
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    @torch.no_grad()
+    def step(self):
+        marks = [self._mark()]
+        self._reduce_scatter()
+        marks.append(self._mark())
+        if not self._calibrated:
+            self._calibrate()
+        if self.local is not None:
+            self.local.step()
+        marks.append(self._mark())
+        self._all_gather()
+        marks.append(self._mark())
+        self._events = marks
+
+    def last_breakdown_ms(self):
+        """Device time of the last step's three phases (synchronises)."""
+        if not self._events or self._events[0] is None:
+            return {}
+        torch.cuda.synchronize(self.device)
+        m = self._events
+        launches = 0
+        if self.local is not None and getattr(self.local, "_plan", None) is not None:
+            launches = sum(len(set(t.get("classes", [1]))) for t in self.local._plan.tables)
+        return {"reduce_scatter": m[0].elapsed_time(m[1]), "local_step": m[1].elapsed_time(m[2]),
+                "all_gather": m[2].elapsed_time(m[3]), "kernel_launches_per_step": launches}
+
+    def zero_grad(self):
+        self.flat_grad.zero_()
+
+    def state_dict(self):
+        """This rank's shard of the optimizer state plus the (identical everywhere) codebook."""
+        return {"rank": self.rank, "world": self.world, "periods": getattr(self, "periods", None),
+                "local": None if self.local is None else self.local.state_dict()}
+
+    def load_state_dict(self, sd):
+        if sd["world"] != self.world or sd["rank"] != self.rank:
+            raise ValueError("Zero1Gefen state was saved for rank {}/{}".format(sd["rank"], sd["world"]))
+        if self.local is not None and sd["local"] is not None:
+            self.local.load_state_dict(sd["local"])
+            self.codebook = self.local._gefen_codebook
+            self._calibrated = self.codebook is not None
+        self.periods = sd.get("periods")

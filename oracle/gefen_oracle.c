@@ -26,7 +26,9 @@
 #define DT_F64 3
 
 static int g_contract = 1;
+static int g_p1_variant = 0;   /* which product the period-1 second-moment update fuses, see below */
 void oracle_set_contraction(int mode) { g_contract = mode; }
+void oracle_set_period1_variant(int v) { g_p1_variant = v; }
 int oracle_get_contraction(void) { return g_contract; }
 
 /* ---------------------------------------------------------------- dtype helpers */
@@ -209,8 +211,10 @@ void oracle_period1_update(void* p, const void* g, int s_dt, uint8_t* codes, voi
             const float gv = load_as_float(g, i, s_dt);
             const float prev = load_as_float(v, i, v_dt);
             /* beta2*prev + ((1-beta2)*g)*g */
-            const float nv = g_contract ? fmaf(beta2, prev, ((1.0f - beta2) * gv) * gv)
-                                        : beta2 * prev + (1.0f - beta2) * gv * gv;
+            float nv;
+            if (!g_contract) nv = beta2 * prev + (1.0f - beta2) * gv * gv;
+            else if (g_p1_variant == 0) nv = fmaf(beta2, prev, ((1.0f - beta2) * gv) * gv);
+            else nv = fmaf((1.0f - beta2) * gv, gv, beta2 * prev);
             store_from_float(v, i, v_dt, nv);
             const float u = two_products(beta1, old_mag * cb[codes[i]], 1.0f - beta1, gv);
             const float a = fabsf(u);
