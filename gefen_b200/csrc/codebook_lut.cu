@@ -90,6 +90,10 @@ static int launch_prepare(const float* codebook, int k, void* ws, cudaStream_t s
     return GEFEN_B200_OK;
 }
 
+int launch_codebook_prepare(const float* codebook, int codebook_size, void* ws, cudaStream_t stream) {
+    return launch_prepare(codebook, codebook_size, ws, stream);
+}
+
 // Library-owned workspaces, one per device, for callers of the reference-shaped entry points
 // that pass no workspace. Rebuilt before every use, on the caller's stream.
 static std::mutex g_ws_mutex;

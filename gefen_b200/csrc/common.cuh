@@ -51,6 +51,8 @@ static_assert(kWsLutOff + kLutBytes == GEFEN_B200_CODEBOOK_WS_BYTES, "workspace 
 // current device, rebuilt on `stream` (see codebook_lut.cu).
 int resolve_codebook_ws(const float* codebook, int codebook_size, const void* caller_ws,
                         cudaStream_t stream, const void** ws_out);
+// Enqueues the kernel that fills `ws` (device, GEFEN_B200_CODEBOOK_WS_BYTES) from `codebook`.
+int launch_codebook_prepare(const float* codebook, int codebook_size, void* ws, cudaStream_t stream);
 
 // ------------------------------------------------------------------ device helpers
 #if defined(__CUDACC__)

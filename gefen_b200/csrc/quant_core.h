@@ -149,6 +149,15 @@ GEFEN_HD int lut_query(float x, const unsigned char* lut_bytes, bool* slow) {
     return static_cast<int>(e.y & 0xFFu) + (x > c.f ? 1 : 0);
 }
 
+// Same without the flag test, for tables known to have no undecidable cell (word 1 is then the
+// bare count).
+GEFEN_HD uint32_t lut_query_fast(float x, const unsigned char* lut_bytes) {
+    const uint2v e = *reinterpret_cast<const uint2v*>(lut_bytes + lut_byte_offset(x));
+    union { float f; uint32_t u; } c;
+    c.u = e.x;
+    return e.y + (x > c.f ? 1u : 0u);
+}
+
 // ---------------------------------------------------------------------------------------------
 // a / b with b > 0 fixed per block and |a| <= b. `rb` must be the correctly rounded 1/b.
 // q0 = a*rb is within one ulp; the exact remainder (one FMA) corrects it to the IEEE quotient.

@@ -33,6 +33,11 @@ namespace gefen {
 __device__ __forceinline__ float ema_update(float beta, float cur, float omb, float g) {
     return fmaf(beta, cur, omb * g);
 }
+// In the reference's period-1 kernel (automatic_gefen_fused_kernel.cu:360, :392) nvcc fuses the other
+// product of the same expression; measured against the reference build, bit-identical with this form.
+__device__ __forceinline__ float ema_update_period1(float beta, float cur, float omb, float g) {
+    return fmaf(omb, g, beta * cur);
+}
 
 struct StepLaunch {
     const gefen_b200_step_tensor_t* table;  // device table, or nullptr: the row in the kernel params
@@ -45,11 +50,17 @@ struct StepLaunch {
 
 constexpr int kSmemWs = GEFEN_B200_CODEBOOK_WS_BYTES;
 constexpr int kMaxSmem = 227 * 1024;
+// The fast path reads the codebook twice per element with data-dependent indices. Sixteen
+// interleaved copies (entry e of copy c at word 16*e + c, copy = lane mod 16) leave at most a
+// two-way bank conflict instead of the ~3.5-way one of a single 1 KB table.
+constexpr int kRepCopies = 16;
+constexpr int kSmemRep = kMaxCodebook * kRepCopies * 4;
 
 struct SmemView {
     const float* cb;             // 256, padded with the last entry
     const float* thr;            // 256, padded with +inf
     const unsigned char* lut;    // kLutBytes
+    const float* rep;            // fast path only: kRepCopies interleaved copies of cb, offset by the lane's copy
     int k;                       // true codebook size
     bool slow;                   // the table has undecidable cells: use entry_exact
 };
@@ -73,6 +84,7 @@ __device__ __forceinline__ bool stage_tables(const unsigned char* ws, unsigned c
     view.cb = reinterpret_cast<const float*>(smem + kWsCodebookOff);
     view.thr = reinterpret_cast<const float*>(smem + kWsThresholdOff);
     view.lut = smem + kWsLutOff;
+    view.rep = nullptr;
     view.k = 1;
     view.slow = true;
     if (!ok) return false;
@@ -192,11 +204,12 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
     const float old_mag = load_state(t.mag, b, t.mag_dtype);
     float4* stage_a = reinterpret_cast<float4*>(stage);
     float4* stage_b = stage_a + nchunks;
+    const float* rep = s.rep;  // this lane's copy of the codebook: entry e at rep[e * kRepCopies]
 
     // ---- pass over codes and gradients (the only read of both)
     float absmax = 0.0f;
     float sumsq = 0.0f;
-    constexpr int U = 2;  // chunks in flight per lane
+    constexpr int U = 4;  // chunks in flight per lane
     for (int c0 = lane; c0 < nchunks; c0 += 32 * U) {
         uint2 craw[U];
         Chunk<S> graw[U];
@@ -218,7 +231,7 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const uint32_t code = (cw[i >> 2] >> (8 * (i & 3))) & 0xFFu;
-                    const float cur = old_mag * s.cb[code];
+                    const float cur = old_mag * rep[code * kRepCopies];
                     m[i] = ema_update(beta1, cur, omb1, g[i]);
                     absmax = max_abs_nan(absmax, m[i]);
                     sumsq = fmaf(g[i], g[i], sumsq);
@@ -273,39 +286,42 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
     const bool fastdiv = !exact_path && div_range_ok(absmax);
     const float rinv = fastdiv ? 1.0f / absmax : 0.0f;
     const bool do_update = muon || t.lr != 0.0f;
+    const bool load_p = !muon && do_update;
     const bool wd = (flags & GEFEN_B200_STEP_WEIGHT_DECAY) != 0;
     const bool nesterov = (flags & GEFEN_B200_STEP_NESTEROV) != 0;
     const float lr = t.lr;
     const float wd_mul = t.wd_mul;
 
-    // ---- re-encode and update
+    // ---- re-encode and update; the parameters of the next chunk are fetched while this one is encoded
+    Chunk<S> pnext;
+    if (load_p && lane < nchunks) pnext.load(t.p, chunk0 + lane);
     for (int c = lane; c < nchunks; c += 32) {
-        Chunk<S> praw;
-        if (!muon && do_update) praw.load(t.p, chunk0 + c);
+        Chunk<S> praw = pnext;
+        if (load_p && c + 32 < nchunks) pnext.load(t.p, chunk0 + c + 32);
         const float4 ma = stage_a[c], mb = stage_b[c];
         const float m[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};
-        uint32_t cw[2] = {0u, 0u};
+        uint32_t code[8];
         float q[8];
         if (fastdiv) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const float x = div_by_block_constant(m[i], absmax, rinv);
-                bool unused;
-                const uint32_t code = static_cast<uint32_t>(lut_query(x, s.lut, &unused));
-                cw[i >> 2] |= code << (8 * (i & 3));
-                q[i] = s.cb[code] * absmax;
+                code[i] = lut_query_fast(x, s.lut);
+                q[i] = rep[code[i] * kRepCopies] * absmax;
             }
         } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 float x = 0.0f;
                 if (nonzero) x = m[i] / absmax;
-                const uint32_t code = static_cast<uint32_t>(entry_exact(x, s.thr, s.cb, s.k));
-                cw[i >> 2] |= code << (8 * (i & 3));
-                q[i] = s.cb[code] * absmax;
+                code[i] = static_cast<uint32_t>(entry_exact(x, s.thr, s.cb, s.k));
+                q[i] = s.cb[code[i]] * absmax;
             }
         }
-        codes_out[c] = make_uint2(cw[0], cw[1]);
+        uint2 cw;
+        cw.x = __byte_perm(__byte_perm(code[0], code[1], 0x0040), __byte_perm(code[2], code[3], 0x0040), 0x5410);
+        cw.y = __byte_perm(__byte_perm(code[4], code[5], 0x0040), __byte_perm(code[6], code[7], 0x0040), 0x5410);
+        codes_out[c] = cw;
         if (muon) {
             if (nesterov) {
                 // torch: m.mul_(momentum).add_(g, alpha=1-momentum) on the rounded momentum
@@ -326,12 +342,15 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
         } else if (do_update) {
             float pv[8];
             praw.unpack(pv);
+            if (wd) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                float pi = pv[i];
-                if (wd) pi = ScalarIO<S>::round(pi * wd_mul);
-                pv[i] = fmaf(-(q[i] * step), lr, pi);
+                for (int i = 0; i < 8; ++i) pv[i] *= wd_mul;
+                Chunk<S> rounded;       // the separate multiply of the reference rounds to the parameter dtype
+                rounded.pack(pv);
+                rounded.unpack(pv);
             }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) pv[i] = fmaf(-(q[i] * step), lr, pv[i]);
             praw.pack(pv);
             praw.store(t.p, chunk0 + c);
         }
@@ -350,7 +369,13 @@ __global__ void __launch_bounds__(512) step_vec_kernel(const __grid_constant__ S
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int warps = blockDim.x >> 5;
-    float* stage = reinterpret_cast<float*>(smem + kSmemWs) + static_cast<size_t>(warp) * L.stage_floats;
+    {
+        float* rep = reinterpret_cast<float*>(smem + kSmemWs);
+        for (int i = threadIdx.x; i < kMaxCodebook * kRepCopies; i += blockDim.x) rep[i] = s.cb[i / kRepCopies];
+        s.rep = rep + (lane & (kRepCopies - 1));
+        __syncthreads();
+    }
+    float* stage = reinterpret_cast<float*>(smem + kSmemWs + kSmemRep) + static_cast<size_t>(warp) * L.stage_floats;
     const long long warp_global = static_cast<long long>(blockIdx.x) * warps + warp;
     const long long warp_stride = static_cast<long long>(gridDim.x) * warps;
     int ti = 0;
@@ -422,7 +447,7 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
                 store_state(v_ptr, start + i, v_dtype, fmaf(beta2, prev, (omb2 * gi) * gi));
             }
             const float cur = old_mag * s.cb[codes[i]];
-            const float u = ema_update(beta1, cur, omb1, gi);
+            const float u = period1 ? ema_update_period1(beta1, cur, omb1, gi) : ema_update(beta1, cur, omb1, gi);
             absmax = fmaxf(absmax, fabsf(u));
             sumsq = fmaf(gi, gi, sumsq);
         }
@@ -468,7 +493,7 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
         for (int i = tig; i < period; i += GROUP) {
             const float gi = ScalarIO<S>::load(g + i);
             const float cur = old_mag * s.cb[codes[i]];
-            const float u = ema_update(beta1, cur, omb1, gi);
+            const float u = period1 ? ema_update_period1(beta1, cur, omb1, gi) : ema_update(beta1, cur, omb1, gi);
             float x = 0.0f;
             if (absmax > 0.0f) x = u / absmax;
             const uint32_t code = static_cast<uint32_t>(entry_exact(x, s.thr, s.cb, s.k));
@@ -554,11 +579,11 @@ static int launch_vec(StepLaunch L, const gefen_b200_step_tensor_t& single, long
         configured[dev] = true;
     }
     const long long stage_bytes = max_period * 4;
-    int warps = static_cast<int>((kMaxSmem - kStaticSmemSlack - kSmemWs) / stage_bytes);
+    int warps = static_cast<int>((kMaxSmem - kStaticSmemSlack - kSmemWs - kSmemRep) / stage_bytes);
     if (warps > kFastMaxWarps) warps = kFastMaxWarps;
     if (warps < 1) return fail(GEFEN_B200_EINVAL, "internal: period %lld too large for the staged path", max_period);
     if (L.total_blocks < warps) warps = static_cast<int>(L.total_blocks);
-    const int smem = kSmemWs + static_cast<int>(stage_bytes) * warps;
+    const int smem = kSmemWs + kSmemRep + static_cast<int>(stage_bytes) * warps;
     int ctas_per_sm = (kMaxSmem - kStaticSmemSlack) / (smem + kStaticSmemSlack);
     if (ctas_per_sm > 2) ctas_per_sm = 2;
     if (ctas_per_sm < 1) ctas_per_sm = 1;
