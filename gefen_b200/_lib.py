@@ -62,6 +62,8 @@ def _declare(lib):
         "gefen_b200_automatic_vmean_update": (i32, [vp, i32, vp, i32, i64, i64, dbl, vp]),
         "gefen_b200_automatic_gefen_fused_update_from_vmean": (
             i32, [vp, vp, i32, vp, vp, i32, vp, i32, vp, i32, vp, i32, i64, i64, dbl, dbl, dbl, dbl, dbl, vp]),
+        "gefen_b200_automatic_gefen_fused_update_from_vmean_static_ws": (
+            i32, [vp, vp, i32, vp, vp, i32, vp, i32, vp, i32, i32, i64, i64, dbl, dbl, dbl, dbl, dbl, vp]),
         "gefen_b200_automatic_gefen_fused_update": (
             i32, [vp, vp, i32, vp, vp, i32, vp, vp, i32, vp, i32, i64, i64, dbl, dbl, vp]),
         "gefen_b200_automatic_gefen_period1_update": (

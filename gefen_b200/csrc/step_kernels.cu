@@ -24,6 +24,8 @@
 // call passes a one-row table inside the kernel parameters.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace gefen {
 
 // fp32 contraction choices. They reproduce what nvcc emits for the reference source when it is
@@ -791,6 +793,61 @@ int gefen_b200_automatic_gefen_muon_momentum(
     t.flags = GEFEN_B200_STEP_MUON;
     t.mag_dtype = magnitude_dtype; t.v_dtype = GEFEN_B200_F32;
     return run_single(t, grad_dtype, nullptr, codebook, codebook_size, codebook_ws, static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same step for callers that must not allocate device memory.
+//
+// Who needs it: code that runs after all device memory has been handed to another owner (a
+// framework's caching allocator holding the whole card, a fixed memory plan of an inference or
+// training runtime), and code on paths where an allocation is simply not allowed to happen
+// (latency-critical loops, library hooks that promise not to touch the allocator). The regular
+// entry point, when it is given no codebook workspace, allocates one per device with cudaMalloc on
+// first use; this one keeps that workspace in a fixed array inside the library image instead.
+//
+// The array costs GEFEN_B200_CODEBOOK_WS_BYTES (67 616 bytes) of device memory on every GPU that
+// loads the library, until the process exits. It is sized for the largest codebook the kernels
+// accept, 256 entries; a larger codebook is rejected. Every call rewrites the whole array from the
+// codebook it is given, on the caller's stream, before the step kernel reads it, so nothing has to
+// be cleared and consecutive calls on one stream are independent; calls that may run concurrently
+// on the same GPU (different streams) share the array and would race on it.
+static __device__ __align__(256) unsigned char g_static_codebook_ws[GEFEN_B200_CODEBOOK_WS_BYTES];
+
+// In host code the array's name is only a handle: the device address comes from the runtime, once
+// per device, with that device current.
+static std::mutex g_static_ws_mutex;
+static void* g_static_ws_address[64];
+
+static int static_codebook_ws(void** out) {
+    int dev = 0;
+    GEFEN_CHECK_CUDA(cudaGetDevice(&dev));
+    GEFEN_CHECK_ARG(dev >= 0 && dev < 64, "Unsupported device ordinal %d.", dev);
+    std::lock_guard<std::mutex> lock(g_static_ws_mutex);
+    if (g_static_ws_address[dev] == nullptr) {
+        void* address = nullptr;
+        GEFEN_CHECK_CUDA(cudaGetSymbolAddress(&address, g_static_codebook_ws));
+        g_static_ws_address[dev] = address;
+    }
+    *out = g_static_ws_address[dev];
+    return GEFEN_B200_OK;
+}
+
+int gefen_b200_automatic_gefen_fused_update_from_vmean_static_ws(
+    void* p, const void* grad_view, int param_dtype, uint8_t* m_sign, void* m_magnitude, int magnitude_dtype,
+    const void* vmean, int vmean_dtype, const float* codebook, int codebook_size, int packed_indices,
+    int64_t num_blocks, int64_t period, double beta1, double lr, double bias_correction_1,
+    double bias_correction_2, double eps, void* stream) {
+    GEFEN_CHECK_ARG(codebook != nullptr, "Expected a codebook pointer.");
+    GEFEN_CHECK_ARG(codebook_size >= 1 && codebook_size <= kMaxCodebook,
+                    "The built-in workspace holds tables for at most 256 codebook entries, got %d.", codebook_size);
+    void* ws = nullptr;
+    int rc = static_codebook_ws(&ws);
+    if (rc != GEFEN_B200_OK) return rc;
+    rc = launch_codebook_prepare(codebook, codebook_size, ws, static_cast<cudaStream_t>(stream));
+    if (rc != GEFEN_B200_OK) return rc;
+    return gefen_b200_automatic_gefen_fused_update_from_vmean(
+        p, grad_view, param_dtype, m_sign, m_magnitude, magnitude_dtype, vmean, vmean_dtype, codebook, codebook_size,
+        ws, packed_indices, num_blocks, period, beta1, lr, bias_correction_1, bias_correction_2, eps, stream);
 }
 
 int gefen_b200_step_tensor_size(void) { return static_cast<int>(sizeof(gefen_b200_step_tensor_t)); }

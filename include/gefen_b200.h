@@ -74,6 +74,22 @@ int gefen_b200_automatic_gefen_fused_update_from_vmean(
     int64_t period, double beta1, double lr, double bias_correction_1, double bias_correction_2,
     double eps, void* stream);
 
+/* The step above for callers that are not allowed to allocate device memory: processes whose
+ * whole card already belongs to another allocator, runtimes with a fixed memory plan, hooks that
+ * promise to stay away from the allocator. It has no counterpart in the reference. Instead of a
+ * caller-provided or lazily cudaMalloc'ed codebook workspace it uses a fixed array inside the
+ * library image (GEFEN_B200_CODEBOOK_WS_BYTES on every GPU that loads the library, for the life of
+ * the process), sized for the largest codebook the kernels accept: 256 entries; larger codebooks
+ * are rejected with GEFEN_B200_EINVAL. Inputs and outputs are the caller's, as above. The first
+ * call on a device looks the array's address up (cudaGetSymbolAddress), so make that first call
+ * before starting any stream capture. The array is rewritten from `codebook` on `stream` at every
+ * call; calls that can overlap on one GPU share it and race. No cudaMalloc/cudaFree is issued. */
+int gefen_b200_automatic_gefen_fused_update_from_vmean_static_ws(
+    void* p, const void* grad_view, int param_dtype, uint8_t* m_sign, void* m_magnitude,
+    int magnitude_dtype, const void* vmean, int vmean_dtype, const float* codebook,
+    int codebook_size, int packed_indices, int64_t num_blocks, int64_t period, double beta1,
+    double lr, double bias_correction_1, double bias_correction_2, double eps, void* stream);
+
 /* Replaces automatic_gefen_fused_update_cuda (gefen_cuda_binding.cpp:6-16;
  * automatic_gefen_fused_kernel.cu:556-674): same as above with a precomputed fp32 stepsize[nb]. */
 int gefen_b200_automatic_gefen_fused_update(
