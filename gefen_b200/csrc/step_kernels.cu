@@ -25,6 +25,7 @@
 #include "common.cuh"
 
 #include <mutex>
+#include <stdlib.h>
 
 namespace gefen {
 
@@ -187,11 +188,46 @@ template <> struct Chunk<float> {
     }
 };
 
+// Pulls the lines of this warp's NEXT block towards L2 while the current block is being worked on,
+// so that its loads later pay an L2 hit instead of a DRAM round trip (shared memory takes almost
+// all of L1, and the registers are busy: a hint costs neither).
+__device__ __forceinline__ void prefetch_l2_range(const void* base, long long bytes, int lane) {
+    const char* p = static_cast<const char*>(base);
+    for (long long off = static_cast<long long>(lane) * 128; off < bytes; off += 32 * 128) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p + off));
+    }
+}
+
+// The updated momenta of chunk c: from the warp's staging slice, or recomputed from codes and
+// gradients (which the first pass left in L1/L2) when the kernel runs without staging.
+template <typename S, bool STAGED>
+__device__ __forceinline__ void block_momenta(const gefen_b200_step_tensor_t& t, const SmemView& s, const float4* stage_a,
+                                              const float4* stage_b, const uint2* codes_in, long long chunk0, int c,
+                                              float old_mag, float beta1, float omb1, float (&m)[8]) {
+    if (STAGED) {
+        const float4 ma = stage_a[c], mb = stage_b[c];
+        m[0] = ma.x; m[1] = ma.y; m[2] = ma.z; m[3] = ma.w;
+        m[4] = mb.x; m[5] = mb.y; m[6] = mb.z; m[7] = mb.w;
+    } else {
+        const uint2 craw = codes_in[c];
+        Chunk<S> graw;
+        graw.load(t.g, chunk0 + c);
+        float g[8];
+        graw.unpack(g);
+        const uint32_t cw[2] = {craw.x, craw.y};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t code = (cw[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+            m[i] = ema_update(beta1, old_mag * s.rep[code * kRepCopies], omb1, g[i]);
+        }
+    }
+}
+
 // --------------------------------------------------------------------------- fast path
 // One warp, one block of t.period = 8 * nchunks elements. `stage` holds period floats for this warp:
 // the first halves of all chunks, then the second halves, so that every 128-bit shared access of
 // a warp is conflict-free.
-template <typename S>
+template <typename S, bool STAGED>
 __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& t, long long b, const float* stepsize,
                                                 const SmemView& s, float* stage, int lane) {
     const int nchunks = static_cast<int>(t.period >> 3);
@@ -211,7 +247,7 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
     // ---- pass over codes and gradients (the only read of both)
     float absmax = 0.0f;
     float sumsq = 0.0f;
-    constexpr int U = 4;  // chunks in flight per lane
+    constexpr int U = STAGED ? 4 : 2;  // chunks in flight per lane
     for (int c0 = lane; c0 < nchunks; c0 += 32 * U) {
         uint2 craw[U];
         Chunk<S> graw[U];
@@ -238,8 +274,10 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
                     absmax = max_abs_nan(absmax, m[i]);
                     sumsq = fmaf(g[i], g[i], sumsq);
                 }
-                stage_a[c] = make_float4(m[0], m[1], m[2], m[3]);
-                stage_b[c] = make_float4(m[4], m[5], m[6], m[7]);
+                if (STAGED) {
+                    stage_a[c] = make_float4(m[0], m[1], m[2], m[3]);
+                    stage_b[c] = make_float4(m[4], m[5], m[6], m[7]);
+                }
             }
         }
     }
@@ -273,9 +311,10 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
     if (!(absmax <= 3.0e38f)) {
         float mx = 0.0f;
         for (int c = lane; c < nchunks; c += 32) {
-            const float4 a = stage_a[c], d = stage_b[c];
-            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
-            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(d.x), fabsf(d.y)), fmaxf(fabsf(d.z), fabsf(d.w))));
+            float m[8];
+            block_momenta<S, STAGED>(t, s, stage_a, stage_b, codes_in, chunk0, c, old_mag, beta1, omb1, m);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(m[i]));
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -300,8 +339,8 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
     for (int c = lane; c < nchunks; c += 32) {
         Chunk<S> praw = pnext;
         if (load_p && c + 32 < nchunks) pnext.load(t.p, chunk0 + c + 32);
-        const float4 ma = stage_a[c], mb = stage_b[c];
-        const float m[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};
+        float m[8];
+        block_momenta<S, STAGED>(t, s, stage_a, stage_b, codes_in, chunk0, c, old_mag, beta1, omb1, m);
         uint32_t code[8];
         float q[8];
         if (fastdiv) {
@@ -360,8 +399,8 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
     __syncwarp();  // the staging slice is free for this warp's next block
 }
 
-template <typename S>
-__global__ void __launch_bounds__(512) step_vec_kernel(const __grid_constant__ StepLaunch L,
+template <typename S, bool STAGED>
+__global__ void __launch_bounds__(512, STAGED ? 1 : 2) step_vec_kernel(const __grid_constant__ StepLaunch L,
                                                            const __grid_constant__ gefen_b200_step_tensor_t single) {
     extern __shared__ __align__(128) unsigned char smem[];
     SmemView s;
@@ -380,14 +419,26 @@ __global__ void __launch_bounds__(512) step_vec_kernel(const __grid_constant__ S
     float* stage = reinterpret_cast<float*>(smem + kSmemWs + kSmemRep) + static_cast<size_t>(warp) * L.stage_floats;
     const long long warp_global = static_cast<long long>(blockIdx.x) * warps + warp;
     const long long warp_stride = static_cast<long long>(gridDim.x) * warps;
-    int ti = 0;
-    gefen_b200_step_tensor_t t = table[0];
+    const gefen_b200_step_tensor_t* __restrict__ tp = table;
+    long long t_first = tp->first_block, t_count = tp->num_blocks;
     for (long long gb = warp_global; gb < L.total_blocks; gb += warp_stride) {
-        if (gb < t.first_block || gb >= t.first_block + t.num_blocks) {
-            ti = find_tensor(table, L.n_tensors, gb);
-            t = table[ti];
+        if (gb < t_first || gb >= t_first + t_count) {
+            tp = table + find_tensor(table, L.n_tensors, gb);
+            t_first = tp->first_block;
+            t_count = tp->num_blocks;
         }
-        warp_block_step<S>(t, gb - t.first_block, L.stepsize, s, stage, lane);
+        const gefen_b200_step_tensor_t& t = *tp;
+        const long long nb_local = gb - t_first;
+        const long long next = nb_local + warp_stride;
+        // same tensor: hint the next block of this warp (measured: pays for 2-byte dtypes with long blocks only)
+        if (STAGED && sizeof(S) == 2 && t.period >= 1024 && next < t_count) {
+            const long long elem0 = next * t.period;
+            prefetch_l2_range(t.codes + elem0, t.period, lane);
+            prefetch_l2_range(static_cast<const char*>(t.g) + elem0 * sizeof(S), t.period * sizeof(S), lane);
+            if (!(t.flags & GEFEN_B200_STEP_MUON))
+                prefetch_l2_range(static_cast<const char*>(t.p) + elem0 * sizeof(S), t.period * sizeof(S), lane);
+        }
+        warp_block_step<S, STAGED>(t, nb_local, L.stepsize, s, stage, lane);
     }
 }
 
@@ -570,30 +621,51 @@ constexpr int kFastMaxPeriod = 8192;
 constexpr int kFastMaxWarps = 16;
 constexpr int kStaticSmemSlack = 1024;  // static __shared__ of the kernels plus the per-CTA reservation
 
-template <typename S>
-static int launch_vec(StepLaunch L, const gefen_b200_step_tensor_t& single, long long max_period, cudaStream_t stream) {
+// GEFEN_B200_STEP_STAGED=0/1 in the environment overrides the choice of fast-path variant (for
+// measurements); by default the staged variant is used.
+static int staged_default() {
+    static int cached = -1;
+    if (cached < 0) {
+        const char* e = getenv("GEFEN_B200_STEP_STAGED");
+        cached = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return cached;
+}
+
+template <typename S, bool STAGED>
+static int launch_vec_variant(StepLaunch L, const gefen_b200_step_tensor_t& single, long long max_period,
+                              cudaStream_t stream) {
     static bool configured[64];
     int dev = 0;
     GEFEN_CHECK_CUDA(cudaGetDevice(&dev));
-    auto kernel = step_vec_kernel<S>;
+    auto kernel = step_vec_kernel<S, STAGED>;
     if (dev < 64 && !configured[dev]) {
         GEFEN_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem - kStaticSmemSlack));
         configured[dev] = true;
     }
-    const long long stage_bytes = max_period * 4;
-    int warps = static_cast<int>((kMaxSmem - kStaticSmemSlack - kSmemWs - kSmemRep) / stage_bytes);
-    if (warps > kFastMaxWarps) warps = kFastMaxWarps;
-    if (warps < 1) return fail(GEFEN_B200_EINVAL, "internal: period %lld too large for the staged path", max_period);
+    const long long stage_bytes = STAGED ? max_period * 4 : 0;
+    int warps = kFastMaxWarps;
+    if (STAGED) {
+        warps = static_cast<int>((kMaxSmem - kStaticSmemSlack - kSmemWs - kSmemRep) / stage_bytes);
+        if (warps > kFastMaxWarps) warps = kFastMaxWarps;
+        if (warps < 1) return fail(GEFEN_B200_EINVAL, "internal: period %lld too large for the staged path", max_period);
+    }
     if (L.total_blocks < warps) warps = static_cast<int>(L.total_blocks);
     const int smem = kSmemWs + kSmemRep + static_cast<int>(stage_bytes) * warps;
     int ctas_per_sm = (kMaxSmem - kStaticSmemSlack) / (smem + kStaticSmemSlack);
     if (ctas_per_sm > 2) ctas_per_sm = 2;
     if (ctas_per_sm < 1) ctas_per_sm = 1;
-    L.stage_floats = static_cast<int>(max_period);
+    L.stage_floats = STAGED ? static_cast<int>(max_period) : 0;
     const int grid = grid_for(L.total_blocks, warps, ctas_per_sm);
     kernel<<<grid, warps * 32, smem, stream>>>(L, single);
     GEFEN_CHECK_CUDA(cudaGetLastError());
     return GEFEN_B200_OK;
+}
+
+template <typename S>
+static int launch_vec(StepLaunch L, const gefen_b200_step_tensor_t& single, long long max_period, cudaStream_t stream) {
+    if (staged_default()) return launch_vec_variant<S, true>(L, single, max_period, stream);
+    return launch_vec_variant<S, false>(L, single, max_period, stream);
 }
 
 template <typename S>
