@@ -287,6 +287,37 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     return result, e2e
 
 
+def run_microbench(spec: str, steps: int, warmup: int):
+    """Single-tensor step kernel on seeded random state, e.g. bf16:2048:65536 = dtype:period:blocks.
+    Small enough for profiler captures; prints one JSON line."""
+    from gefen_b200.kernels.automatic_gefen_fused import automatic_gefen_fused_update_from_vmean_cuda
+
+    name, period, blocks = spec.split(":")
+    period, blocks = int(period), int(blocks)
+    dtype = {"bf16": torch.bfloat16, "f32": torch.float32, "f16": torch.float16}[name]
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    inner = torch.sort(torch.tanh(torch.randn(254, generator=gen, device=dev) * 0.6)).values
+    cb = torch.cat([torch.tensor([-1.0], device=dev), inner, torch.tensor([1.0], device=dev)]).float().contiguous()
+    g = (torch.randn(blocks, period, generator=gen, device=dev) * 1e-3).to(dtype)
+    p = (torch.randn(blocks, period, generator=gen, device=dev) * 0.02).to(dtype)
+    codes = torch.randint(0, 256, (blocks, period), dtype=torch.uint8, generator=gen, device=dev)
+    mag = (torch.rand(blocks, 1, generator=gen, device=dev) * 2e-3).to(dtype)
+    v = (torch.rand(blocks, 1, generator=gen, device=dev) * 1e-6 + 1e-9).to(dtype)
+    args = (0.9, 3e-4, 1 - 0.9 ** 3, 1 - 0.999 ** 3, 1e-8)
+
+    def once():
+        automatic_gefen_fused_update_from_vmean_cuda(p, g, codes, mag, v, cb, False, *args)
+
+    for _ in range(max(warmup, 3)):
+        once()
+    ms = timed(once, steps)
+    bytes_per_launch = blocks * period * (3 * p.element_size() + 2) + blocks * 4 * p.element_size()
+    peak, kind = measured_peaks()
+    print(json.dumps({"microbench": spec, "ms_per_launch": ms, "algorithmic_bytes": bytes_per_launch,
+                      "achieved_gbs": bytes_per_launch / ms / 1e6, "frac_of_{}_peak".format(kind): bytes_per_launch / ms / 1e6 / peak}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -298,7 +329,11 @@ def main():
                     help="size of the CPU baseline's sample of the workload, in elements")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--microbench", default=None, help="dtype:period:blocks, single-tensor step kernel only")
     args = ap.parse_args()
+    if args.microbench:
+        run_microbench(args.microbench, args.steps, args.warmup)
+        return
     cfg = WORKLOADS[args.workload]
 
     rank = int(os.environ.get("RANK", "0"))
