@@ -78,11 +78,13 @@ def _declare(lib):
         "gefen_b200_average_within_block_coefficient_of_variation": (i32, [vp, i32, i64, i64, i32, vp, vp]),
         "gefen_b200_period_scratch_doubles": (i64, [i64, i64]),
         "gefen_b200_average_adjacent_log_block_mean_difference": (i32, [vp, i32, i64, i64, i32, dbl, vp, vp, vp]),
+        "gefen_b200_period_scan_scratch_doubles": (i64, [i64, vp, i32]),
         "gefen_b200_period_scan": (i32, [vp, i32, i64, i32, dbl, vp, i32, vp, vp, vp]),
         "gefen_b200_lloyd_accumulate": (i32, [vp, i32, i64, i64, vp, i32, vp, vp, vp, vp]),
         "gefen_b200_lloyd_mse": (i32, [vp, i32, i64, i64, vp, vp, i32, vp, vp, vp, vp]),
         "gefen_b200_exact_dp_scratch_bytes": (i64, [i32, i32]),
         "gefen_b200_exact_dp": (i32, [vp, vp, vp, i32, i32, i32, vp, vp, vp]),
+        "gefen_b200_ns_gemm_tn": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i64, dbl, dbl, vp, vp]),
     }
     for name, (restype, argtypes) in sig.items():
         fn = getattr(lib, name)

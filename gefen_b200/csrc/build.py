@@ -25,6 +25,7 @@ SOURCES = [
     "step_kernels.cu",
     "calib_kernels.cu",
     "exact_dp.cu",
+    "ns_gemm.cu",
 ]
 HEADERS = ["common.cuh", "quant_core.h", "../../include/gefen_b200.h"]
 

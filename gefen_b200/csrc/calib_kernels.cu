@@ -11,6 +11,9 @@
 // a block's elements, where one is needed, comes from L1.
 #include "common.cuh"
 
+#include <algorithm>
+#include <vector>
+
 namespace gefen {
 
 constexpr int kThreads = 256;
@@ -178,6 +181,34 @@ __global__ void adjacent_diff_final_kernel(const double* __restrict__ partial, i
     }
 }
 
+// out[j] = sum of `ratio` consecutive entries of in[], added left to right: the block sums of period
+// p from those of a divisor q of p (ratio = p / q). Logs are taken once per element, not once per
+// candidate period.
+__global__ void __launch_bounds__(kThreads) regroup_sums_kernel(const double* __restrict__ in, long long ratio,
+                                                                long long num_out, double* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    if (ratio >= 64) {
+        const long long w0 = static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+        const long long stride = static_cast<long long>(gridDim.x) * kWarps;
+        for (long long j = w0; j < num_out; j += stride) {
+            const double* src = in + j * ratio;
+            double acc = 0.0;
+            for (long long i = lane; i < ratio; i += 32) acc += src[i];
+            acc = warp_sum(acc);
+            if (lane == 0) out[j] = acc;
+        }
+    } else {
+        const long long t0 = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+        const long long stride = static_cast<long long>(gridDim.x) * kThreads;
+        for (long long j = t0; j < num_out; j += stride) {
+            const double* src = in + j * ratio;
+            double acc = 0.0;
+            for (long long i = 0; i < ratio; ++i) acc += src[i];
+            out[j] = acc;
+        }
+    }
+}
+
 // Mean within-block variance / coefficient of variation of x (= v or v*v), fp32 sums
 // (reference: period_variance_kernel.cu:13-106). One warp per block.
 template <typename S, bool SQUARED, bool COV>
@@ -334,29 +365,82 @@ static int check_flat(const void* values, int dtype, int64_t numel, int64_t peri
 
 constexpr int kMaxPartials = 1024;
 
+static int launch_block_logsums(const void* values, int dtype, int64_t numel, int64_t period, bool squared, double eps,
+                                double* sums, unsigned long long* invalid, cudaStream_t stream) {
+    const int64_t nb = numel / period;
+    const int grid = period >= 64 ? persistent_grid(nb, kWarps, 8) : persistent_grid(nb, kThreads, 8);
+    GEFEN_DISPATCH_S(dtype, {
+        if (squared)
+            block_logsum_kernel<S, true><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(values), period, nb, eps, sums, invalid);
+        else
+            block_logsum_kernel<S, false><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(values), period, nb, eps, sums, invalid);
+    });
+    GEFEN_CHECK_CUDA(cudaGetLastError());
+    return GEFEN_B200_OK;
+}
+
+// score = mean over adjacent pairs of |S[j+1]/P - S[j]/P|; `partial` holds kMaxPartials doubles.
+static int launch_adjacent_score(const double* sums, int64_t nb, int64_t period, const unsigned long long* invalid,
+                                 double* partial, double* stats, cudaStream_t stream) {
+    const int64_t pairs = nb - 1;
+    int n_partial = static_cast<int>((pairs + 4095) / 4096);
+    if (n_partial > kMaxPartials) n_partial = kMaxPartials;
+    if (n_partial < 1) n_partial = 1;
+    adjacent_diff_partial_kernel<<<n_partial, kThreads, 0, stream>>>(sums, pairs, static_cast<double>(period), partial);
+    GEFEN_CHECK_CUDA(cudaGetLastError());
+    adjacent_diff_final_kernel<<<1, 32, 0, stream>>>(partial, n_partial, static_cast<double>(pairs), invalid, stats);
+    GEFEN_CHECK_CUDA(cudaGetLastError());
+    return GEFEN_B200_OK;
+}
+
 static int adjacent_score(const void* values, int dtype, int64_t numel, int64_t period, bool squared, double eps,
                           double* stats, double* block_sums, cudaStream_t stream) {
     const int64_t nb = numel / period;
     unsigned long long* invalid = reinterpret_cast<unsigned long long*>(block_sums + nb);
     double* partial = block_sums + nb + 1;
     GEFEN_CHECK_CUDA(cudaMemsetAsync(invalid, 0, sizeof(unsigned long long), stream));
-    const int grid = period >= 64 ? persistent_grid(nb, kWarps, 8) : persistent_grid(nb, kThreads, 8);
-    GEFEN_DISPATCH_S(dtype, {
-        if (squared)
-            block_logsum_kernel<S, true><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(values), period, nb, eps, block_sums, invalid);
-        else
-            block_logsum_kernel<S, false><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(values), period, nb, eps, block_sums, invalid);
-    });
-    GEFEN_CHECK_CUDA(cudaGetLastError());
-    const int64_t pairs = nb - 1;
-    int n_partial = static_cast<int>((pairs + 4095) / 4096);
-    if (n_partial > kMaxPartials) n_partial = kMaxPartials;
-    if (n_partial < 1) n_partial = 1;
-    adjacent_diff_partial_kernel<<<n_partial, kThreads, 0, stream>>>(block_sums, pairs, static_cast<double>(period), partial);
-    GEFEN_CHECK_CUDA(cudaGetLastError());
-    adjacent_diff_final_kernel<<<1, 32, 0, stream>>>(partial, n_partial, static_cast<double>(pairs), invalid, stats);
-    GEFEN_CHECK_CUDA(cudaGetLastError());
-    return GEFEN_B200_OK;
+    int rc = launch_block_logsums(values, dtype, numel, period, squared, eps, block_sums, invalid, stream);
+    if (rc != GEFEN_B200_OK) return rc;
+    return launch_adjacent_score(block_sums, nb, period, invalid, partial, stats, stream);
+}
+
+static int64_t gcd64(int64_t a, int64_t b) { while (b) { const int64_t t = a % b; a = b; b = t; } return a; }
+
+// Plan of the hierarchical scan: the base period (gcd of all candidates), and for every candidate
+// the largest smaller candidate (or the base) that divides it. Offsets index one scratch array:
+// [invalid | partials | base sums | sums of candidate 0 | sums of candidate 1 | ...].
+struct ScanPlan {
+    int64_t base;
+    std::vector<int> order;        // candidate indices by ascending period
+    std::vector<int> parent;       // per candidate: index of the parent candidate, -1 = base
+    std::vector<int64_t> offset;   // per candidate: offset of its sums (== base offset if period == base)
+    int64_t base_offset;
+    int64_t total;
+};
+
+static ScanPlan make_scan_plan(int64_t numel, const int64_t* periods, int n) {
+    ScanPlan plan;
+    plan.base = 0;
+    for (int i = 0; i < n; ++i) plan.base = gcd64(plan.base, periods[i]);
+    plan.order.resize(n);
+    for (int i = 0; i < n; ++i) plan.order[i] = i;
+    std::sort(plan.order.begin(), plan.order.end(), [&](int x, int y) { return periods[x] < periods[y]; });
+    plan.parent.assign(n, -1);
+    plan.offset.assign(n, 0);
+    plan.base_offset = 1 + kMaxPartials;
+    int64_t cursor = plan.base_offset + numel / plan.base;
+    for (int oi = 0; oi < n; ++oi) {
+        const int i = plan.order[oi];
+        if (periods[i] == plan.base) { plan.offset[i] = plan.base_offset; continue; }
+        for (int oj = oi - 1; oj >= 0; --oj) {
+            const int j = plan.order[oj];
+            if (periods[j] < periods[i] && periods[i] % periods[j] == 0) { plan.parent[i] = j; break; }
+        }
+        plan.offset[i] = cursor;
+        cursor += numel / periods[i];
+    }
+    plan.total = cursor;
+    return plan;
 }
 
 }  // namespace gefen
@@ -442,14 +526,21 @@ int gefen_b200_average_adjacent_log_block_mean_difference(const void* values, in
     return adjacent_score(values, dtype, numel, period, input_is_squared != 0, epsilon, stats, block_sums, stream);
 }
 
+int64_t gefen_b200_period_scan_scratch_doubles(int64_t numel, const int64_t* host_periods, int n_periods) {
+    if (numel <= 0 || n_periods <= 0 || host_periods == nullptr) return 0;
+    for (int i = 0; i < n_periods; ++i)
+        if (host_periods[i] <= 0 || numel % host_periods[i] != 0) return 0;
+    return make_scan_plan(numel, host_periods, n_periods).total;
+}
+
 int gefen_b200_period_scan(const void* values, int dtype, int64_t numel, int input_is_squared, double epsilon,
-                           const int64_t* host_periods, int n_periods, double* stats, double* block_sums,
+                           const int64_t* host_periods, int n_periods, double* stats, double* scratch,
                            void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     GEFEN_CHECK_ARG(n_periods >= 0, "Expected a non-negative number of periods.");
     if (n_periods == 0) return GEFEN_B200_OK;
-    GEFEN_CHECK_ARG(host_periods != nullptr && stats != nullptr && block_sums != nullptr,
-                    "Expected non-null periods, stats and block_sums.");
+    GEFEN_CHECK_ARG(host_periods != nullptr && stats != nullptr && scratch != nullptr,
+                    "Expected non-null periods, stats and scratch.");
     GEFEN_CHECK_ARG(epsilon > 0.0, "Expected a positive epsilon.");
     for (int i = 0; i < n_periods; ++i) {
         int rc = check_flat(values, dtype, numel, host_periods[i]);
@@ -457,9 +548,28 @@ int gefen_b200_period_scan(const void* values, int dtype, int64_t numel, int inp
         GEFEN_CHECK_ARG(numel / host_periods[i] >= 2, "Expected at least two blocks for period %lld.",
                         static_cast<long long>(host_periods[i]));
     }
-    for (int i = 0; i < n_periods; ++i) {
-        int rc = adjacent_score(values, dtype, numel, host_periods[i], input_is_squared != 0, epsilon, stats + 2 * i,
-                                block_sums, stream);
+    const ScanPlan plan = make_scan_plan(numel, host_periods, n_periods);
+    unsigned long long* invalid = reinterpret_cast<unsigned long long*>(scratch);
+    double* partial = scratch + 1;
+    GEFEN_CHECK_CUDA(cudaMemsetAsync(invalid, 0, sizeof(unsigned long long), stream));
+    // the only pass over the tensor: log sums at the base granularity
+    int rc = launch_block_logsums(values, dtype, numel, plan.base, input_is_squared != 0, epsilon,
+                                  scratch + plan.base_offset, invalid, stream);
+    if (rc != GEFEN_B200_OK) return rc;
+    for (int oi = 0; oi < n_periods; ++oi) {
+        const int i = plan.order[oi];
+        const int64_t p = host_periods[i];
+        const int64_t nb = numel / p;
+        double* sums = scratch + plan.offset[i];
+        if (p != plan.base) {
+            const int64_t q = plan.parent[i] < 0 ? plan.base : host_periods[plan.parent[i]];
+            const double* src = scratch + (plan.parent[i] < 0 ? plan.base_offset : plan.offset[plan.parent[i]]);
+            const int64_t ratio = p / q;
+            const int grid = ratio >= 64 ? persistent_grid(nb, kWarps, 8) : persistent_grid(nb, kThreads, 8);
+            regroup_sums_kernel<<<grid, kThreads, 0, stream>>>(src, ratio, nb, sums);
+            GEFEN_CHECK_CUDA(cudaGetLastError());
+        }
+        rc = launch_adjacent_score(sums, nb, p, invalid, partial, stats + 2 * i, stream);
         if (rc != GEFEN_B200_OK) return rc;
     }
     return GEFEN_B200_OK;

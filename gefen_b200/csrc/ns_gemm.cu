@@ -1,0 +1,333 @@
+// bf16 GEMM on the 5th-generation tensor cores for GefenMuon's Newton-Schulz iteration
+// (reference: gefen_muon.py:16-51, where the three products per iteration are torch.addmm / `@`,
+// i.e. cuBLAS):
+//
+//     D[M,N] = alpha * A[M,K] * B[N,K]^T + beta * C[M,N]        (bf16 in/out, fp32 accumulation)
+//
+// and optionally Dt[N,M] = D^T in the same pass. Both operands are K-major (row-major with K
+// contiguous), which covers every product of the iteration once X and X^T are both kept:
+//     G  = X X^T               A = B = X
+//     Bm = b*G + c*G*G         A = B = C = G      (G is symmetric, so G*G = G*G^T)
+//     X' = a*X + Bm*X          A = Bm, B = X^T, C = X, Dt receives X'^T for the next iteration
+//
+// Structure (one 128 x BN output tile per CTA, 6 warps):
+//   warp 4  : TMA producer. cp.async.bulk.tensor 2-D loads of 128x64 (A) and BNx64 (B) bf16 boxes,
+//             128-byte swizzle, into a STAGES-deep shared-memory ring, completion on mbarriers.
+//   warp 5  : allocates TMEM and issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=BN, K=16)
+//             from one thread; tcgen05.commit releases ring slots and finally signals the epilogue.
+//   warps 0-3: epilogue. tcgen05.ld of the fp32 accumulators (lane = row), alpha/beta, bf16 stores.
+// Every mbarrier wait is bounded: on a time-out the CTA raises a flag in global memory, the
+// roles drain, TMEM is released and the kernel returns.
+#include "common.cuh"
+
+#include <cuda.h>
+#include <mutex>
+
+namespace gefen {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;                 // 64 bf16 = one 128-byte swizzle row
+constexpr int kGemmThreads = 192;
+constexpr uint32_t kSpinLimit = 20000000u;
+
+struct GemmArgs {
+    const __nv_bfloat16* c;
+    __nv_bfloat16* d;
+    __nv_bfloat16* dt;
+    int M, N, K;
+    long long ldc, ldd, lddt;
+    float alpha, beta;
+    int* status;
+};
+
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((it & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major, 128-byte-swizzled tile whose rows are 128 bytes
+// apart: 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100),
+// layout type 2 (SWIZZLE_128B). The leading byte offset is not used by swizzled K-major layouts.
+__device__ __forceinline__ uint64_t umma_desc_k_major_sw128(uint32_t smem_addr) {
+    uint64_t desc = 0;
+    desc |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    desc |= static_cast<uint64_t>(1) << 16;
+    desc |= static_cast<uint64_t>(1024 >> 4) << 32;
+    desc |= static_cast<uint64_t>(1) << 46;
+    desc |= static_cast<uint64_t>(2) << 61;
+    return desc;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1) ns_gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                     const __grid_constant__ CUtensorMap map_b,
+                                                                     const __grid_constant__ GemmArgs args) {
+    constexpr int kABytes = kBM * kBK * 2;
+    constexpr int kBBytes = BN * kBK * 2;
+    constexpr int kStageBytes = kABytes + kBBytes;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    __shared__ uint64_t full_bar[STAGES];
+    __shared__ uint64_t empty_bar[STAGES];
+    __shared__ uint64_t acc_bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * kBM;
+    const int n0 = blockIdx.x * BN;
+    const int k_blocks = (args.K + kBK - 1) / kBK;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(&acc_bar, 1);
+        fence_mbar_init();
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 4) {
+        // ---------------- producer
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t parity = ((kb / STAGES) & 1) ^ 1;
+                if (!wait_or_abort(&empty_bar[s], parity, &abort_flag)) break;
+                mbar_expect_tx(&full_bar[s], kStageBytes);
+                unsigned char* a_dst = smem + s * kStageBytes;
+                tma_load_2d(a_dst, &map_a, kb * kBK, m0, &full_bar[s]);
+                tma_load_2d(a_dst + kABytes, &map_b, kb * kBK, n0, &full_bar[s]);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 5) {
+        // ---------------- MMA issuer
+        if (lane == 0) {
+            // instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, N = BN, M = 128
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                                       (static_cast<uint32_t>(kBM >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t parity = (kb / STAGES) & 1;
+                ok = wait_or_abort(&full_bar[s], parity, &abort_flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
+                const uint64_t desc_a = umma_desc_k_major_sw128(a_addr);
+                const uint64_t desc_b = umma_desc_k_major_sw128(a_addr + kABytes);
+#pragma unroll
+                for (int k = 0; k < kBK / 16; ++k) {
+                    // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the address field
+                    umma_bf16(tmem_base, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&empty_bar[s]);   // the slot is free once these MMAs have read it
+            }
+            umma_commit(&acc_bar);            // accumulators complete (or abandoned)
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue: warp w owns TMEM lanes (rows) 32w .. 32w+31
+        const bool ok = wait_or_abort(&acc_bar, 0, &abort_flag);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int row = m0 + warp * 32 + lane;
+        const bool row_ok = row < args.M;
+        if (ok && !abort_flag) {
+#pragma unroll 1
+            for (int j = 0; j < BN / 32; ++j) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(j * 32);
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                      "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                      "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                    : "r"(taddr)
+                    : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int col0 = n0 + j * 32;
+                if (row_ok && col0 < args.N) {
+                    float v[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = args.alpha * __uint_as_float(r[i]);
+                    const bool full_cols = col0 + 32 <= args.N;
+                    if (args.beta != 0.0f) {
+                        const __nv_bfloat16* crow = args.c + static_cast<long long>(row) * args.ldc + col0;
+                        if (full_cols && ((reinterpret_cast<uintptr_t>(crow) & 15u) == 0)) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const uint4 raw = reinterpret_cast<const uint4*>(crow)[q];
+                                const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    v[q * 8 + 2 * e] = fmaf(args.beta, __uint_as_float(w[e] << 16), v[q * 8 + 2 * e]);
+                                    v[q * 8 + 2 * e + 1] = fmaf(args.beta, __uint_as_float(w[e] & 0xFFFF0000u), v[q * 8 + 2 * e + 1]);
+                                }
+                            }
+                        } else {
+                            for (int i = 0; i < 32 && col0 + i < args.N; ++i) v[i] = fmaf(args.beta, __bfloat162float(crow[i]), v[i]);
+                        }
+                    }
+                    __nv_bfloat16* drow = args.d + static_cast<long long>(row) * args.ldd + col0;
+                    if (full_cols && ((reinterpret_cast<uintptr_t>(drow) & 15u) == 0)) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const __nv_bfloat162 h = __floats2bfloat162_rn(v[q * 8 + 2 * e], v[q * 8 + 2 * e + 1]);
+                                w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                            }
+                            reinterpret_cast<uint4*>(drow)[q] = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    } else {
+                        for (int i = 0; i < 32 && col0 + i < args.N; ++i) drow[i] = __float2bfloat16_rn(v[i]);
+                    }
+                    if (args.dt != nullptr) {
+                        // transposed copy: for a fixed column the lanes of a warp write consecutive addresses
+                        for (int i = 0; i < 32 && col0 + i < args.N; ++i)
+                            args.dt[static_cast<long long>(col0 + i) * args.lddt + row] = __float2bfloat16_rn(v[i]);
+                    }
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 5) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+    }
+    if (threadIdx.x == 0 && abort_flag && args.status != nullptr) atomicExch(args.status, 1);
+}
+
+// ------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+        }
+    });
+    return fn;
+}
+
+// [rows, K] bf16 row-major with leading dimension ld (elements); box = 64 (K) x box_rows, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, long long rows, long long k, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return fail(GEFEN_B200_ECUDA, "cuTensorMapEncodeTiled is not available from the driver.");
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return fail(GEFEN_B200_ECUDA, "cuTensorMapEncodeTiled failed with code %d.", static_cast<int>(rc));
+    return GEFEN_B200_OK;
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, cudaStream_t stream) {
+    constexpr int smem = STAGES * (kBM * kBK * 2 + BN * kBK * 2) + 1024;
+    static bool configured[64];
+    int dev = 0;
+    GEFEN_CHECK_CUDA(cudaGetDevice(&dev));
+    auto kernel = ns_gemm_tn_kernel<BN, STAGES>;
+    if (dev < 64 && !configured[dev]) {
+        GEFEN_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured[dev] = true;
+    }
+    dim3 grid((args.N + BN - 1) / BN, (args.M + kBM - 1) / kBM);
+    kernel<<<grid, kGemmThreads, smem, stream>>>(ma, mb, args);
+    GEFEN_CHECK_CUDA(cudaGetLastError());
+    return GEFEN_B200_OK;
+}
+
+}  // namespace gefen
+
+using namespace gefen;
+
+extern "C" int gefen_b200_ns_gemm_tn(const void* a, const void* b, const void* c, void* d, void* dt, int M, int N, int K,
+                                     int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, int64_t lddt, double alpha,
+                                     double beta, int* status, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    GEFEN_CHECK_ARG(a != nullptr && b != nullptr && d != nullptr, "Expected non-null A, B and D.");
+    GEFEN_CHECK_ARG(M > 0 && N > 0 && K > 0, "Expected positive GEMM sizes.");
+    GEFEN_CHECK_ARG(beta == 0.0 || c != nullptr, "Expected C when beta != 0.");
+    GEFEN_CHECK_ARG(aligned16(a) && aligned16(b) && lda % 8 == 0 && ldb % 8 == 0 && lda >= K && ldb >= K,
+                    "Expected 16-byte aligned A and B with leading dimensions that are multiples of 8 elements.");
+    GEFEN_CHECK_ARG(ldd >= N && (c == nullptr || ldc >= N) && (dt == nullptr || lddt >= M), "Bad leading dimension.");
+    const int bn = (N >= 2048 || (static_cast<long long>((M + 127) / 128) * ((N + 255) / 256)) >= sm_count()) ? 256 : 128;
+    CUtensorMap ma, mb;
+    int rc = make_map(&ma, a, M, K, lda, kBM);
+    if (rc != GEFEN_B200_OK) return rc;
+    rc = make_map(&mb, b, N, K, ldb, bn);
+    if (rc != GEFEN_B200_OK) return rc;
+    GemmArgs args;
+    args.c = static_cast<const __nv_bfloat16*>(c);
+    args.d = static_cast<__nv_bfloat16*>(d);
+    args.dt = static_cast<__nv_bfloat16*>(dt);
+    args.M = M; args.N = N; args.K = K;
+    args.ldc = ldc; args.ldd = ldd; args.lddt = lddt;
+    args.alpha = static_cast<float>(alpha);
+    args.beta = static_cast<float>(beta);
+    args.status = status;
+    if (bn == 256) return launch_gemm<256, 4>(ma, mb, args, stream);
+    return launch_gemm<128, 6>(ma, mb, args, stream);
+}

@@ -72,7 +72,7 @@ def period_scan_async(flat: torch.Tensor, periods, *, input_is_squared: bool, ep
     stats = torch.empty((n, 2), dtype=torch.float64, device=flat.device)
     if n == 0:
         return stats
-    scratch_len = lib.gefen_b200_period_scratch_doubles(flat.numel(), int(host_periods.min()))
+    scratch_len = lib.gefen_b200_period_scan_scratch_doubles(flat.numel(), host_periods.ctypes.data, n)
     scratch = torch.empty(scratch_len, dtype=torch.float64, device=flat.device)
     with _lib.device_guard(flat.device):
         _lib.check(lib.gefen_b200_period_scan(

@@ -180,12 +180,17 @@ int gefen_b200_average_adjacent_log_block_mean_difference(const void* values, in
                                                           void* stream);
 
 /* All candidate periods of one tensor in one call with no host synchronisation in between
- * (replaces the per-divisor launch + .item() loop of partitioning.py:259-268). stats holds
- * 2 * n_periods doubles: stats[2*i] = score of host_periods[i], stats[2*i+1] = its invalid
- * count. `block_sums` must hold gefen_b200_period_scratch_doubles(numel, smallest period). */
+ * (replaces the per-divisor launch + .item() loop of partitioning.py:259-268). The logarithm is
+ * taken ONCE per element: block sums are formed at the gcd of the candidate periods and every
+ * candidate's sums are regrouped from those of its largest already-computed divisor. stats holds
+ * 2 * n_periods doubles: stats[2*i] = score of host_periods[i], stats[2*i+1] = the number of
+ * elements whose log input was <= 0. `scratch` must hold
+ * gefen_b200_period_scan_scratch_doubles(numel, host_periods, n_periods) doubles. */
+int64_t gefen_b200_period_scan_scratch_doubles(int64_t numel, const int64_t* host_periods,
+                                               int n_periods);
 int gefen_b200_period_scan(const void* values, int dtype, int64_t numel, int input_is_squared,
                            double epsilon, const int64_t* host_periods, int n_periods,
-                           double* stats, double* block_sums, void* stream);
+                           double* stats, double* scratch, void* stream);
 
 /* Replace gefen_lloyd_accumulate_cuda and gefen_lloyd_mse_cuda (gefen_cuda_binding.cpp:90-105;
  * lloyd_max_fused_kernel.cu:244-356). */
@@ -207,6 +212,16 @@ int64_t gefen_b200_exact_dp_scratch_bytes(int num_points, int num_codebooks);
 int gefen_b200_exact_dp(const double* prefix_w, const double* prefix_wx, const double* prefix_wx2,
                         int num_points, int num_codebooks, int force_endpoints, void* dp_scratch,
                         float* codebook_out, void* stream);
+
+/* bf16 GEMM on the tcgen05 tensor cores for GefenMuon's Newton-Schulz iteration (replaces the
+ * torch.addmm / `@` calls, i.e. cuBLAS, of gefen_muon.py:39-47):
+ *   D[M,N] = alpha * A[M,K] * B[N,K]^T + beta * C[M,N], and Dt[N,M] = D^T when dt != NULL.
+ * All matrices bf16 row-major with leading dimensions in elements; A and B 16-byte aligned with
+ * lda, ldb multiples of 8. fp32 accumulation, one rounding to bf16. `status` (device int, may be
+ * NULL) is set to 1 if a bounded wait inside the kernel ran out. */
+int gefen_b200_ns_gemm_tn(const void* a, const void* b, const void* c, void* d, void* dt, int M,
+                          int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd,
+                          int64_t lddt, double alpha, double beta, int* status, void* stream);
 
 #ifdef __cplusplus
 }
