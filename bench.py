@@ -33,6 +33,8 @@ WORKLOADS = {
     "llama_1_5b": dict(shapes=workloads.llama_1_5b, dtype=torch.bfloat16, lr=3e-4, wd=0.1, sigma=1e-3, tau=1.0),
     "gpt2_125m": dict(shapes=workloads.gpt2_125m, dtype=torch.float32, lr=1e-3, wd=0.0, sigma=1e-3, tau=1.0),
     "llama_32b": dict(shapes=workloads.llama_32b, dtype=torch.bfloat16, lr=1.5e-4, wd=0.1, sigma=1e-3, tau=1.0),
+    "qwen3_muon": dict(shapes=workloads.qwen3_1_7b_matrices, dtype=torch.bfloat16, lr=0.02, wd=0.1, sigma=1e-3, tau=0.5,
+                       muon=True),
 }
 
 
@@ -287,6 +289,65 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     return result, e2e
 
 
+def ns_flops(shape, steps=5):
+    m, n = min(shape), max(shape)
+    return steps * (4 * m * m * n + 2 * m ** 3)
+
+
+def run_muon_arm(args, cfg):
+    """GefenMuon on the Qwen3-1.7B-shaped matrices, one GPU: whole step, then Newton-Schulz alone on
+    this library's tcgen05 GEMM and on torch's (cuBLAS) GEMMs for the same inputs."""
+    from gefen_b200 import GefenMuon
+    from gefen_b200 import newton_schulz as ns
+
+    device = torch.device("cuda", 0)
+    shapes, params, grads = build_model(cfg, device)
+    named = [(name, torch.nn.Parameter(p)) for (name, _), p in zip(shapes, params)]
+    for (_, p), g in zip(named, grads):
+        p.grad = g
+    opt = GefenMuon(named, lr=cfg["lr"], weight_decay=cfg["wd"], momentum=0.95, ns_steps=5)
+    calibration_ms = timed(opt.step, 1)
+    for _ in range(max(args.warmup - 1, 2)):
+        opt.step()
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms = timed(opt.step, args.steps)
+    clocks = sampler.stop()
+    ns.check_status(device)
+    total_flops = sum(ns_flops(s) for _, s in shapes)
+
+    def ns_all():
+        for g in grads:
+            ns.zeropower_via_newtonschulz(g, (3.4445, -4.7750, 2.0315), 5, 1e-7)
+
+    results = {}
+    for mode in ("tcgen05", "torch"):
+        ns.USE_TCGEN05 = mode == "tcgen05"
+        ns_all()
+        results[mode] = timed(ns_all, max(2, min(args.steps, 5)))
+    ns.USE_TCGEN05 = True
+    peak_file = ROOT / "MEASURED_PEAKS.json"
+    peak = json.loads(peak_file.read_text())["bf16_tflops_sustained"] if peak_file.exists() else 1400.0
+    achieved = total_flops / results["tcgen05"] / 1e9
+    elems = sum(workloads.numel(s) for _, s in shapes)
+    line = {
+        "metric": "optimizer_step_ms", "value": ms, "unit": "ms", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "optimizer": "GefenMuon(momentum=0.95, ns_steps=5)", "lr": cfg["lr"],
+                   "weight_decay": cfg["wd"], "matrices": len(shapes), "elements": elems},
+        "calibration_first_step_ms": calibration_ms, "clocks": clocks,
+        "roofline": {"bound": "tensor", "kernel": "ns_gemm_tn_kernel", "achieved": achieved, "peak": peak,
+                     "peak_kind": "measured cuBLAS bf16, sustained", "unit": "TFLOP/s", "frac": achieved / peak,
+                     "traffic": None, "algorithmic_flops_per_step": total_flops,
+                     "newton_schulz_ms": results["tcgen05"],
+                     "newton_schulz_ms_torch_cublas": results["torch"],
+                     "torch_cublas_tflops": total_flops / results["torch"] / 1e9},
+        "gpu_launches": args.steps * (len(shapes) * 15 + 8),
+    }
+    print(json.dumps(line))
+
+
 def run_microbench(spec: str, steps: int, warmup: int):
     """Single-tensor step kernel on seeded random state, e.g. bf16:2048:65536 = dtype:period:blocks.
     Small enough for profiler captures; prints one JSON line."""
@@ -344,6 +405,11 @@ def main():
         run_reference_arm(args, cfg, rank)
         return
 
+    if cfg.get("muon"):
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device")
+        run_muon_arm(args, cfg)
+        return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: gefen_b200 has no CPU path (use --impl reference for the "
                          "CPU oracle port)")

@@ -79,6 +79,19 @@ __device__ __forceinline__ uint64_t umma_desc_k_major_sw128(uint32_t smem_addr) 
     return desc;
 }
 
+// MN-major operand ([K rows][MN contiguous] in memory), 128-byte swizzle: the tile is stored as
+// groups of 64 MN-elements (one 128-byte row per K index, 8-row swizzle atoms 1024 bytes apart =
+// stride byte offset); successive 64-element groups are `group_bytes` apart (leading byte offset).
+__device__ __forceinline__ uint64_t umma_desc_mn_major_sw128(uint32_t smem_addr, uint32_t group_bytes) {
+    uint64_t desc = 0;
+    desc |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    desc |= static_cast<uint64_t>(group_bytes >> 4) << 16;
+    desc |= static_cast<uint64_t>(1024 >> 4) << 32;
+    desc |= static_cast<uint64_t>(1) << 46;
+    desc |= static_cast<uint64_t>(2) << 61;
+    return desc;
+}
+
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -92,7 +105,11 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-template <int BN, int STAGES>
+// B_MN = false: B is [N, K] row-major (K-major operand). B_MN = true: B is [K, N] row-major
+// (MN-major operand), i.e. D = alpha * A * B + beta * C without any transposed copy of B.
+// A_MN: likewise A given as [K, M] row-major (D = alpha * A^T * B ...), used for the Gram matrix of a
+// tall matrix, Y^T Y, without transposing Y.
+template <int BN, int STAGES, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1) ns_gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                      const __grid_constant__ CUtensorMap map_b,
                                                                      const __grid_constant__ GemmArgs args) {
@@ -139,8 +156,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) ns_gemm_tn_kernel(const __gri
                 if (!wait_or_abort(&empty_bar[s], parity, &abort_flag)) break;
                 mbar_expect_tx(&full_bar[s], kStageBytes);
                 unsigned char* a_dst = smem + s * kStageBytes;
-                tma_load_2d(a_dst, &map_a, kb * kBK, m0, &full_bar[s]);
-                tma_load_2d(a_dst + kABytes, &map_b, kb * kBK, n0, &full_bar[s]);
+                if (!A_MN) {
+                    tma_load_2d(a_dst, &map_a, kb * kBK, m0, &full_bar[s]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < kBM / 64; ++j)
+                        tma_load_2d(a_dst + j * (kBK * 128), &map_a, m0 + 64 * j, kb * kBK, &full_bar[s]);
+                }
+                if (!B_MN) {
+                    tma_load_2d(a_dst + kABytes, &map_b, kb * kBK, n0, &full_bar[s]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < BN / 64; ++j)   // 64 K-rows x 64 N-columns per box
+                        tma_load_2d(a_dst + kABytes + j * (kBK * 128), &map_b, n0 + 64 * j, kb * kBK, &full_bar[s]);
+                }
             }
         }
         __syncwarp();
@@ -148,8 +177,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) ns_gemm_tn_kernel(const __gri
         // ---------------- MMA issuer
         if (lane == 0) {
             // instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, N = BN, M = 128
-            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
-                                       (static_cast<uint32_t>(kBM >> 4) << 24);
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (A_MN ? (1u << 15) : 0u) | (B_MN ? (1u << 16) : 0u) |
+                                       (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
             bool ok = true;
             for (int kb = 0; kb < k_blocks && ok; ++kb) {
                 const int s = kb % STAGES;
@@ -158,12 +187,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) ns_gemm_tn_kernel(const __gri
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
-                const uint64_t desc_a = umma_desc_k_major_sw128(a_addr);
-                const uint64_t desc_b = umma_desc_k_major_sw128(a_addr + kABytes);
+                const uint64_t desc_a = A_MN ? umma_desc_mn_major_sw128(a_addr, kBK * 128) : umma_desc_k_major_sw128(a_addr);
+                const uint64_t desc_b = B_MN ? umma_desc_mn_major_sw128(a_addr + kABytes, kBK * 128)
+                                             : umma_desc_k_major_sw128(a_addr + kABytes);
 #pragma unroll
                 for (int k = 0; k < kBK / 16; ++k) {
-                    // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the address field
-                    umma_bf16(tmem_base, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    // K-major: 16 bf16 along K = 32 bytes inside the swizzle row (+2 in the address field);
+                    // MN-major: 16 K-rows of 128 bytes = 2048 bytes (+128)
+                    umma_bf16(tmem_base, desc_a + (A_MN ? 128 : 2) * k, desc_b + (B_MN ? 128 : 2) * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(&empty_bar[s]);   // the slot is free once these MMAs have read it
             }
@@ -267,7 +298,7 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// [rows, K] bf16 row-major with leading dimension ld (elements); box = 64 (K) x box_rows, 128-byte swizzle.
+// [rows, cols] bf16 row-major with leading dimension ld (elements); box = 64 (inner) x box_rows, 128-byte swizzle.
 static int make_map(CUtensorMap* map, const void* base, long long rows, long long k, long long ld, int box_rows) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return fail(GEFEN_B200_ECUDA, "cuTensorMapEncodeTiled is not available from the driver.");
@@ -282,13 +313,13 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
     return GEFEN_B200_OK;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, cudaStream_t stream) {
     constexpr int smem = STAGES * (kBM * kBK * 2 + BN * kBK * 2) + 1024;
     static bool configured[64];
     int dev = 0;
     GEFEN_CHECK_CUDA(cudaGetDevice(&dev));
-    auto kernel = ns_gemm_tn_kernel<BN, STAGES>;
+    auto kernel = ns_gemm_tn_kernel<BN, STAGES, A_MN, B_MN>;
     if (dev < 64 && !configured[dev]) {
         GEFEN_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         configured[dev] = true;
@@ -303,21 +334,22 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmA
 
 using namespace gefen;
 
-extern "C" int gefen_b200_ns_gemm_tn(const void* a, const void* b, const void* c, void* d, void* dt, int M, int N, int K,
-                                     int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, int64_t lddt, double alpha,
-                                     double beta, int* status, void* stream_) {
+static int ns_gemm(const void* a, bool a_is_km, const void* b, bool b_is_kn, const void* c, void* d, void* dt, int M, int N, int K,
+                   int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, int64_t lddt, double alpha, double beta,
+                   int* status, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     GEFEN_CHECK_ARG(a != nullptr && b != nullptr && d != nullptr, "Expected non-null A, B and D.");
     GEFEN_CHECK_ARG(M > 0 && N > 0 && K > 0, "Expected positive GEMM sizes.");
     GEFEN_CHECK_ARG(beta == 0.0 || c != nullptr, "Expected C when beta != 0.");
-    GEFEN_CHECK_ARG(aligned16(a) && aligned16(b) && lda % 8 == 0 && ldb % 8 == 0 && lda >= K && ldb >= K,
+    GEFEN_CHECK_ARG(aligned16(a) && aligned16(b) && lda % 8 == 0 && ldb % 8 == 0 && lda >= (a_is_km ? M : K) &&
+                        ldb >= (b_is_kn ? N : K),
                     "Expected 16-byte aligned A and B with leading dimensions that are multiples of 8 elements.");
     GEFEN_CHECK_ARG(ldd >= N && (c == nullptr || ldc >= N) && (dt == nullptr || lddt >= M), "Bad leading dimension.");
     const int bn = (N >= 2048 || (static_cast<long long>((M + 127) / 128) * ((N + 255) / 256)) >= sm_count()) ? 256 : 128;
     CUtensorMap ma, mb;
-    int rc = make_map(&ma, a, M, K, lda, kBM);
+    int rc = a_is_km ? make_map(&ma, a, K, M, lda, kBK) : make_map(&ma, a, M, K, lda, kBM);
     if (rc != GEFEN_B200_OK) return rc;
-    rc = make_map(&mb, b, N, K, ldb, bn);
+    rc = b_is_kn ? make_map(&mb, b, K, N, ldb, kBK) : make_map(&mb, b, N, K, ldb, bn);
     if (rc != GEFEN_B200_OK) return rc;
     GemmArgs args;
     args.c = static_cast<const __nv_bfloat16*>(c);
@@ -328,6 +360,33 @@ extern "C" int gefen_b200_ns_gemm_tn(const void* a, const void* b, const void* c
     args.alpha = static_cast<float>(alpha);
     args.beta = static_cast<float>(beta);
     args.status = status;
-    if (bn == 256) return launch_gemm<256, 4>(ma, mb, args, stream);
-    return launch_gemm<128, 6>(ma, mb, args, stream);
+    if (a_is_km && b_is_kn) {
+        if (bn == 256) return launch_gemm<256, 4, true, true>(ma, mb, args, stream);
+        return launch_gemm<128, 6, true, true>(ma, mb, args, stream);
+    }
+    if (a_is_km) return fail(GEFEN_B200_EUNSUPPORTED, "A given as [K, M] is only combined with B given as [K, N].");
+    if (b_is_kn) {
+        if (bn == 256) return launch_gemm<256, 4, false, true>(ma, mb, args, stream);
+        return launch_gemm<128, 6, false, true>(ma, mb, args, stream);
+    }
+    if (bn == 256) return launch_gemm<256, 4, false, false>(ma, mb, args, stream);
+    return launch_gemm<128, 6, false, false>(ma, mb, args, stream);
+}
+
+extern "C" int gefen_b200_ns_gemm_tn(const void* a, const void* b, const void* c, void* d, void* dt, int M, int N, int K,
+                                     int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, int64_t lddt, double alpha,
+                                     double beta, int* status, void* stream) {
+    return ns_gemm(a, false, b, false, c, d, dt, M, N, K, lda, ldb, ldc, ldd, lddt, alpha, beta, status, stream);
+}
+
+extern "C" int gefen_b200_ns_gemm_nn(const void* a, const void* b, const void* c, void* d, int M, int N, int K,
+                                     int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, double alpha, double beta,
+                                     int* status, void* stream) {
+    return ns_gemm(a, false, b, true, c, d, nullptr, M, N, K, lda, ldb, ldc, ldd, 0, alpha, beta, status, stream);
+}
+
+extern "C" int gefen_b200_ns_gemm_tt(const void* a, const void* b, const void* c, void* d, int M, int N, int K,
+                                     int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, double alpha, double beta,
+                                     int* status, void* stream) {
+    return ns_gemm(a, true, b, true, c, d, nullptr, M, N, K, lda, ldb, ldc, ldd, 0, alpha, beta, status, stream);
 }

@@ -56,6 +56,37 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tensor] = None, 
     return out
 
 
+def gemm_nn(a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tensor] = None, alpha: float = 1.0, beta: float = 0.0,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M,N] = alpha * a[M,K] @ b[K,N] + beta * c[M,N]. bf16, row-major."""
+    M, K = a.shape
+    N = b.shape[1]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    for t in (a, b, c, out):
+        if t is not None and (t.dtype != torch.bfloat16 or t.stride(-1) != 1):
+            raise ValueError("gemm_nn expects bf16 matrices with unit inner stride")
+    with _lib.device_guard(a.device):
+        _lib.check(_lib.load().gefen_b200_ns_gemm_nn(
+            _lib.ptr(a), _lib.ptr(b), _lib.ptr(c), _lib.ptr(out), M, N, K, a.stride(0), b.stride(0),
+            0 if c is None else c.stride(0), out.stride(0), float(alpha), float(beta), _lib.ptr(_status(a.device)),
+            _lib.current_stream(a.device)))
+    return out
+
+
+def gemm_tt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M,N] = a[K,M]^T @ b[K,N]. bf16, row-major."""
+    K, M = a.shape
+    N = b.shape[1]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    with _lib.device_guard(a.device):
+        _lib.check(_lib.load().gefen_b200_ns_gemm_tt(
+            _lib.ptr(a), _lib.ptr(b), None, _lib.ptr(out), M, N, K, a.stride(0), b.stride(0), 0, out.stride(0), 1.0, 0.0,
+            _lib.ptr(_status(a.device)), _lib.current_stream(a.device)))
+    return out
+
+
 def _supported(m: int, n: int) -> bool:
     return USE_TCGEN05 and m % 8 == 0 and n % 8 == 0
 
@@ -72,34 +103,32 @@ def zeropower_via_newtonschulz(grad: torch.Tensor, ns_coefficients: Tuple[float,
         raise ValueError("gefen_b200 runs Newton-Schulz on the GPU only, got device {}".format(grad.device))
     a, b, c = ns_coefficients
     x = grad.bfloat16()
-    transposed = grad.size(0) > grad.size(1)
-    if transposed:
-        x = x.T
-    x = x / x.norm().clamp(min=eps)          # bf16 norm and quotient, as the reference's div_
-    m, n = x.shape
-    if not _supported(m, n) or ns_steps == 0:
+    rows, cols = x.shape
+    if not _supported(rows, cols) or ns_steps == 0:
+        transposed = rows > cols
+        if transposed:
+            x = x.T
+        x = x / x.norm().clamp(min=eps)
         for _ in range(ns_steps):
             gram = x @ x.T
             gram_update = torch.addmm(gram, gram, gram, beta=b, alpha=c)
             x = torch.addmm(x, gram_update, x, beta=a)
         return x.T if transposed else x
 
-    # wide X [m, n] and its transpose [n, m], both contiguous
-    if transposed:
-        xt = x.T.contiguous()       # the original orientation
-        xw = x.contiguous()
-    else:
-        xw = x.contiguous()
-        xt = x.T.contiguous()
-    dev = x.device
-    gram = torch.empty((m, m), dtype=torch.bfloat16, device=dev)
-    poly = torch.empty((m, m), dtype=torch.bfloat16, device=dev)
-    xw_next = torch.empty_like(xw)
-    xt_next = torch.empty_like(xt)
+    # bf16 norm and quotient, as the reference's div_ (the Frobenius norm does not care about orientation)
+    x = (x / x.norm().clamp(min=eps)).contiguous()
+    m = min(rows, cols)
+    gram = torch.empty((m, m), dtype=torch.bfloat16, device=x.device)
+    poly = torch.empty((m, m), dtype=torch.bfloat16, device=x.device)
+    nxt = torch.empty_like(x)
     for _ in range(ns_steps):
-        gemm_tn(xw, xw, out=gram)                                          # G = X X^T
-        gemm_tn(gram, gram, c=gram, alpha=c, beta=b, out=poly)              # B = b G + c G G   (G symmetric)
-        gemm_tn(poly, xt, c=xw, alpha=1.0, beta=a, out=xw_next, out_t=xt_next)   # X' = a X + B X, and X'^T
-        xw, xw_next = xw_next, xw
-        xt, xt_next = xt_next, xt
-    return xt if transposed else xw
+        if rows <= cols:
+            gemm_tn(x, x, out=gram)                                   # G = X X^T          (K-major operands)
+            gemm_tn(gram, gram, c=gram, alpha=c, beta=b, out=poly)     # B = b G + c G G    (G symmetric)
+            gemm_nn(poly, x, c=x, alpha=1.0, beta=a, out=nxt)          # X' = a X + B X     (X as MN-major operand)
+        else:
+            gemm_tt(x, x, out=gram)                                   # G = Y^T Y          (both MN-major)
+            gemm_tn(gram, gram, c=gram, alpha=c, beta=b, out=poly)
+            gemm_nn(x, poly, c=x, alpha=1.0, beta=a, out=nxt)          # Y' = a Y + Y B
+        x, nxt = nxt, x
+    return x

@@ -222,6 +222,16 @@ int gefen_b200_exact_dp(const double* prefix_w, const double* prefix_wx, const d
 int gefen_b200_ns_gemm_tn(const void* a, const void* b, const void* c, void* d, void* dt, int M,
                           int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd,
                           int64_t lddt, double alpha, double beta, int* status, void* stream);
+/* Same with B given as [K, N] row-major (an MN-major tensor-core operand):
+ *   D[M,N] = alpha * A[M,K] * B[K,N] + beta * C[M,N]. */
+int gefen_b200_ns_gemm_nn(const void* a, const void* b, const void* c, void* d, int M, int N,
+                          int K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, double alpha,
+                          double beta, int* status, void* stream);
+/* Both operands given K-first: A as [K, M] and B as [K, N], row-major:
+ *   D[M,N] = alpha * A^T * B + beta * C  (the Gram matrix Y^T Y of a tall Y without a transpose). */
+int gefen_b200_ns_gemm_tt(const void* a, const void* b, const void* c, void* d, int M, int N,
+                          int K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, double alpha,
+                          double beta, int* status, void* stream);
 
 #ifdef __cplusplus
 }

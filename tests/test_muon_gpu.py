@@ -104,3 +104,18 @@ def test_newton_schulz_matches_library_gemms(cuda_device):
         want = (x.T if shape[0] > shape[1] else x).float()
         assert mine.shape == want.shape
         assert float((mine - want).norm() / want.norm()) <= 2e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 512, 1024), (384, 640, 200), (2048, 6144, 2048), (96, 72, 136)])
+def test_tcgen05_gemm_with_row_major_b(cuda_device, M, N, K):
+    """B given as [K, N] row-major: an MN-major tensor-core operand, no transposed copy."""
+    from gefen_b200.newton_schulz import check_status, gemm_nn
+
+    gen = torch.Generator(device=cuda_device).manual_seed(M * 3 + N + K)
+    a = (torch.randn(M, K, generator=gen, device=cuda_device) / K ** 0.5).bfloat16()
+    b = torch.randn(K, N, generator=gen, device=cuda_device).bfloat16()
+    c = torch.randn(M, N, generator=gen, device=cuda_device).bfloat16()
+    want = 1.5 * (a.float() @ b.float()) + 0.5 * c.float()
+    out = gemm_nn(a, b, c=c, alpha=1.5, beta=0.5)
+    check_status(cuda_device)
+    assert float((out.float() - want).abs().max()) <= 1e-2 * float(want.abs().max())
