@@ -261,7 +261,10 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     achieved = vec_bytes / vec_ms / 1e6
     result["roofline"] = {"bound": "hbm", "kernel": "step_vec_kernel<bf16>" if elem_bytes == 2 else "step_vec_kernel<f32>",
                           "achieved": achieved, "peak": peak, "peak_kind": peak_kind + " copy bandwidth, burst",
-                          "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                          "unit": "GB/s", "frac": achieved / peak,
+                          # dram read+write of one launch: 0.953 x algorithmic, scaled from the ncu capture of a
+                          # 134 M-element launch of the same kernel (profiles/step_vec_kernel_bf16_period2048.md)
+                          "traffic": 0.953 * vec_bytes if elem_bytes == 2 else None,
                           "algorithmic_bytes_per_launch": vec_bytes, "launch_ms": vec_ms}
     result["launches_per_step"] = len(set(cls))
 
@@ -353,6 +356,8 @@ def run_microbench(spec: str, steps: int, warmup: int):
     Small enough for profiler captures; prints one JSON line."""
     from gefen_b200.kernels.automatic_gefen_fused import automatic_gefen_fused_update_from_vmean_cuda
 
+    if spec.split(":")[0] in ("gemm", "hist", "scan"):
+        return run_microbench_other(spec, steps, warmup)
     name, period, blocks = spec.split(":")
     period, blocks = int(period), int(blocks)
     dtype = {"bf16": torch.bfloat16, "f32": torch.float32, "f16": torch.float16}[name]
@@ -377,6 +382,59 @@ def run_microbench(spec: str, steps: int, warmup: int):
     peak, kind = measured_peaks()
     print(json.dumps({"microbench": spec, "ms_per_launch": ms, "algorithmic_bytes": bytes_per_launch,
                       "achieved_gbs": bytes_per_launch / ms / 1e6, "frac_of_{}_peak".format(kind): bytes_per_launch / ms / 1e6 / peak}))
+
+
+def run_microbench_other(spec: str, steps: int, warmup: int):
+    """gemm:M:N:K (tcgen05 GEMM, K-major operands), hist:dtype:rows:cols (exact histogram, period = cols),
+    scan:dtype:rows:cols (all candidate periods of one tensor)."""
+    parts = spec.split(":")
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    out = {"microbench": spec}
+    if parts[0] == "gemm":
+        from gefen_b200.newton_schulz import check_status, gemm_tn
+
+        M, N, K = (int(x) for x in parts[1:])
+        a = torch.randn(M, K, generator=gen, device=dev).bfloat16()
+        b = torch.randn(N, K, generator=gen, device=dev).bfloat16()
+        d = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        for _ in range(max(warmup, 3)):
+            gemm_tn(a, b, out=d)
+        ms = timed(lambda: gemm_tn(a, b, out=d), steps)
+        check_status(dev)
+        for _ in range(3):
+            torch.mm(a, b.T)
+        ref = timed(lambda: torch.mm(a, b.T), steps)
+        out.update({"ms": ms, "tflops": 2.0 * M * N * K / ms / 1e9, "torch_matmul_ms": ref,
+                    "torch_matmul_tflops": 2.0 * M * N * K / ref / 1e9})
+    else:
+        dtype = {"bf16": torch.bfloat16, "f32": torch.float32}[parts[1]]
+        rows, cols = int(parts[2]), int(parts[3])
+        g = workloads.make_grad((rows, cols), 0, 0, dtype, dev)
+        flat = g.reshape(-1)
+        if parts[0] == "hist":
+            from gefen_b200.kernels.exact_histogram_fused import gefen_exact_histogram_cuda
+
+            counts = torch.zeros(4096, dtype=torch.int64, device=dev)
+            period = cols if cols <= 1024 else 2048
+            for _ in range(max(warmup, 3)):
+                gefen_exact_histogram_cuda(flat, period, counts)
+            ms = timed(lambda: gefen_exact_histogram_cuda(flat, period, counts), steps)
+            out.update({"ms": ms, "period": period, "achieved_gbs": flat.numel() * flat.element_size() / ms / 1e6})
+        else:
+            from gefen_b200 import partitioning
+
+            def scan():
+                return partitioning.find_period_by_block_variance(flat, print_results=False, backend="cuda_kernel",
+                                                                  input_is_squared=False)
+
+            for _ in range(max(warmup, 2)):
+                period = scan()
+            ms = timed(scan, steps)
+            cands = partitioning.decision_periods(partitioning.candidate_periods(flat.numel()))
+            out.update({"ms": ms, "period": period, "candidates": len(cands),
+                        "achieved_gbs_one_read": flat.numel() * flat.element_size() / ms / 1e6})
+    print(json.dumps(out))
 
 
 def main():
