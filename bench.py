@@ -356,7 +356,7 @@ def run_microbench(spec: str, steps: int, warmup: int):
     Small enough for profiler captures; prints one JSON line."""
     from gefen_b200.kernels.automatic_gefen_fused import automatic_gefen_fused_update_from_vmean_cuda
 
-    if spec.split(":")[0] in ("gemm", "hist", "scan"):
+    if spec.split(":")[0] in ("gemm", "hist", "scan", "ns"):
         return run_microbench_other(spec, steps, warmup)
     name, period, blocks = spec.split(":")
     period, blocks = int(period), int(blocks)
@@ -391,6 +391,25 @@ def run_microbench_other(spec: str, steps: int, warmup: int):
     dev = torch.device("cuda", 0)
     gen = torch.Generator(device=dev).manual_seed(0)
     out = {"microbench": spec}
+    if parts[0] == "ns":
+        from gefen_b200 import newton_schulz as ns
+
+        rows, cols = int(parts[1]), int(parts[2])
+        g = (torch.randn(rows, cols, generator=gen, device=dev) * 1e-3).bfloat16()
+        coeffs = (3.4445, -4.7750, 2.0315)
+        res = {}
+        for mode in ("tcgen05", "torch"):
+            ns.USE_TCGEN05 = mode == "tcgen05"
+            for _ in range(max(warmup, 3)):
+                ns.zeropower_via_newtonschulz(g, coeffs, 5, 1e-7)
+            res[mode] = timed(lambda: ns.zeropower_via_newtonschulz(g, coeffs, 5, 1e-7), steps)
+        ns.USE_TCGEN05 = True
+        ns.check_status(dev)
+        flops = ns_flops((rows, cols))
+        out.update({"ms": res["tcgen05"], "tflops": flops / res["tcgen05"] / 1e9, "torch_ms": res["torch"],
+                    "torch_tflops": flops / res["torch"] / 1e9})
+        print(json.dumps(out))
+        return
     if parts[0] == "gemm":
         from gefen_b200.newton_schulz import check_status, gemm_tn
 

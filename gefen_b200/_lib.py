@@ -84,9 +84,10 @@ def _declare(lib):
         "gefen_b200_lloyd_mse": (i32, [vp, i32, i64, i64, vp, vp, i32, vp, vp, vp, vp]),
         "gefen_b200_exact_dp_scratch_bytes": (i64, [i32, i32]),
         "gefen_b200_exact_dp": (i32, [vp, vp, vp, i32, i32, i32, vp, vp, vp]),
-        "gefen_b200_ns_gemm_tn": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i64, dbl, dbl, vp, vp]),
+        "gefen_b200_ns_gemm_tn": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i64, dbl, dbl, i32, vp, vp]),
+        "gefen_b200_newton_schulz": (i32, [vp, vp, vp, vp, i32, i32, i32, dbl, dbl, dbl, vp, vp]),
         "gefen_b200_ns_gemm_nn": (i32, [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, dbl, dbl, vp, vp]),
-        "gefen_b200_ns_gemm_tt": (i32, [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, dbl, dbl, vp, vp]),
+        "gefen_b200_ns_gemm_tt": (i32, [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, dbl, dbl, i32, vp, vp]),
     }
     for name, (restype, argtypes) in sig.items():
         fn = getattr(lib, name)

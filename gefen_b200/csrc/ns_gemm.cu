@@ -37,6 +37,8 @@ struct GemmArgs {
     int M, N, K;
     long long ldc, ldd, lddt;
     float alpha, beta;
+    int symmetric;   // the result is known to be symmetric (M == N): compute the tiles that touch the upper
+                     // triangle only and write every element above the diagonal to its mirror position too
     int* status;
 };
 
@@ -129,6 +131,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) ns_gemm_tn_kernel(const __gri
     const int m0 = blockIdx.y * kBM;
     const int n0 = blockIdx.x * BN;
     const int k_blocks = (args.K + kBK - 1) / kBK;
+    if (args.symmetric && n0 + BN <= m0) return;   // tile entirely below the diagonal: its mirror image computes it
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -203,10 +206,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1) ns_gemm_tn_kernel(const __gri
         __syncwarp();
     } else {
         // ---------------- epilogue: warp w owns TMEM lanes (rows) 32w .. 32w+31
-        const bool ok = wait_or_abort(&acc_bar, 0, &abort_flag);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int row = m0 + warp * 32 + lane;
         const bool row_ok = row < args.M;
+        // C does not depend on the accumulators: the first chunk's row segment is fetched while the main
+        // loop runs, and chunk j+1's while chunk j is converted and stored.
+        const bool use_c = row_ok && args.beta != 0.0f;
+        const __nv_bfloat16* crow_base = use_c ? args.c + static_cast<long long>(row) * args.ldc : nullptr;
+        const bool c_vec = use_c && ((reinterpret_cast<uintptr_t>(crow_base) & 15u) == 0) && (args.ldc % 8 == 0) && (n0 % 8 == 0);
+        uint4 cnext[4];
+        auto fetch_c = [&](int j) {
+            const int col0 = n0 + j * 32;
+            if (c_vec && col0 + 32 <= args.N) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) cnext[q] = reinterpret_cast<const uint4*>(crow_base + col0)[q];
+            }
+        };
+        fetch_c(0);
+        const bool ok = wait_or_abort(&acc_bar, 0, &abort_flag);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok && !abort_flag) {
 #pragma unroll 1
             for (int j = 0; j < BN / 32; ++j) {
@@ -222,32 +239,44 @@ __global__ void __launch_bounds__(kGemmThreads, 1) ns_gemm_tn_kernel(const __gri
                       "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                     : "r"(taddr)
                     : "memory");
+                uint4 ccur[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) ccur[q] = cnext[q];
+                if (j + 1 < BN / 32) fetch_c(j + 1);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 const int col0 = n0 + j * 32;
-                if (row_ok && col0 < args.N) {
-                    float v[32];
+                if (col0 >= args.N) continue;
+                const bool full_cols = col0 + 32 <= args.N;
+                float v[32];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = args.alpha * __uint_as_float(r[i]);
-                    const bool full_cols = col0 + 32 <= args.N;
-                    if (args.beta != 0.0f) {
-                        const __nv_bfloat16* crow = args.c + static_cast<long long>(row) * args.ldc + col0;
-                        if (full_cols && ((reinterpret_cast<uintptr_t>(crow) & 15u) == 0)) {
+                for (int i = 0; i < 32; ++i) v[i] = args.alpha * __uint_as_float(r[i]);
+                if (use_c) {
+                    const __nv_bfloat16* crow = crow_base + col0;
+                    if (full_cols && c_vec) {
 #pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                const uint4 raw = reinterpret_cast<const uint4*>(crow)[q];
-                                const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+                        for (int q = 0; q < 4; ++q) {
+                            const uint4 raw = ccur[q];
+                            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    v[q * 8 + 2 * e] = fmaf(args.beta, __uint_as_float(w[e] << 16), v[q * 8 + 2 * e]);
-                                    v[q * 8 + 2 * e + 1] = fmaf(args.beta, __uint_as_float(w[e] & 0xFFFF0000u), v[q * 8 + 2 * e + 1]);
-                                }
+                            for (int e = 0; e < 4; ++e) {
+                                v[q * 8 + 2 * e] = fmaf(args.beta, __uint_as_float(w[e] << 16), v[q * 8 + 2 * e]);
+                                v[q * 8 + 2 * e + 1] = fmaf(args.beta, __uint_as_float(w[e] & 0xFFFF0000u), v[q * 8 + 2 * e + 1]);
                             }
-                        } else {
-                            for (int i = 0; i < 32 && col0 + i < args.N; ++i) v[i] = fmaf(args.beta, __bfloat162float(crow[i]), v[i]);
                         }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col0 + i < args.N) v[i] = fmaf(args.beta, __bfloat162float(crow[i]), v[i]);
                     }
+                }
+                if (row_ok) {
                     __nv_bfloat16* drow = args.d + static_cast<long long>(row) * args.ldd + col0;
-                    if (full_cols && ((reinterpret_cast<uintptr_t>(drow) & 15u) == 0)) {
+                    if (args.symmetric && col0 < row) {
+                        // chunk crosses or lies left of the diagonal: only the elements with column >= row
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col0 + i < args.N && col0 + i >= row) drow[i] = __float2bfloat16_rn(v[i]);
+                    } else if (full_cols && ((reinterpret_cast<uintptr_t>(drow) & 15u) == 0)) {
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             uint32_t w[4];
@@ -259,12 +288,40 @@ __global__ void __launch_bounds__(kGemmThreads, 1) ns_gemm_tn_kernel(const __gri
                             reinterpret_cast<uint4*>(drow)[q] = make_uint4(w[0], w[1], w[2], w[3]);
                         }
                     } else {
-                        for (int i = 0; i < 32 && col0 + i < args.N; ++i) drow[i] = __float2bfloat16_rn(v[i]);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col0 + i < args.N) drow[i] = __float2bfloat16_rn(v[i]);
                     }
                     if (args.dt != nullptr) {
                         // transposed copy: for a fixed column the lanes of a warp write consecutive addresses
-                        for (int i = 0; i < 32 && col0 + i < args.N; ++i)
-                            args.dt[static_cast<long long>(col0 + i) * args.lddt + row] = __float2bfloat16_rn(v[i]);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col0 + i < args.N)
+                                args.dt[static_cast<long long>(col0 + i) * args.lddt + row] = __float2bfloat16_rn(v[i]);
+                    }
+                }
+                if (args.symmetric) {
+                    // mirror: element (row, c) with c > row also goes to (c, row)
+                    const int warp_row0 = m0 + warp * 32;
+                    if (col0 > warp_row0 + 31 && warp_row0 + 31 < args.M && full_cols) {
+                        // the whole chunk is right of every row of this warp (warp-uniform): lanes pair up so
+                        // that each store carries two consecutive rows of one column (4 bytes)
+                        const bool odd = (lane & 1) != 0;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            const float send = odd ? v[i] : v[i + 1];
+                            const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+                            const float lo = odd ? recv : v[i];          // value of the even row
+                            const float hi = odd ? v[i + 1] : recv;      // value of the odd row
+                            const int c = col0 + i + (odd ? 1 : 0);
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                            *reinterpret_cast<__nv_bfloat162*>(args.d + static_cast<long long>(c) * args.ldd + (row & ~1)) = h;
+                        }
+                    } else if (row_ok && col0 + 31 > row) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col0 + i < args.N && col0 + i > row)
+                                args.d[static_cast<long long>(col0 + i) * args.ldd + row] = __float2bfloat16_rn(v[i]);
                     }
                 }
             }
@@ -336,15 +393,20 @@ using namespace gefen;
 
 static int ns_gemm(const void* a, bool a_is_km, const void* b, bool b_is_kn, const void* c, void* d, void* dt, int M, int N, int K,
                    int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, int64_t lddt, double alpha, double beta,
-                   int* status, void* stream_) {
+                   int symmetric, int* status, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     GEFEN_CHECK_ARG(a != nullptr && b != nullptr && d != nullptr, "Expected non-null A, B and D.");
     GEFEN_CHECK_ARG(M > 0 && N > 0 && K > 0, "Expected positive GEMM sizes.");
     GEFEN_CHECK_ARG(beta == 0.0 || c != nullptr, "Expected C when beta != 0.");
+    GEFEN_CHECK_ARG(!symmetric || (M == N && ldd % 2 == 0 && (reinterpret_cast<uintptr_t>(d) & 3u) == 0 && dt == nullptr),
+                    "A symmetric result needs M == N, an even leading dimension and no transposed output.");
     GEFEN_CHECK_ARG(aligned16(a) && aligned16(b) && lda % 8 == 0 && ldb % 8 == 0 && lda >= (a_is_km ? M : K) &&
                         ldb >= (b_is_kn ? N : K),
                     "Expected 16-byte aligned A and B with leading dimensions that are multiples of 8 elements.");
     GEFEN_CHECK_ARG(ldd >= N && (c == nullptr || ldc >= N) && (dt == nullptr || lddt >= M), "Bad leading dimension.");
+    // 128 x 256 tiles have the better arithmetic intensity; 128 x 128 tiles are used for small problems
+    // that would leave most SMs without a tile (measured: for 2048-wide outputs the wider tile wins
+    // even when a symmetric result computes only 72 of them)
     const int bn = (N >= 2048 || (static_cast<long long>((M + 127) / 128) * ((N + 255) / 256)) >= sm_count()) ? 256 : 128;
     CUtensorMap ma, mb;
     int rc = a_is_km ? make_map(&ma, a, K, M, lda, kBK) : make_map(&ma, a, M, K, lda, kBM);
@@ -359,6 +421,7 @@ static int ns_gemm(const void* a, bool a_is_km, const void* b, bool b_is_kn, con
     args.ldc = ldc; args.ldd = ldd; args.lddt = lddt;
     args.alpha = static_cast<float>(alpha);
     args.beta = static_cast<float>(beta);
+    args.symmetric = symmetric;
     args.status = status;
     if (a_is_km && b_is_kn) {
         if (bn == 256) return launch_gemm<256, 4, true, true>(ma, mb, args, stream);
@@ -373,20 +436,54 @@ static int ns_gemm(const void* a, bool a_is_km, const void* b, bool b_is_kn, con
     return launch_gemm<128, 6, false, false>(ma, mb, args, stream);
 }
 
+// The whole Newton-Schulz iteration of one matrix, enqueued from native code (fifteen GEMM launches
+// for five steps) so that the host cost per product is a tensor-map encode and a launch.
+extern "C" int gefen_b200_newton_schulz(void* x0, void* x1, void* gram, void* poly, int rows, int cols, int steps,
+                                        double a, double b, double c, int* status, void* stream) {
+    GEFEN_CHECK_ARG(x0 && x1 && gram && poly, "Expected non-null buffers.");
+    GEFEN_CHECK_ARG(rows > 0 && cols > 0 && rows % 8 == 0 && cols % 8 == 0, "Expected dimensions that are multiples of 8.");
+    GEFEN_CHECK_ARG(steps >= 0 && steps < 100, "Number of steps must be less than 100.");
+    const int m = rows < cols ? rows : cols;
+    void* cur = x0;
+    void* nxt = x1;
+    for (int it = 0; it < steps; ++it) {
+        int rc;
+        if (rows <= cols) {
+            // G = X X^T ; B = b G + c G G ; X' = a X + B X
+            rc = ns_gemm(cur, false, cur, false, nullptr, gram, nullptr, m, m, cols, cols, cols, 0, m, 0, 1.0, 0.0, 1, status, stream);
+            if (rc != GEFEN_B200_OK) return rc;
+            rc = ns_gemm(gram, false, gram, false, gram, poly, nullptr, m, m, m, m, m, m, m, 0, c, b, 1, status, stream);
+            if (rc != GEFEN_B200_OK) return rc;
+            rc = ns_gemm(poly, false, cur, true, cur, nxt, nullptr, rows, cols, m, m, cols, cols, cols, 0, 1.0, a, 0, status, stream);
+            if (rc != GEFEN_B200_OK) return rc;
+        } else {
+            // G = Y^T Y ; B = b G + c G G ; Y' = a Y + Y B
+            rc = ns_gemm(cur, true, cur, true, nullptr, gram, nullptr, m, m, rows, cols, cols, 0, m, 0, 1.0, 0.0, 1, status, stream);
+            if (rc != GEFEN_B200_OK) return rc;
+            rc = ns_gemm(gram, false, gram, false, gram, poly, nullptr, m, m, m, m, m, m, m, 0, c, b, 1, status, stream);
+            if (rc != GEFEN_B200_OK) return rc;
+            rc = ns_gemm(cur, false, poly, true, cur, nxt, nullptr, rows, cols, m, cols, m, cols, cols, 0, 1.0, a, 0, status, stream);
+            if (rc != GEFEN_B200_OK) return rc;
+        }
+        void* t = cur; cur = nxt; nxt = t;
+    }
+    return GEFEN_B200_OK;
+}
+
 extern "C" int gefen_b200_ns_gemm_tn(const void* a, const void* b, const void* c, void* d, void* dt, int M, int N, int K,
                                      int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, int64_t lddt, double alpha,
-                                     double beta, int* status, void* stream) {
-    return ns_gemm(a, false, b, false, c, d, dt, M, N, K, lda, ldb, ldc, ldd, lddt, alpha, beta, status, stream);
+                                     double beta, int symmetric, int* status, void* stream) {
+    return ns_gemm(a, false, b, false, c, d, dt, M, N, K, lda, ldb, ldc, ldd, lddt, alpha, beta, symmetric, status, stream);
 }
 
 extern "C" int gefen_b200_ns_gemm_nn(const void* a, const void* b, const void* c, void* d, int M, int N, int K,
                                      int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, double alpha, double beta,
                                      int* status, void* stream) {
-    return ns_gemm(a, false, b, true, c, d, nullptr, M, N, K, lda, ldb, ldc, ldd, 0, alpha, beta, status, stream);
+    return ns_gemm(a, false, b, true, c, d, nullptr, M, N, K, lda, ldb, ldc, ldd, 0, alpha, beta, 0, status, stream);
 }
 
 extern "C" int gefen_b200_ns_gemm_tt(const void* a, const void* b, const void* c, void* d, int M, int N, int K,
                                      int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, double alpha, double beta,
-                                     int* status, void* stream) {
-    return ns_gemm(a, true, b, true, c, d, nullptr, M, N, K, lda, ldb, ldc, ldd, 0, alpha, beta, status, stream);
+                                     int symmetric, int* status, void* stream) {
+    return ns_gemm(a, true, b, true, c, d, nullptr, M, N, K, lda, ldb, ldc, ldd, 0, alpha, beta, symmetric, status, stream);
 }

@@ -22,6 +22,19 @@ _STATUS = {}
 USE_TCGEN05 = os.environ.get("GEFEN_B200_NS", "tcgen05") != "torch"
 
 
+_SCRATCH = {}
+
+
+def _scratch(device, numel: int) -> torch.Tensor:
+    """Per-device bf16 scratch for the iteration (Gram matrix, polynomial, second iterate), grown on demand.
+    Work on one stream is ordered, so successive matrices can share it."""
+    t = _SCRATCH.get(device.index)
+    if t is None or t.numel() < numel:
+        t = torch.empty(numel, dtype=torch.bfloat16, device=device)
+        _SCRATCH[device.index] = t
+    return t[:numel]
+
+
 def _status(device) -> torch.Tensor:
     t = _STATUS.get(device.index)
     if t is None:
@@ -39,8 +52,9 @@ def check_status(device) -> None:
 
 
 def gemm_tn(a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tensor] = None, alpha: float = 1.0, beta: float = 0.0,
-            out: Optional[torch.Tensor] = None, out_t: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[M,N] = alpha * a[M,K] @ b[N,K]^T + beta * c[M,N]; out_t[N,M] = out^T if given. bf16, row-major."""
+            out: Optional[torch.Tensor] = None, out_t: Optional[torch.Tensor] = None, symmetric: bool = False) -> torch.Tensor:
+    """out[M,N] = alpha * a[M,K] @ b[N,K]^T + beta * c[M,N]; out_t[N,M] = out^T if given. bf16, row-major.
+    symmetric=True promises a symmetric result (a is b, c symmetric): half of the tiles are computed."""
     M, K = a.shape
     N = b.shape[0]
     if out is None:
@@ -52,7 +66,7 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tensor] = None, 
         _lib.check(_lib.load().gefen_b200_ns_gemm_tn(
             _lib.ptr(a), _lib.ptr(b), _lib.ptr(c), _lib.ptr(out), _lib.ptr(out_t), M, N, K, a.stride(0), b.stride(0),
             0 if c is None else c.stride(0), out.stride(0), 0 if out_t is None else out_t.stride(0), float(alpha),
-            float(beta), _lib.ptr(_status(a.device)), _lib.current_stream(a.device)))
+            float(beta), int(symmetric), _lib.ptr(_status(a.device)), _lib.current_stream(a.device)))
     return out
 
 
@@ -74,7 +88,7 @@ def gemm_nn(a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tensor] = None, 
     return out
 
 
-def gemm_tt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def gemm_tt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, symmetric: bool = False) -> torch.Tensor:
     """out[M,N] = a[K,M]^T @ b[K,N]. bf16, row-major."""
     K, M = a.shape
     N = b.shape[1]
@@ -83,7 +97,7 @@ def gemm_tt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
     with _lib.device_guard(a.device):
         _lib.check(_lib.load().gefen_b200_ns_gemm_tt(
             _lib.ptr(a), _lib.ptr(b), None, _lib.ptr(out), M, N, K, a.stride(0), b.stride(0), 0, out.stride(0), 1.0, 0.0,
-            _lib.ptr(_status(a.device)), _lib.current_stream(a.device)))
+            int(symmetric), _lib.ptr(_status(a.device)), _lib.current_stream(a.device)))
     return out
 
 
@@ -118,17 +132,12 @@ def zeropower_via_newtonschulz(grad: torch.Tensor, ns_coefficients: Tuple[float,
     # bf16 norm and quotient, as the reference's div_ (the Frobenius norm does not care about orientation)
     x = (x / x.norm().clamp(min=eps)).contiguous()
     m = min(rows, cols)
-    gram = torch.empty((m, m), dtype=torch.bfloat16, device=x.device)
-    poly = torch.empty((m, m), dtype=torch.bfloat16, device=x.device)
-    nxt = torch.empty_like(x)
-    for _ in range(ns_steps):
-        if rows <= cols:
-            gemm_tn(x, x, out=gram)                                   # G = X X^T          (K-major operands)
-            gemm_tn(gram, gram, c=gram, alpha=c, beta=b, out=poly)     # B = b G + c G G    (G symmetric)
-            gemm_nn(poly, x, c=x, alpha=1.0, beta=a, out=nxt)          # X' = a X + B X     (X as MN-major operand)
-        else:
-            gemm_tt(x, x, out=gram)                                   # G = Y^T Y          (both MN-major)
-            gemm_tn(gram, gram, c=gram, alpha=c, beta=b, out=poly)
-            gemm_nn(x, poly, c=x, alpha=1.0, beta=a, out=nxt)          # Y' = a Y + Y B
-        x, nxt = nxt, x
-    return x
+    scratch = _scratch(x.device, 2 * m * m + rows * cols)
+    gram = scratch[: m * m]
+    poly = scratch[m * m: 2 * m * m]
+    nxt = scratch[2 * m * m:].view(rows, cols)
+    with _lib.device_guard(x.device):
+        _lib.check(_lib.load().gefen_b200_newton_schulz(
+            _lib.ptr(x), _lib.ptr(nxt), _lib.ptr(gram), _lib.ptr(poly), rows, cols, int(ns_steps), float(a), float(b),
+            float(c), _lib.ptr(_status(x.device)), _lib.current_stream(x.device)))
+    return x if ns_steps % 2 == 0 else nxt.clone()

@@ -218,10 +218,13 @@ int gefen_b200_exact_dp(const double* prefix_w, const double* prefix_wx, const d
  *   D[M,N] = alpha * A[M,K] * B[N,K]^T + beta * C[M,N], and Dt[N,M] = D^T when dt != NULL.
  * All matrices bf16 row-major with leading dimensions in elements; A and B 16-byte aligned with
  * lda, ldb multiples of 8. fp32 accumulation, one rounding to bf16. `status` (device int, may be
- * NULL) is set to 1 if a bounded wait inside the kernel ran out. */
+ * NULL) is set to 1 if a bounded wait inside the kernel ran out. `symmetric` != 0 promises that
+ * the result is symmetric (M == N, e.g. A == B, C symmetric): only the tiles touching the upper
+ * triangle are computed and every element is also written to its mirror position. */
 int gefen_b200_ns_gemm_tn(const void* a, const void* b, const void* c, void* d, void* dt, int M,
                           int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd,
-                          int64_t lddt, double alpha, double beta, int* status, void* stream);
+                          int64_t lddt, double alpha, double beta, int symmetric, int* status,
+                          void* stream);
 /* Same with B given as [K, N] row-major (an MN-major tensor-core operand):
  *   D[M,N] = alpha * A[M,K] * B[K,N] + beta * C[M,N]. */
 int gefen_b200_ns_gemm_nn(const void* a, const void* b, const void* c, void* d, int M, int N,
@@ -231,7 +234,16 @@ int gefen_b200_ns_gemm_nn(const void* a, const void* b, const void* c, void* d, 
  *   D[M,N] = alpha * A^T * B + beta * C  (the Gram matrix Y^T Y of a tall Y without a transpose). */
 int gefen_b200_ns_gemm_tt(const void* a, const void* b, const void* c, void* d, int M, int N,
                           int K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, double alpha,
-                          double beta, int* status, void* stream);
+                          double beta, int symmetric, int* status, void* stream);
+
+/* `steps` Newton-Schulz iterations (reference: gefen_muon.py:38-47) of one already normalised bf16
+ * matrix [rows, cols] (row-major, contiguous, dimensions multiples of 8), enqueued as 3 * steps
+ * GEMMs: G = X X^T, B = b G + c G G, X <- a X + B X on the wide orientation, or the mirrored form
+ * (Y^T Y, Y B) for rows > cols, so no transpose is ever materialised. x0 holds the input; the
+ * iterates alternate between x0 and x1 and the result is in x0 when steps is even, else in x1.
+ * gram and poly are [min(rows,cols)]^2 bf16 scratch. */
+int gefen_b200_newton_schulz(void* x0, void* x1, void* gram, void* poly, int rows, int cols,
+                             int steps, double a, double b, double c, int* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -119,3 +119,23 @@ def test_tcgen05_gemm_with_row_major_b(cuda_device, M, N, K):
     out = gemm_nn(a, b, c=c, alpha=1.5, beta=0.5)
     check_status(cuda_device)
     assert float((out.float() - want).abs().max()) <= 1e-2 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("m,k", [(128, 256), (384, 200), (2048, 1024), (1000, 512)])
+def test_tcgen05_gemm_symmetric_output(cuda_device, m, k):
+    """Gram matrix with only the upper-triangle tiles computed and mirrored: bit-identical to the full product."""
+    from gefen_b200.newton_schulz import check_status, gemm_tn
+
+    gen = torch.Generator(device=cuda_device).manual_seed(m + k)
+    x = (torch.randn(m, k, generator=gen, device=cuda_device) / k ** 0.5).bfloat16()
+    full = gemm_tn(x, x)
+    sym = torch.full((m, m), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    gemm_tn(x, x, out=sym, symmetric=True)
+    check_status(cuda_device)
+    assert torch.equal(sym, full)
+    assert torch.equal(sym, sym.T.contiguous())
+    poly_full = gemm_tn(full, full, c=full, alpha=2.0315, beta=-4.775)
+    poly_sym = torch.full((m, m), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    gemm_tn(full, full, c=full, alpha=2.0315, beta=-4.775, out=poly_sym, symmetric=True)
+    check_status(cuda_device)
+    assert torch.equal(poly_sym, poly_full)
