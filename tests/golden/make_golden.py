@@ -85,7 +85,24 @@ def main(reference_root: str) -> None:
         "vmean": [opt.state[p]["vmean"].clone() for p in params],
         "codebook": opt._gefen_codebook.clone(),
     }
-    # 5. histogram accumulation of step 0 (float32 total over tensors in parameter order)
+    # 5. checkpoint interchange: the reference's state_dict after three steps, and where the reference
+    #    itself gets to after two more steps from that checkpoint
+    import copy
+
+    params = [torch.nn.Parameter(make_param(s, 0, i) if len(s) == 2 else torch.ones(s)) for i, s in enumerate(SHAPES)]
+    opt = Gefen([("p{}".format(i), p) for i, p in enumerate(params)], lr=1e-3, weight_decay=0.01, fused=False)
+    for step in range(3):
+        for i, (p, s) in enumerate(zip(params, SHAPES)):
+            p.grad = make_grad(s, 0, i, step)
+        opt.step()
+    checkpoint = {"state_dict": copy.deepcopy(opt.state_dict()), "params": [p.detach().clone() for p in params]}
+    for step in range(3, 5):
+        for i, (p, s) in enumerate(zip(params, SHAPES)):
+            p.grad = make_grad(s, 0, i, step)
+        opt.step()
+    checkpoint["params_after_two_more"] = [p.detach().clone() for p in params]
+    checkpoint["codes_after_two_more"] = [opt.state[p]["m_codebook"].clone() for p in params]
+    out["checkpoint"] = checkpoint
     torch.save(out, HERE / "reference_golden.pt")
     print("wrote", HERE / "reference_golden.pt")
 

@@ -111,3 +111,38 @@ def test_missing_library_is_loud(monkeypatch, cuda_device, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "nope.so")
     with pytest.raises(_lib.GefenB200Error):
         _lib.load()
+
+
+def test_loads_a_checkpoint_written_by_the_reference(cuda_device):
+    """A state_dict produced by the reference optimizer (CPU, three steps; tests/golden) is loaded as
+    is; two more steps here must land where the reference itself lands (its CPU arithmetic differs
+    from its kernels' by rounding only)."""
+    from pathlib import Path
+
+    from gefen_b200 import Gefen
+
+    golden = torch.load(Path(__file__).resolve().parent / "golden" / "reference_golden.pt", weights_only=False)
+    ck = golden["checkpoint"]
+    shapes = golden["ten_steps_fp32"]["shapes"]
+    params = [torch.nn.Parameter(p.clone().to(cuda_device)) for p in ck["params"]]
+    opt = Gefen([("p{}".format(i), p) for i, p in enumerate(params)], lr=1e-3, weight_decay=0.01)
+    opt.load_state_dict(ck["state_dict"])
+    assert opt._gefen_global_step == 3
+    st = opt.state[params[0]]
+    assert st["m_codebook"].dtype == torch.uint8 and st["m_codebook"].device.type == "cuda"
+    assert st["step"] == 3 and isinstance(st["automatic_period"], int)
+    for step in range(3, 5):
+        for i, (p, s) in enumerate(zip(params, shapes)):
+            p.grad = make_grad(s, 0, i, step).to(cuda_device)
+        opt.step()
+    total = agree = 0
+    for p, want, codes in zip(params, ck["params_after_two_more"], ck["codes_after_two_more"]):
+        assert rel_l2(p.detach().cpu(), want) <= 2e-5
+        diff = (opt.state[p]["m_codebook"].cpu().int() - codes.int()).abs()
+        assert int(diff.max()) <= 1
+        total += diff.numel()
+        agree += int((diff == 0).sum())
+    assert agree / total >= 0.999
+    # and back: the reference's loader only needs the same keys
+    sd = opt.state_dict()
+    assert set(sd["state"][0]) == set(ck["state_dict"]["state"][0])
