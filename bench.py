@@ -231,8 +231,12 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     elem_bytes = params[0].element_size()
     total_elems = sum(workloads.numel(s) for _, s in shapes)
     algo_bytes = workloads.step_bytes(shapes, per_tensor, elem_bytes, elem_bytes)
+    by_period = {}
+    for (_, shape), period in zip(shapes, per_tensor):
+        by_period[period] = by_period.get(period, 0) + workloads.numel(shape)
     result = {"ms": ms, "calibration_ms": calibration_ms, "clocks": clocks, "algo_bytes": algo_bytes,
-              "total_elems": total_elems, "n_tensors": len(shapes), "periods": sorted(set(periods))}
+              "total_elems": total_elems, "n_tensors": len(shapes), "periods": sorted(set(periods)),
+              "period_elements": {str(k): by_period[k] for k in sorted(by_period)}}
     if world > 1:
         result["breakdown"] = opt.last_breakdown_ms()
         return result, None
@@ -511,7 +515,7 @@ def main():
                        "tensors": result["n_tensors"], "elements": result["total_elems"],
                        "parallelism": "zero1-dp{}".format(world) if world > 1 else "single-gpu",
                        "l2": "inputs ({:.1f} GB per step) are larger than L2".format(result["algo_bytes"] / 1e9),
-                       "periods": result["periods"]},
+                       "periods": result["periods"], "elements_by_period": result["period_elements"]},
             "effective_hbm_gbs": eff_gbs, "effective_hbm_frac_of_{}".format(peak_kind): eff_gbs * (1 if world == 1 else 1.0 / world) / peak,
             "algorithmic_bytes_per_step": result["algo_bytes"],
             "calibration_first_step_ms": result["calibration_ms"],

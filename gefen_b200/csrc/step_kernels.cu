@@ -53,10 +53,10 @@ struct StepLaunch {
 
 constexpr int kSmemWs = GEFEN_B200_CODEBOOK_WS_BYTES;
 constexpr int kMaxSmem = 227 * 1024;
-// The fast path reads the codebook twice per element with data-dependent indices. Sixteen
-// interleaved copies (entry e of copy c at word 16*e + c, copy = lane mod 16) leave at most a
-// two-way bank conflict instead of the ~3.5-way one of a single 1 KB table.
-constexpr int kRepCopies = 16;
+// The fast path reads the codebook twice per element with data-dependent indices. One copy per
+// lane (entry e of lane c at word 32*e + c, a 128-byte row per entry) makes every such read
+// conflict-free, against the ~3.5-way conflict of a single 1 KB table.
+constexpr int kRepCopies = 32;
 constexpr int kSmemRep = kMaxCodebook * kRepCopies * 4;
 
 struct SmemView {
@@ -201,8 +201,8 @@ __device__ __forceinline__ void prefetch_l2_range(const void* base, long long by
 // The updated momenta of chunk c: from the warp's staging slice, or recomputed from codes and
 // gradients (which the first pass left in L1/L2) when the kernel runs without staging.
 template <typename S, bool STAGED>
-__device__ __forceinline__ void block_momenta(const gefen_b200_step_tensor_t& t, const SmemView& s, const float4* stage_a,
-                                              const float4* stage_b, const uint2* codes_in, long long chunk0, int c,
+__device__ __forceinline__ void block_momenta(const void* g_blk, const SmemView& s, const float4* stage_a,
+                                              const float4* stage_b, const uint2* codes_in, int c,
                                               float old_mag, float beta1, float omb1, float (&m)[8]) {
     if (STAGED) {
         const float4 ma = stage_a[c], mb = stage_b[c];
@@ -211,7 +211,7 @@ __device__ __forceinline__ void block_momenta(const gefen_b200_step_tensor_t& t,
     } else {
         const uint2 craw = codes_in[c];
         Chunk<S> graw;
-        graw.load(t.g, chunk0 + c);
+        graw.load(g_blk, c);
         float g[8];
         graw.unpack(g);
         const uint32_t cw[2] = {craw.x, craw.y};
@@ -224,44 +224,101 @@ __device__ __forceinline__ void block_momenta(const gefen_b200_step_tensor_t& t,
 }
 
 // --------------------------------------------------------------------------- fast path
-// One warp, one block of t.period = 8 * nchunks elements. `stage` holds period floats for this warp:
-// the first halves of all chunks, then the second halves, so that every 128-bit shared access of
-// a warp is conflict-free.
-template <typename S, bool STAGED>
-__device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& t, long long b, const float* stepsize,
-                                                const SmemView& s, float* stage, int lane) {
-    const int nchunks = static_cast<int>(t.period >> 3);
-    const long long chunk0 = b * nchunks;  // chunk index of the block start, in units of 8 elements
-    const uint2* codes_in = reinterpret_cast<const uint2*>(t.codes) + chunk0;
-    uint2* codes_out = reinterpret_cast<uint2*>(t.codes) + chunk0;
+// Lanes that share one block: all 32 for blocks of 256 elements or more, otherwise the smallest
+// power of two that covers the block's chunks, so that a warp works on 32 / lanes blocks at once.
+__host__ __device__ __forceinline__ int lanes_per_block(long long period) {
+    const long long nchunks = period >> 3;
+    int lanes = 1;
+    while (lanes < 32 && lanes < nchunks) lanes <<= 1;
+    return lanes;
+}
+// Work units (one warp pass each) of a tensor on the fast path.
+__host__ __device__ __forceinline__ long long vec_units(long long num_blocks, long long period) {
+    const int group = 32 / lanes_per_block(period);
+    return (num_blocks + group - 1) / group;
+}
+
+// Reductions over aligned groups of `lanes` lanes (a power of two); every lane of the warp calls them.
+__device__ __forceinline__ float group_max_nan(float v, int lanes) {
+    for (int o = lanes >> 1; o > 0; o >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, v, o);
+        asm("max.NaN.f32 %0, %1, %2;" : "=f"(v) : "f"(v), "f"(other));
+    }
+    return v;
+}
+__device__ __forceinline__ float group_max(float v, int lanes) {
+    for (int o = lanes >> 1; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float group_sum(float v, int lanes) {
+    for (int o = lanes >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// One warp, one unit: 32 / LANES consecutive blocks of t.period = 8 * nchunks elements, LANES lanes
+// each (LANES = lanes_per_block(t.period), uniform over the warp; FULL fixes it to 32 at compile
+// time). A block's slice of `stage` holds period floats: the first halves of all chunks, then the
+// second halves, so that the 128-bit shared accesses of a full warp are conflict-free.
+// The descriptor lives in global or parameter memory, which the stores below might alias as far as
+// the compiler can tell: everything the loops need from it is copied into locals first.
+template <typename S, bool STAGED, bool FULL>
+__device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& t, long long unit, const float* stepsize,
+                                                const SmemView& s, float* stage, int warp_lane) {
+    const int period = static_cast<int>(t.period);     // at most kFastMaxPeriod
+    const int LANES = FULL ? 32 : lanes_per_block(period);
+    const int lane = warp_lane & (LANES - 1);          // lane within the block's group
+    const int member = warp_lane >> (31 - __clz(LANES));   // which block of the unit
+    const long long b = unit * (32 / LANES) + member;
+    const bool valid = b < t.num_blocks;               // the last unit of a tensor may be short
+    const int nchunks = valid ? (period >> 3) : 0;
+    stage += member * period;
+    const long long elem0 = b * static_cast<long long>(period);
+    const uint2* const codes_in = reinterpret_cast<const uint2*>(t.codes + elem0);
+    uint2* const codes_out = reinterpret_cast<uint2*>(t.codes + elem0);
+    const S* const g_blk = static_cast<const S*>(t.g) + elem0;   // chunk c of the block = 8 elements at g_blk + 8 c
+    S* const p_blk = static_cast<S*>(t.p) + elem0;
     const uint32_t flags = t.flags;
     const bool muon = (flags & GEFEN_B200_STEP_MUON) != 0;
 
     const float beta1 = t.beta1;
     const float omb1 = 1.0f - beta1;
-    const float old_mag = load_state(t.mag, b, t.mag_dtype);
-    float4* stage_a = reinterpret_cast<float4*>(stage);
-    float4* stage_b = stage_a + nchunks;
+    const float old_mag = valid ? load_state(t.mag, b, t.mag_dtype) : 0.0f;
+    float4* const stage_a = reinterpret_cast<float4*>(stage);
+    float4* const stage_b = stage_a + (period >> 3);
     const float* rep = s.rep;  // this lane's copy of the codebook: entry e at rep[e * kRepCopies]
+
+    // Everything the block needs from HBM besides codes and gradients is requested now, so that its
+    // latency overlaps the first pass: the second moment and, where the registers allow it (2-byte
+    // types), the first chunk of parameters.
+    constexpr bool kEarlyParams = sizeof(S) == 2;
+    const float lr = t.lr;
+    const float wd_mul = t.wd_mul;
+    const float nesterov_alpha = t.beta2;
+    const bool do_update = muon || lr != 0.0f;
+    const bool load_p = !muon && do_update;
+    float v_in = 1.0f;
+    if (!muon && valid) v_in = stepsize != nullptr ? stepsize[b] : load_state(t.v, b, t.v_dtype);
+    Chunk<S> pnext;
+    if (kEarlyParams && load_p && lane < nchunks) pnext.load(p_blk, lane);
 
     // ---- pass over codes and gradients (the only read of both)
     float absmax = 0.0f;
     float sumsq = 0.0f;
-    constexpr int U = STAGED ? 4 : 2;  // chunks in flight per lane
-    for (int c0 = lane; c0 < nchunks; c0 += 32 * U) {
+    constexpr int U = !FULL ? 1 : (STAGED ? 4 : 2);  // chunks in flight per lane (short blocks: one chunk per lane)
+    for (int c0 = lane; c0 < nchunks; c0 += LANES * U) {
         uint2 craw[U];
         Chunk<S> graw[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int c = c0 + 32 * u;
+            const int c = c0 + LANES * u;
             if (c < nchunks) {
                 craw[u] = codes_in[c];
-                graw[u].load(t.g, chunk0 + c);
+                graw[u].load(g_blk, c);
             }
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int c = c0 + 32 * u;
+            const int c = c0 + LANES * u;
             if (c < nchunks) {
                 float g[8], m[8];
                 graw[u].unpack(g);
@@ -281,24 +338,21 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
             }
         }
     }
-    absmax = warp_max_nan(absmax);
+    absmax = group_max_nan(absmax, LANES);
 
     // ---- second moment (optionally fused) and the step size
     float step = 0.0f;
     if (!muon) {
         if (stepsize != nullptr) {
-            step = stepsize[b];
+            step = v_in;
         } else {
-            float v;
+            float v = v_in;
             if (flags & GEFEN_B200_STEP_FUSE_VMEAN) {
-                const float mean_sq = warp_sum(sumsq) / static_cast<float>(t.period);
-                const float prev = load_state(t.v, b, t.v_dtype);
-                const float nv = fmaf(t.beta2, prev, (1.0f - t.beta2) * mean_sq);
+                const float mean_sq = group_sum(sumsq, LANES) / static_cast<float>(period);
+                const float nv = fmaf(t.beta2, v_in, (1.0f - t.beta2) * mean_sq);
                 v = 0.0f;
-                if (lane == 0) v = store_state(t.v, b, t.v_dtype, nv);
-                v = __shfl_sync(0xffffffffu, v, 0);
-            } else {
-                v = load_state(t.v, b, t.v_dtype);
+                if (lane == 0 && valid) v = store_state(t.v, b, t.v_dtype, nv);
+                v = __shfl_sync(0xffffffffu, v, warp_lane & ~(LANES - 1));
             }
             step = adam_step_size(v, t.bc1, t.bc2, t.eps);
         }
@@ -308,39 +362,32 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
     // ---- rare: a NaN or Inf in the block. The reference's max ignores NaN; redo it that way and
     // let the exact (threshold) quantiser handle non-finite quotients.
     bool exact_path = s.slow;
-    if (!(absmax <= 3.0e38f)) {
+    if (__any_sync(0xffffffffu, !(absmax <= 3.0e38f))) {   // warp-uniform: the reduction below shuffles
         float mx = 0.0f;
-        for (int c = lane; c < nchunks; c += 32) {
+        for (int c = lane; c < nchunks; c += LANES) {
             float m[8];
-            block_momenta<S, STAGED>(t, s, stage_a, stage_b, codes_in, chunk0, c, old_mag, beta1, omb1, m);
+            block_momenta<S, STAGED>(g_blk, s, stage_a, stage_b, codes_in, c, old_mag, beta1, omb1, m);
 #pragma unroll
             for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(m[i]));
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        absmax = mx;
+        absmax = group_max(mx, LANES);
         exact_path = true;
     }
-    if (lane == 0) store_state(t.mag, b, t.mag_dtype, absmax);
+    if (lane == 0 && valid) store_state(t.mag, b, t.mag_dtype, absmax);
 
     const bool nonzero = absmax > 0.0f;
     const bool fastdiv = !exact_path && div_range_ok(absmax);
     const float rinv = fastdiv ? 1.0f / absmax : 0.0f;
-    const bool do_update = muon || t.lr != 0.0f;
-    const bool load_p = !muon && do_update;
     const bool wd = (flags & GEFEN_B200_STEP_WEIGHT_DECAY) != 0;
     const bool nesterov = (flags & GEFEN_B200_STEP_NESTEROV) != 0;
-    const float lr = t.lr;
-    const float wd_mul = t.wd_mul;
 
     // ---- re-encode and update; the parameters of the next chunk are fetched while this one is encoded
-    Chunk<S> pnext;
-    if (load_p && lane < nchunks) pnext.load(t.p, chunk0 + lane);
-    for (int c = lane; c < nchunks; c += 32) {
+    if (!kEarlyParams && load_p && lane < nchunks) pnext.load(p_blk, lane);
+    for (int c = lane; c < nchunks; c += LANES) {
         Chunk<S> praw = pnext;
-        if (load_p && c + 32 < nchunks) pnext.load(t.p, chunk0 + c + 32);
+        if (load_p && c + LANES < nchunks) pnext.load(p_blk, c + LANES);
         float m[8];
-        block_momenta<S, STAGED>(t, s, stage_a, stage_b, codes_in, chunk0, c, old_mag, beta1, omb1, m);
+        block_momenta<S, STAGED>(g_blk, s, stage_a, stage_b, codes_in, c, old_mag, beta1, omb1, m);
         uint32_t code[8];
         float q[8];
         if (fastdiv) {
@@ -368,18 +415,18 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
                 // torch: m.mul_(momentum).add_(g, alpha=1-momentum) on the rounded momentum
                 // (reference: gefen_muon.py:312-314); alpha travels in t.beta2.
                 Chunk<S> g2;
-                g2.load(t.g, chunk0 + c);
+                g2.load(g_blk, c);
                 float g[8];
                 g2.unpack(g);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const float m1 = ScalarIO<S>::round(ScalarIO<S>::round(q[i]) * beta1);
-                    q[i] = fmaf(t.beta2, g[i], m1);
+                    q[i] = fmaf(nesterov_alpha, g[i], m1);
                 }
             }
             Chunk<S> out;
             out.pack(q);
-            out.store(t.p, chunk0 + c);
+            out.store(p_blk, c);
         } else if (do_update) {
             float pv[8];
             praw.unpack(pv);
@@ -393,7 +440,7 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
 #pragma unroll
             for (int i = 0; i < 8; ++i) pv[i] = fmaf(-(q[i] * step), lr, pv[i]);
             praw.pack(pv);
-            praw.store(t.p, chunk0 + c);
+            praw.store(p_blk, c);
         }
     }
     __syncwarp();  // the staging slice is free for this warp's next block
@@ -420,12 +467,13 @@ __global__ void __launch_bounds__(512, STAGED ? 1 : 2) step_vec_kernel(const __g
     const long long warp_global = static_cast<long long>(blockIdx.x) * warps + warp;
     const long long warp_stride = static_cast<long long>(gridDim.x) * warps;
     const gefen_b200_step_tensor_t* __restrict__ tp = table;
-    long long t_first = tp->first_block, t_count = tp->num_blocks;
+    // On this path first_block and total_blocks count work units (see vec_units), not blocks.
+    long long t_first = tp->first_block, t_count = vec_units(tp->num_blocks, tp->period);
     for (long long gb = warp_global; gb < L.total_blocks; gb += warp_stride) {
         if (gb < t_first || gb >= t_first + t_count) {
             tp = table + find_tensor(table, L.n_tensors, gb);
             t_first = tp->first_block;
-            t_count = tp->num_blocks;
+            t_count = vec_units(tp->num_blocks, tp->period);
         }
         const gefen_b200_step_tensor_t& t = *tp;
         const long long nb_local = gb - t_first;
@@ -438,7 +486,8 @@ __global__ void __launch_bounds__(512, STAGED ? 1 : 2) step_vec_kernel(const __g
             if (!(t.flags & GEFEN_B200_STEP_MUON))
                 prefetch_l2_range(static_cast<const char*>(t.p) + elem0 * sizeof(S), t.period * sizeof(S), lane);
         }
-        warp_block_step<S, STAGED>(t, nb_local, L.stepsize, s, stage, lane);
+        if (t.period >= 256) warp_block_step<S, STAGED, true>(t, nb_local, L.stepsize, s, stage, lane);
+        else warp_block_step<S, STAGED, false>(t, nb_local, L.stepsize, s, stage, lane);
     }
 }
 
@@ -619,7 +668,8 @@ static int grid_for(long long groups_needed, int groups_per_cta, int ctas_per_sm
 
 constexpr int kFastMaxPeriod = 8192;
 constexpr int kFastMaxWarps = 16;
-constexpr int kStaticSmemSlack = 1024;  // static __shared__ of the kernels plus the per-CTA reservation
+constexpr int kStaticSmemSlack = 256;   // static __shared__ of the kernels (counted against the per-CTA limit)
+constexpr int kCtaReservedSmem = 1024;  // what the hardware sets aside per resident CTA (not part of the limit)
 
 // GEFEN_B200_STEP_STAGED=0/1 in the environment overrides the choice of fast-path variant (for
 // measurements); by default the staged variant is used.
@@ -643,7 +693,8 @@ static int launch_vec_variant(StepLaunch L, const gefen_b200_step_tensor_t& sing
         GEFEN_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem - kStaticSmemSlack));
         configured[dev] = true;
     }
-    const long long stage_bytes = STAGED ? max_period * 4 : 0;
+    // a warp stages one long block, or the 32 / lanes short blocks (at most 256 elements together) of a unit
+    const long long stage_bytes = STAGED ? (max_period > 256 ? max_period : 256) * 4 : 0;
     int warps = kFastMaxWarps;
     if (STAGED) {
         warps = static_cast<int>((kMaxSmem - kStaticSmemSlack - kSmemWs - kSmemRep) / stage_bytes);
@@ -652,10 +703,10 @@ static int launch_vec_variant(StepLaunch L, const gefen_b200_step_tensor_t& sing
     }
     if (L.total_blocks < warps) warps = static_cast<int>(L.total_blocks);
     const int smem = kSmemWs + kSmemRep + static_cast<int>(stage_bytes) * warps;
-    int ctas_per_sm = (kMaxSmem - kStaticSmemSlack) / (smem + kStaticSmemSlack);
+    int ctas_per_sm = (kMaxSmem + kCtaReservedSmem) / (smem + kStaticSmemSlack + kCtaReservedSmem);
     if (ctas_per_sm > 2) ctas_per_sm = 2;
     if (ctas_per_sm < 1) ctas_per_sm = 1;
-    L.stage_floats = STAGED ? static_cast<int>(max_period) : 0;
+    L.stage_floats = static_cast<int>(stage_bytes / 4);
     const int grid = grid_for(L.total_blocks, warps, ctas_per_sm);
     kernel<<<grid, warps * 32, smem, stream>>>(L, single);
     GEFEN_CHECK_CUDA(cudaGetLastError());
@@ -746,10 +797,11 @@ static int run_single(gefen_b200_step_tensor_t& t, int param_dtype, const float*
     L.table = nullptr;
     L.n_tensors = 1;
     L.stage_floats = 0;
-    L.total_blocks = t.num_blocks;
+    const int cls = tensor_class(t, param_dtype);
+    L.total_blocks = cls >= 1 ? vec_units(t.num_blocks, t.period) : t.num_blocks;
     L.ws = static_cast<const unsigned char*>(ws);
     L.stepsize = stepsize;
-    return launch_class(tensor_class(t, param_dtype), param_dtype, L, t, t.period, stream);
+    return launch_class(cls, param_dtype, L, t, t.period, stream);
 }
 
 }  // namespace gefen
@@ -956,8 +1008,9 @@ int gefen_b200_multi_tensor_step(gefen_b200_step_tensor_t* host_table, void* dev
         int end = begin;
         long long first = 0;
         while (end < n_tensors && host_table[end].reserved_[0] == host_table[begin].reserved_[0]) {
-            host_table[end].first_block = first;
-            first += host_table[end].num_blocks;
+            host_table[end].first_block = first;   // in work units on the vector path, in blocks elsewhere
+            first += host_table[end].reserved_[0] >= 1 ? vec_units(host_table[end].num_blocks, host_table[end].period)
+                                                       : host_table[end].num_blocks;
             ++end;
         }
         host_table[begin].reserved_[1] = end - begin;  // run length, read back below
@@ -968,7 +1021,8 @@ int gefen_b200_multi_tensor_step(gefen_b200_step_tensor_t* host_table, void* dev
     for (int begin = 0; begin < n_tensors;) {
         const int run = host_table[begin].reserved_[1];
         const gefen_b200_step_tensor_t& last = host_table[begin + run - 1];
-        const long long total = last.first_block + last.num_blocks;
+        const long long total = last.first_block + (last.reserved_[0] >= 1 ? vec_units(last.num_blocks, last.period)
+                                                                            : last.num_blocks);
         long long max_period = 0;
         for (int i = begin; i < begin + run; ++i) max_period = host_table[i].period > max_period ? host_table[i].period : max_period;
         if (total > 0) {

@@ -13,7 +13,9 @@ DTYPES = [torch.float32, torch.bfloat16, torch.float16]
 # (num_blocks, period): fast path (multiples of 8 up to 2048, ragged last pass included), the generic
 # warp path (odd / tiny periods) and the generic CTA path (period > 2048)
 SHAPES = [(64, 512), (33, 768), (20, 1152), (16, 2048), (9, 1120), (7, 1664), (5, 8), (40, 24), (11, 12),
-          (301, 1), (13, 37), (6, 4096), (3, 3000), (2, 10007)]
+          (301, 1), (13, 37), (6, 4096), (3, 3000), (2, 10007),
+          # blocks shorter than 256 elements share a warp (32, 16, 8, 4, 2 blocks per pass), ragged last pass
+          (37, 128), (101, 64), (1001, 16), (67, 8), (3, 256), (50, 40), (21, 104), (1, 8)]
 
 
 def _state(nb, period, dtype, state_dtype, seed):
