@@ -19,7 +19,7 @@ _DTYPE_TAG = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torc
 
 OK, EINVAL, ECUDA, ERUNTIME, EUNSUPPORTED = 0, -1, -2, -3, -4
 
-CODEBOOK_WS_BYTES = 67616
+CODEBOOK_WS_BYTES = 34848
 
 STEP_FUSE_VMEAN = 1
 STEP_WEIGHT_DECAY = 2

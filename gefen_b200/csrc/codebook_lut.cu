@@ -65,15 +65,15 @@ __global__ void __launch_bounds__(256) codebook_prepare_kernel(const float* __re
     uint32_t* ws_lut = reinterpret_cast<uint32_t*>(ws + kWsLutOff);
     ws_cb[t] = cb[t];
     ws_thr[t] = thr[t];
-    bool slow = false;
+    int slow = 0;
     for (int cell = t; cell < kLutBytes / 8; cell += blockDim.x) {
         uint32_t w0 = 0x7f800000u, w1 = 0u;  // padding entries: +inf threshold, nothing below
         if (cell <= kLutCells) lut_build_cell(cell, tcell, thr, k - 1, cb[k - 1], &w0, &w1);
         ws_lut[2 * cell] = w0;
         ws_lut[2 * cell + 1] = w1;
-        slow = slow || (w1 & kLutSlowBit);
+        if (w1 & kLutSlowBit) ++slow;
     }
-    if (slow) atomicOr(&any_slow, 1);
+    if (slow) atomicAdd(&any_slow, slow);
     __syncthreads();
     if (t == 0) {
         int* meta = reinterpret_cast<int*>(ws + kWsMetaOff);

@@ -43,7 +43,7 @@ int sm_count();  // SMs of the current device (cached per device)
 // Layout of the per-codebook workspace (GEFEN_B200_CODEBOOK_WS_BYTES).
 constexpr int kWsCodebookOff = 0;      // 256 floats, tail padded with the last entry
 constexpr int kWsThresholdOff = 1024;  // 256 floats, tail padded with +inf
-constexpr int kWsMetaOff = 2048;       // 4 ints: codebook size, 1 if any table cell is undecidable, 0, 0
+constexpr int kWsMetaOff = 2048;       // 4 ints: codebook size, number of undecidable table cells, 0, 0
 constexpr int kWsLutOff = 2064;        // kLutBytes of 8-byte entries
 static_assert(kWsLutOff + kLutBytes == GEFEN_B200_CODEBOOK_WS_BYTES, "workspace size");
 

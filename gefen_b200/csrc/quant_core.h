@@ -22,8 +22,8 @@
 namespace gefen {
 
 constexpr int kMaxCodebook = 256;          // reference: at most 256 entries (uint8 codes)
-constexpr int kLutCells = 8192;            // cells over [-1, 1); one more cell for x == 1
-constexpr int kLutBytes = 65552;           // 8193 entries of 8 bytes, padded to a multiple of 16
+constexpr int kLutCells = 4096;            // cells over [-1, 1); one more cell for x == 1
+constexpr int kLutBytes = 32784;           // 4097 entries of 8 bytes, padded to a multiple of 16
 constexpr uint32_t kLutSlowBit = 0x80000000u;    // cell cannot be decided by one comparison
 
 struct alignas(8) uint2v { uint32_t x, y; };   // 8-byte table entry, read with one 64-bit load
@@ -98,19 +98,22 @@ GEFEN_HD int entry_exact(float x, const float* thr, const float* cb, int k) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Uniform-grid lookup table over x in [-1, 1]: 8192 cells of width 2^-12 (one more for x == 1).
-// Cell of x: the integer part of fma(x, 32768, magic) keeps round(x * 32768) + 32768 in its low
+// Uniform-grid lookup table over x in [-1, 1]: 4096 cells of width 2^-11 (one more for x == 1),
+// the width of one bin of the 4096-bin histogram the codebook is fitted to, so that codebooks from
+// that fit put at most one threshold in almost every cell.
+// Cell of x: the integer part of fma(x, 16384, magic) keeps round(x * 16384) + 16384 in its low
 // mantissa bits; masking the low three bits gives the BYTE offset of the 8-byte table entry. The
 // map is monotone in x, which is all the table needs: every threshold in a lower cell is below x,
 // every threshold in a higher cell is above it, and the one threshold that may share x's cell is
 // compared exactly in float. entry(x) = below(cell) + (x > threshold(cell)).
 // Entry layout: word 0 = float bits of the cell's threshold (+inf if none), word 1 = number of
 // thresholds below the cell, bit 31 set when the cell cannot be decided this way (two or more
-// thresholds inside, or values above the last codebook entry): such codebooks use entry_exact.
+// thresholds inside, or values above the last codebook entry): values in such cells go through
+// entry_exact.
 GEFEN_HD uint32_t lut_byte_offset(float x) {
     union { float f; uint32_t u; } c;
-    c.f = fmaf(x, 32768.0f, 12582912.0f + 32768.0f);
-    return c.u & 0x1FFF8u;
+    c.f = fmaf(x, 16384.0f, 12582912.0f + 16384.0f);
+    return c.u & 0xFFF8u;
 }
 GEFEN_HD int lut_cell(float x) { return static_cast<int>(lut_byte_offset(x) >> 3); }
 
@@ -140,7 +143,7 @@ GEFEN_HD void lut_build_cell(int cell, const int* tcell, const float* thr, int n
     *word_below = static_cast<uint32_t>(below) | (undecidable ? kLutSlowBit : 0u);
 }
 
-// The fast query; valid when no cell of the table carries kLutSlowBit.
+// The table query; *slow tells the caller to use entry_exact instead.
 GEFEN_HD int lut_query(float x, const unsigned char* lut_bytes, bool* slow) {
     const uint2v e = *reinterpret_cast<const uint2v*>(lut_bytes + lut_byte_offset(x));
     union { float f; uint32_t u; } c;
@@ -149,8 +152,8 @@ GEFEN_HD int lut_query(float x, const unsigned char* lut_bytes, bool* slow) {
     return static_cast<int>(e.y & 0xFFu) + (x > c.f ? 1 : 0);
 }
 
-// Same without the flag test, for tables known to have no undecidable cell (word 1 is then the
-// bare count).
+// Same, with the flag left in bit 31 of the result for the caller to test (several results can be
+// OR-ed and tested once).
 GEFEN_HD uint32_t lut_query_fast(float x, const unsigned char* lut_bytes) {
     const uint2v e = *reinterpret_cast<const uint2v*>(lut_bytes + lut_byte_offset(x));
     union { float f; uint32_t u; } c;

@@ -65,7 +65,6 @@ struct SmemView {
     const unsigned char* lut;    // kLutBytes
     const float* rep;            // fast path only: kRepCopies interleaved copies of cb, offset by the lane's copy
     int k;                       // true codebook size
-    bool slow;                   // the table has undecidable cells: use entry_exact
 };
 
 // Stages the workspace with one bulk copy. Returns false (uniformly for the CTA) if the copy did
@@ -89,11 +88,8 @@ __device__ __forceinline__ bool stage_tables(const unsigned char* ws, unsigned c
     view.lut = smem + kWsLutOff;
     view.rep = nullptr;
     view.k = 1;
-    view.slow = true;
     if (!ok) return false;
-    const int* meta = reinterpret_cast<const int*>(smem + kWsMetaOff);
-    view.k = meta[0];
-    view.slow = meta[1] != 0;
+    view.k = reinterpret_cast<const int*>(smem + kWsMetaOff)[0];
     return true;
 }
 
@@ -361,7 +357,7 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
 
     // ---- rare: a NaN or Inf in the block. The reference's max ignores NaN; redo it that way and
     // let the exact (threshold) quantiser handle non-finite quotients.
-    bool exact_path = s.slow;
+    bool exact_path = false;
     if (__any_sync(0xffffffffu, !(absmax <= 3.0e38f))) {   // warp-uniform: the reduction below shuffles
         float mx = 0.0f;
         for (int c = lane; c < nchunks; c += LANES) {
@@ -391,12 +387,24 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
         uint32_t code[8];
         float q[8];
         if (fastdiv) {
+            uint32_t any = 0u;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const float x = div_by_block_constant(m[i], absmax, rinv);
                 code[i] = lut_query_fast(x, s.lut);
-                q[i] = rep[code[i] * kRepCopies] * absmax;
+                any |= code[i];
             }
+            if (any & kLutSlowBit) {   // rare: a cell with two thresholds, or values above the last entry
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    if (code[i] & kLutSlowBit) {
+                        const float x = div_by_block_constant(m[i], absmax, rinv);
+                        code[i] = static_cast<uint32_t>(entry_exact(x, s.thr, s.cb, s.k));
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) q[i] = rep[code[i] * kRepCopies] * absmax;
         } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -446,8 +454,12 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
     __syncwarp();  // the staging slice is free for this warp's next block
 }
 
+// Warps per CTA of the staged kernel: twenty for 2-byte types (96 registers per thread), sixteen for
+// fp32, whose wider chunks need the full 128.
+template <typename S> __host__ __device__ constexpr int vec_max_threads() { return sizeof(S) == 2 ? 640 : 512; }
+
 template <typename S, bool STAGED>
-__global__ void __launch_bounds__(512, STAGED ? 1 : 2) step_vec_kernel(const __grid_constant__ StepLaunch L,
+__global__ void __launch_bounds__(STAGED ? vec_max_threads<S>() : 512, STAGED ? 1 : 2) step_vec_kernel(const __grid_constant__ StepLaunch L,
                                                            const __grid_constant__ gefen_b200_step_tensor_t single) {
     extern __shared__ __align__(128) unsigned char smem[];
     SmemView s;
@@ -682,6 +694,17 @@ static int staged_default() {
     return cached;
 }
 
+// GEFEN_B200_STEP_WARPS=n caps the warps per CTA of the staged kernel (for measurements).
+static int warps_override() {
+    static int cached = -1;
+    if (cached < 0) {
+        const char* e = getenv("GEFEN_B200_STEP_WARPS");
+        cached = e != nullptr ? atoi(e) : 0;
+        if (cached < 0) cached = 0;
+    }
+    return cached;
+}
+
 template <typename S, bool STAGED>
 static int launch_vec_variant(StepLaunch L, const gefen_b200_step_tensor_t& single, long long max_period,
                               cudaStream_t stream) {
@@ -697,8 +720,10 @@ static int launch_vec_variant(StepLaunch L, const gefen_b200_step_tensor_t& sing
     const long long stage_bytes = STAGED ? (max_period > 256 ? max_period : 256) * 4 : 0;
     int warps = kFastMaxWarps;
     if (STAGED) {
+        int max_warps = vec_max_threads<S>() / 32;
+        if (warps_override() > 0 && warps_override() < max_warps) max_warps = warps_override();
         warps = static_cast<int>((kMaxSmem - kStaticSmemSlack - kSmemWs - kSmemRep) / stage_bytes);
-        if (warps > kFastMaxWarps) warps = kFastMaxWarps;
+        if (warps > max_warps) warps = max_warps;
         if (warps < 1) return fail(GEFEN_B200_EINVAL, "internal: period %lld too large for the staged path", max_period);
     }
     if (L.total_blocks < warps) warps = static_cast<int>(L.total_blocks);
@@ -929,7 +954,7 @@ int gefen_b200_automatic_gefen_muon_momentum(
 // entry point, when it is given no codebook workspace, allocates one per device with cudaMalloc on
 // first use; this one keeps that workspace in a fixed array inside the library image instead.
 //
-// The array costs GEFEN_B200_CODEBOOK_WS_BYTES (67 616 bytes) of device memory on every GPU that
+// The array costs GEFEN_B200_CODEBOOK_WS_BYTES (34 848 bytes) of device memory on every GPU that
 // loads the library, until the process exits. It is sized for the largest codebook the kernels
 // accept, 256 entries; a larger codebook is rejected. Every call rewrites the whole array from the
 // codebook it is given, on the caller's stream, before the step kernel reads it, so nothing has to

@@ -38,8 +38,8 @@ extern "C" {
 
 /* Bytes of the per-codebook workspace filled by gefen_b200_codebook_prepare:
  * 256 padded codebook floats, 256 decision thresholds, 16 bytes of metadata and the
- * 8193-entry lookup table (8 bytes per entry, padded). */
-#define GEFEN_B200_CODEBOOK_WS_BYTES 67616
+ * 4097-entry lookup table (8 bytes per entry, padded). */
+#define GEFEN_B200_CODEBOOK_WS_BYTES 34848
 
 /* flags of gefen_b200_step_tensor_t.flags */
 #define GEFEN_B200_STEP_FUSE_VMEAN 1u   /* update vmean from the gradient inside the step kernel */
