@@ -239,6 +239,10 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
               "period_elements": {str(k): by_period[k] for k in sorted(by_period)}}
     if world > 1:
         result["breakdown"] = opt.last_breakdown_ms()
+        result["breakdown"]["all_gather_mode"] = opt.all_gather_mode
+        result["breakdown"]["reduce_scatter_mode"] = opt.reduce_scatter_mode
+        if opt.fused_errors:
+            result["breakdown"]["fused_errors"] = dict(opt.fused_errors)
         return result, None
 
     # ---- roofline of the dominant kernel: the staged vector step over all its tensors, one launch

@@ -71,6 +71,7 @@ def _declare(lib):
         "gefen_b200_automatic_gefen_muon_momentum": (
             i32, [vp, i32, vp, vp, i32, vp, i32, vp, vp, i32, i64, i64, dbl, vp]),
         "gefen_b200_multi_tensor_step": (i32, [vp, vp, i32, i32, vp, vp]),
+        "gefen_b200_multi_tensor_step_peers": (i32, [vp, vp, i32, i32, vp, vp, i32, vp, i32, dbl, vp]),
         "gefen_b200_step_tensor_size": (i32, []),
         "gefen_b200_step_tensor_class": (i32, [vp, i32]),
         "gefen_b200_exact_histogram": (i32, [vp, i32, i64, i64, vp, i32, vp]),

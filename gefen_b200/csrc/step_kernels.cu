@@ -49,7 +49,22 @@ struct StepLaunch {
     long long total_blocks;
     const unsigned char* ws;                // codebook workspace
     const float* stepsize;                  // optional precomputed per-block step (single tensor only)
+    // ZeRO-1 with the all-gather fused in: every updated parameter is also stored into the same
+    // place of n_peers other GPUs' parameter buffers (byte distance from this GPU's buffer to
+    // theirs in this process's address space; plain peer stores over NVLink, no loads).
+    int n_peers;
+    long long peer_delta[GEFEN_B200_MAX_PEERS];
+    // ... and with the reduce-scatter fused in: the gradient of an element is grad_scale times the
+    // sum over n_grad_srcs buffers (byte distances from this GPU's gradient buffer, rank order, 0
+    // for this rank itself), rounded to the gradient dtype. 0 sources: gradients are used as they are.
+    int n_grad_srcs;
+    float grad_scale;
+    long long grad_delta[GEFEN_B200_MAX_PEERS + 1];
 };
+
+template <typename T> __device__ __forceinline__ T* peer_ptr(T* p, long long delta) {
+    return reinterpret_cast<T*>(reinterpret_cast<uintptr_t>(p) + delta);
+}
 
 constexpr int kSmemWs = GEFEN_B200_CODEBOOK_WS_BYTES;
 constexpr int kMaxSmem = 227 * 1024;
@@ -194,29 +209,11 @@ __device__ __forceinline__ void prefetch_l2_range(const void* base, long long by
     }
 }
 
-// The updated momenta of chunk c: from the warp's staging slice, or recomputed from codes and
-// gradients (which the first pass left in L1/L2) when the kernel runs without staging.
-template <typename S, bool STAGED>
-__device__ __forceinline__ void block_momenta(const void* g_blk, const SmemView& s, const float4* stage_a,
-                                              const float4* stage_b, const uint2* codes_in, int c,
-                                              float old_mag, float beta1, float omb1, float (&m)[8]) {
-    if (STAGED) {
-        const float4 ma = stage_a[c], mb = stage_b[c];
-        m[0] = ma.x; m[1] = ma.y; m[2] = ma.z; m[3] = ma.w;
-        m[4] = mb.x; m[5] = mb.y; m[6] = mb.z; m[7] = mb.w;
-    } else {
-        const uint2 craw = codes_in[c];
-        Chunk<S> graw;
-        graw.load(g_blk, c);
-        float g[8];
-        graw.unpack(g);
-        const uint32_t cw[2] = {craw.x, craw.y};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t code = (cw[i >> 2] >> (8 * (i & 3))) & 0xFFu;
-            m[i] = ema_update(beta1, old_mag * s.rep[code * kRepCopies], omb1, g[i]);
-        }
-    }
+// The updated momenta of chunk c, from the warp's staging slice.
+__device__ __forceinline__ void staged_momenta(const float4* stage_a, const float4* stage_b, int c, float (&m)[8]) {
+    const float4 ma = stage_a[c], mb = stage_b[c];
+    m[0] = ma.x; m[1] = ma.y; m[2] = ma.z; m[3] = ma.w;
+    m[4] = mb.x; m[5] = mb.y; m[6] = mb.z; m[7] = mb.w;
 }
 
 // --------------------------------------------------------------------------- fast path
@@ -251,15 +248,88 @@ __device__ __forceinline__ float group_sum(float v, int lanes) {
     return v;
 }
 
+// First pass of a block whose gradient is averaged over up to NSRC buffers. kSlots 16-byte (fp32:
+// 32-byte) loads per lane are in flight at a time: U chunks x a batch of BS sources; the sources of
+// a chunk are added batch after batch, in the order given.
+template <typename S, int NSRC>
+__device__ __forceinline__ void reduce_pass(const StepLaunch& L, const S* g_blk, const uint2* codes_in, float4* stage_a,
+                                            float4* stage_b, const float* rep, int lane, int LANES, int nchunks,
+                                            float old_mag, float beta1, float omb1, float& absmax, float& sumsq) {
+    constexpr int kSlots = sizeof(S) == 2 ? 4 : 2;
+    constexpr int BS = NSRC < kSlots ? NSRC : kSlots;
+    constexpr int U = kSlots / BS;
+    const int n_src = L.n_grad_srcs;
+    const float scale = L.grad_scale;
+    for (int c0 = lane; c0 < nchunks; c0 += LANES * U) {
+        float acc[U][8];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[u][i] = 0.0f;
+#pragma unroll
+        for (int r0 = 0; r0 < NSRC; r0 += BS) {
+            if (r0 < n_src) {
+                Chunk<S> src[U * BS];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int c = c0 + LANES * u;
+#pragma unroll
+                    for (int r = 0; r < BS; ++r)
+                        if (c < nchunks && r0 + r < n_src) src[u * BS + r].load(peer_ptr(g_blk, L.grad_delta[r0 + r]), c);
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int c = c0 + LANES * u;
+#pragma unroll
+                    for (int r = 0; r < BS; ++r) {
+                        if (c < nchunks && r0 + r < n_src) {
+                            float part[8];
+                            src[u * BS + r].unpack(part);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) acc[u][i] += part[i];
+                        }
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int c = c0 + LANES * u;
+            if (c < nchunks) {
+                const uint2 craw = codes_in[c];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[u][i] *= scale;
+                Chunk<S> rounded;
+                rounded.pack(acc[u]);
+                float g[8], m[8];
+                rounded.unpack(g);
+                const uint32_t cw[2] = {craw.x, craw.y};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t code = (cw[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+                    const float cur = old_mag * rep[code * kRepCopies];
+                    m[i] = ema_update(beta1, cur, omb1, g[i]);
+                    absmax = max_abs_nan(absmax, m[i]);
+                    sumsq = fmaf(g[i], g[i], sumsq);
+                }
+                stage_a[c] = make_float4(m[0], m[1], m[2], m[3]);
+                stage_b[c] = make_float4(m[4], m[5], m[6], m[7]);
+            }
+        }
+    }
+}
+
 // One warp, one unit: 32 / LANES consecutive blocks of t.period = 8 * nchunks elements, LANES lanes
 // each (LANES = lanes_per_block(t.period), uniform over the warp; FULL fixes it to 32 at compile
 // time). A block's slice of `stage` holds period floats: the first halves of all chunks, then the
 // second halves, so that the 128-bit shared accesses of a full warp are conflict-free.
 // The descriptor lives in global or parameter memory, which the stores below might alias as far as
 // the compiler can tell: everything the loops need from it is copied into locals first.
-template <typename S, bool STAGED, bool FULL>
-__device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& t, long long unit, const float* stepsize,
+template <typename S, bool REDUCE, bool FULL>
+__device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& t, long long unit, const StepLaunch& L,
                                                 const SmemView& s, float* stage, int warp_lane) {
+    const float* const stepsize = L.stepsize;
+    const int n_peers = L.n_peers;
     const int period = static_cast<int>(t.period);     // at most kFastMaxPeriod
     const int LANES = FULL ? 32 : lanes_per_block(period);
     const int lane = warp_lane & (LANES - 1);          // lane within the block's group
@@ -300,34 +370,42 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
     // ---- pass over codes and gradients (the only read of both)
     float absmax = 0.0f;
     float sumsq = 0.0f;
-    constexpr int U = !FULL ? 1 : (STAGED ? 4 : 2);  // chunks in flight per lane (short blocks: one chunk per lane)
-    for (int c0 = lane; c0 < nchunks; c0 += LANES * U) {
-        uint2 craw[U];
-        Chunk<S> graw[U];
+    if (REDUCE) {
+        // The gradient of this block is the average over the ranks' buffers (this GPU's and the
+        // peers', read over NVLink), summed in fp32 in rank order and rounded to the gradient dtype,
+        // as a reduce-scatter into that dtype would leave it.
+        const int n_src = L.n_grad_srcs;
+        if (n_src <= 2) reduce_pass<S, 2>(L, g_blk, codes_in, stage_a, stage_b, rep, lane, LANES, nchunks, old_mag, beta1, omb1, absmax, sumsq);
+        else if (n_src <= 4) reduce_pass<S, 4>(L, g_blk, codes_in, stage_a, stage_b, rep, lane, LANES, nchunks, old_mag, beta1, omb1, absmax, sumsq);
+        else reduce_pass<S, 8>(L, g_blk, codes_in, stage_a, stage_b, rep, lane, LANES, nchunks, old_mag, beta1, omb1, absmax, sumsq);
+    } else {
+        constexpr int U = FULL ? 4 : 1;  // chunks in flight per lane (short blocks: one chunk per lane)
+        for (int c0 = lane; c0 < nchunks; c0 += LANES * U) {
+            uint2 craw[U];
+            Chunk<S> graw[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int c = c0 + LANES * u;
-            if (c < nchunks) {
-                craw[u] = codes_in[c];
-                graw[u].load(g_blk, c);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int c = c0 + LANES * u;
-            if (c < nchunks) {
-                float g[8], m[8];
-                graw[u].unpack(g);
-                const uint32_t cw[2] = {craw[u].x, craw[u].y};
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint32_t code = (cw[i >> 2] >> (8 * (i & 3))) & 0xFFu;
-                    const float cur = old_mag * rep[code * kRepCopies];
-                    m[i] = ema_update(beta1, cur, omb1, g[i]);
-                    absmax = max_abs_nan(absmax, m[i]);
-                    sumsq = fmaf(g[i], g[i], sumsq);
+            for (int u = 0; u < U; ++u) {
+                const int c = c0 + LANES * u;
+                if (c < nchunks) {
+                    craw[u] = codes_in[c];
+                    graw[u].load(g_blk, c);
                 }
-                if (STAGED) {
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int c = c0 + LANES * u;
+                if (c < nchunks) {
+                    float g[8], m[8];
+                    graw[u].unpack(g);
+                    const uint32_t cw[2] = {craw[u].x, craw[u].y};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const uint32_t code = (cw[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+                        const float cur = old_mag * rep[code * kRepCopies];
+                        m[i] = ema_update(beta1, cur, omb1, g[i]);
+                        absmax = max_abs_nan(absmax, m[i]);
+                        sumsq = fmaf(g[i], g[i], sumsq);
+                    }
                     stage_a[c] = make_float4(m[0], m[1], m[2], m[3]);
                     stage_b[c] = make_float4(m[4], m[5], m[6], m[7]);
                 }
@@ -362,7 +440,7 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
         float mx = 0.0f;
         for (int c = lane; c < nchunks; c += LANES) {
             float m[8];
-            block_momenta<S, STAGED>(g_blk, s, stage_a, stage_b, codes_in, c, old_mag, beta1, omb1, m);
+            staged_momenta(stage_a, stage_b, c, m);
 #pragma unroll
             for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(m[i]));
         }
@@ -383,7 +461,7 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
         Chunk<S> praw = pnext;
         if (load_p && c + LANES < nchunks) pnext.load(p_blk, c + LANES);
         float m[8];
-        block_momenta<S, STAGED>(g_blk, s, stage_a, stage_b, codes_in, c, old_mag, beta1, omb1, m);
+        staged_momenta(stage_a, stage_b, c, m);
         uint32_t code[8];
         float q[8];
         if (fastdiv) {
@@ -449,6 +527,7 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
             for (int i = 0; i < 8; ++i) pv[i] = fmaf(-(q[i] * step), lr, pv[i]);
             praw.pack(pv);
             praw.store(p_blk, c);
+            for (int r = 0; r < n_peers; ++r) praw.store(peer_ptr(p_blk, L.peer_delta[r]), c);
         }
     }
     __syncwarp();  // the staging slice is free for this warp's next block
@@ -456,10 +535,15 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
 
 // Warps per CTA of the staged kernel: twenty for 2-byte types (96 registers per thread), sixteen for
 // fp32, whose wider chunks need the full 128.
-template <typename S> __host__ __device__ constexpr int vec_max_threads() { return sizeof(S) == 2 ? 640 : 512; }
+// The variant that averages gradients over NVLink holds more loads in flight per thread and is not
+// bound by occupancy: sixteen warps of 128 registers for every type.
+template <typename S, bool REDUCE> __host__ __device__ constexpr int vec_max_threads() {
+    return (sizeof(S) == 2 && !REDUCE) ? 640 : 512;
+}
 
-template <typename S, bool STAGED>
-__global__ void __launch_bounds__(STAGED ? vec_max_threads<S>() : 512, STAGED ? 1 : 2) step_vec_kernel(const __grid_constant__ StepLaunch L,
+// REDUCE: the gradients are averaged over the ranks' buffers inside the kernel (StepLaunch::grad_delta).
+template <typename S, bool REDUCE>
+__global__ void __launch_bounds__(vec_max_threads<S, REDUCE>(), 1) step_vec_kernel(const __grid_constant__ StepLaunch L,
                                                            const __grid_constant__ gefen_b200_step_tensor_t single) {
     extern __shared__ __align__(128) unsigned char smem[];
     SmemView s;
@@ -491,16 +575,26 @@ __global__ void __launch_bounds__(STAGED ? vec_max_threads<S>() : 512, STAGED ? 
         const long long nb_local = gb - t_first;
         const long long next = nb_local + warp_stride;
         // same tensor: hint the next block of this warp (measured: pays for 2-byte dtypes with long blocks only)
-        if (STAGED && sizeof(S) == 2 && t.period >= 1024 && next < t_count) {
+        if (!REDUCE && sizeof(S) == 2 && t.period >= 1024 && next < t_count) {
             const long long elem0 = next * t.period;
             prefetch_l2_range(t.codes + elem0, t.period, lane);
             prefetch_l2_range(static_cast<const char*>(t.g) + elem0 * sizeof(S), t.period * sizeof(S), lane);
             if (!(t.flags & GEFEN_B200_STEP_MUON))
                 prefetch_l2_range(static_cast<const char*>(t.p) + elem0 * sizeof(S), t.period * sizeof(S), lane);
         }
-        if (t.period >= 256) warp_block_step<S, STAGED, true>(t, nb_local, L.stepsize, s, stage, lane);
-        else warp_block_step<S, STAGED, false>(t, nb_local, L.stepsize, s, stage, lane);
+        if (t.period >= 256) warp_block_step<S, REDUCE, true>(t, nb_local, L, s, stage, lane);
+        else warp_block_step<S, REDUCE, false>(t, nb_local, L, s, stage, lane);
     }
+}
+
+// One gradient element as the step sees it: the local value, or the rounded average over the
+// ranks' buffers (see StepLaunch::grad_delta).
+template <typename S>
+__device__ __forceinline__ float gradient_element(const S* g, const StepLaunch& L) {
+    if (L.n_grad_srcs == 0) return ScalarIO<S>::load(g);
+    float acc = 0.0f;
+    for (int r = 0; r < L.n_grad_srcs; ++r) acc += ScalarIO<S>::load(peer_ptr(g, L.grad_delta[r]));
+    return ScalarIO<S>::round(acc * L.grad_scale);
 }
 
 // --------------------------------------------------------------------------- generic path
@@ -555,7 +649,7 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
         // (reference: automatic_gefen_fused_kernel.cu:350-366).
         float absmax = 0.0f, sumsq = 0.0f;
         for (int i = tig; i < period; i += GROUP) {
-            const float gi = ScalarIO<S>::load(g + i);
+            const float gi = gradient_element(g + i, L);
             if (period1) {
                 const float prev = load_state(v_ptr, start + i, v_dtype);
                 store_state(v_ptr, start + i, v_dtype, fmaf(beta2, prev, (omb2 * gi) * gi));
@@ -605,7 +699,7 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
 
         // pass 2: re-encode and update
         for (int i = tig; i < period; i += GROUP) {
-            const float gi = ScalarIO<S>::load(g + i);
+            const float gi = gradient_element(g + i, L);
             const float cur = old_mag * s.cb[codes[i]];
             const float u = period1 ? ema_update_period1(beta1, cur, omb1, gi) : ema_update(beta1, cur, omb1, gi);
             float x = 0.0f;
@@ -622,7 +716,9 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
                 if (period1) st = adam_step_size(load_state(v_ptr, start + i, v_dtype), bc1, bc2, eps);
                 float pi = ScalarIO<S>::load(prm + i);
                 if (wd) pi = ScalarIO<S>::round(pi * wd_mul);
-                ScalarIO<S>::store(prm + i, fmaf(-(q * st), lr, pi));
+                const float updated = fmaf(-(q * st), lr, pi);
+                ScalarIO<S>::store(prm + i, updated);
+                for (int r = 0; r < L.n_peers; ++r) ScalarIO<S>::store(peer_ptr(prm + i, L.peer_delta[r]), updated);
             }
         }
     }
@@ -679,20 +775,8 @@ static int grid_for(long long groups_needed, int groups_per_cta, int ctas_per_sm
 }
 
 constexpr int kFastMaxPeriod = 8192;
-constexpr int kFastMaxWarps = 16;
 constexpr int kStaticSmemSlack = 256;   // static __shared__ of the kernels (counted against the per-CTA limit)
 constexpr int kCtaReservedSmem = 1024;  // what the hardware sets aside per resident CTA (not part of the limit)
-
-// GEFEN_B200_STEP_STAGED=0/1 in the environment overrides the choice of fast-path variant (for
-// measurements); by default the staged variant is used.
-static int staged_default() {
-    static int cached = -1;
-    if (cached < 0) {
-        const char* e = getenv("GEFEN_B200_STEP_STAGED");
-        cached = (e != nullptr && e[0] == '0') ? 0 : 1;
-    }
-    return cached;
-}
 
 // GEFEN_B200_STEP_WARPS=n caps the warps per CTA of the staged kernel (for measurements).
 static int warps_override() {
@@ -705,27 +789,24 @@ static int warps_override() {
     return cached;
 }
 
-template <typename S, bool STAGED>
+template <typename S, bool REDUCE>
 static int launch_vec_variant(StepLaunch L, const gefen_b200_step_tensor_t& single, long long max_period,
                               cudaStream_t stream) {
     static bool configured[64];
     int dev = 0;
     GEFEN_CHECK_CUDA(cudaGetDevice(&dev));
-    auto kernel = step_vec_kernel<S, STAGED>;
+    auto kernel = step_vec_kernel<S, REDUCE>;
     if (dev < 64 && !configured[dev]) {
         GEFEN_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem - kStaticSmemSlack));
         configured[dev] = true;
     }
     // a warp stages one long block, or the 32 / lanes short blocks (at most 256 elements together) of a unit
-    const long long stage_bytes = STAGED ? (max_period > 256 ? max_period : 256) * 4 : 0;
-    int warps = kFastMaxWarps;
-    if (STAGED) {
-        int max_warps = vec_max_threads<S>() / 32;
-        if (warps_override() > 0 && warps_override() < max_warps) max_warps = warps_override();
-        warps = static_cast<int>((kMaxSmem - kStaticSmemSlack - kSmemWs - kSmemRep) / stage_bytes);
-        if (warps > max_warps) warps = max_warps;
-        if (warps < 1) return fail(GEFEN_B200_EINVAL, "internal: period %lld too large for the staged path", max_period);
-    }
+    const long long stage_bytes = (max_period > 256 ? max_period : 256) * 4;
+    int max_warps = vec_max_threads<S, REDUCE>() / 32;
+    if (warps_override() > 0 && warps_override() < max_warps) max_warps = warps_override();
+    int warps = static_cast<int>((kMaxSmem - kStaticSmemSlack - kSmemWs - kSmemRep) / stage_bytes);
+    if (warps > max_warps) warps = max_warps;
+    if (warps < 1) return fail(GEFEN_B200_EINVAL, "internal: period %lld too large for the staged path", max_period);
     if (L.total_blocks < warps) warps = static_cast<int>(L.total_blocks);
     const int smem = kSmemWs + kSmemRep + static_cast<int>(stage_bytes) * warps;
     int ctas_per_sm = (kMaxSmem + kCtaReservedSmem) / (smem + kStaticSmemSlack + kCtaReservedSmem);
@@ -740,7 +821,7 @@ static int launch_vec_variant(StepLaunch L, const gefen_b200_step_tensor_t& sing
 
 template <typename S>
 static int launch_vec(StepLaunch L, const gefen_b200_step_tensor_t& single, long long max_period, cudaStream_t stream) {
-    if (staged_default()) return launch_vec_variant<S, true>(L, single, max_period, stream);
+    if (L.n_grad_srcs > 0) return launch_vec_variant<S, true>(L, single, max_period, stream);
     return launch_vec_variant<S, false>(L, single, max_period, stream);
 }
 
@@ -826,6 +907,9 @@ static int run_single(gefen_b200_step_tensor_t& t, int param_dtype, const float*
     L.total_blocks = cls >= 1 ? vec_units(t.num_blocks, t.period) : t.num_blocks;
     L.ws = static_cast<const unsigned char*>(ws);
     L.stepsize = stepsize;
+    L.n_peers = 0;
+    L.n_grad_srcs = 0;
+    L.grad_scale = 1.0f;
     return launch_class(cls, param_dtype, L, t, t.period, stream);
 }
 
@@ -1008,7 +1092,26 @@ int gefen_b200_step_tensor_class(const gefen_b200_step_tensor_t* host_entry, int
 
 int gefen_b200_multi_tensor_step(gefen_b200_step_tensor_t* host_table, void* device_table, int n_tensors,
                                  int param_dtype, const void* codebook_ws, void* stream_) {
+    return gefen_b200_multi_tensor_step_peers(host_table, device_table, n_tensors, param_dtype, codebook_ws, nullptr, 0,
+                                              nullptr, 0, 1.0, stream_);
+}
+
+int gefen_b200_multi_tensor_step_peers(gefen_b200_step_tensor_t* host_table, void* device_table, int n_tensors,
+                                       int param_dtype, const void* codebook_ws, const int64_t* peer_deltas,
+                                       int n_peers, const int64_t* grad_deltas, int n_grad_srcs, double grad_scale,
+                                       void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    GEFEN_CHECK_ARG(n_grad_srcs >= 0 && n_grad_srcs <= GEFEN_B200_MAX_PEERS + 1,
+                    "Expected between 0 and %d gradient buffers, got %d.", GEFEN_B200_MAX_PEERS + 1, n_grad_srcs);
+    GEFEN_CHECK_ARG(n_grad_srcs == 0 || grad_deltas != nullptr, "Expected offsets for %d gradient buffers.", n_grad_srcs);
+    for (int r = 0; r < n_grad_srcs; ++r)
+        GEFEN_CHECK_ARG(grad_deltas[r] % 16 == 0, "Gradient buffer offset %d is not a multiple of 16 bytes.", r);
+    GEFEN_CHECK_ARG(n_grad_srcs == 0 || param_dtype != GEFEN_B200_F64, "Gradient averaging supports fp32, fp16 and bf16.");
+    GEFEN_CHECK_ARG(n_peers >= 0 && n_peers <= GEFEN_B200_MAX_PEERS, "Expected between 0 and %d peers, got %d.",
+                    GEFEN_B200_MAX_PEERS, n_peers);
+    GEFEN_CHECK_ARG(n_peers == 0 || peer_deltas != nullptr, "Expected peer offsets for %d peers.", n_peers);
+    for (int r = 0; r < n_peers; ++r)
+        GEFEN_CHECK_ARG(peer_deltas[r] % 16 == 0, "Peer offset %d is not a multiple of 16 bytes.", r);
     GEFEN_CHECK_ARG(n_tensors >= 0, "Expected a non-negative tensor count.");
     if (n_tensors == 0) return GEFEN_B200_OK;
     GEFEN_CHECK_ARG(host_table != nullptr && device_table != nullptr && codebook_ws != nullptr,
@@ -1058,6 +1161,11 @@ int gefen_b200_multi_tensor_step(gefen_b200_step_tensor_t* host_table, void* dev
             L.total_blocks = total;
             L.ws = static_cast<const unsigned char*>(codebook_ws);
             L.stepsize = nullptr;
+            L.n_peers = n_peers;
+            for (int r = 0; r < n_peers; ++r) L.peer_delta[r] = peer_deltas[r];
+            L.n_grad_srcs = n_grad_srcs;
+            L.grad_scale = static_cast<float>(grad_scale);
+            for (int r = 0; r < n_grad_srcs; ++r) L.grad_delta[r] = grad_deltas[r];
             const int rc = launch_class(host_table[begin].reserved_[0], param_dtype, L, host_table[begin], max_period, stream);
             if (rc != GEFEN_B200_OK) return rc;
         }

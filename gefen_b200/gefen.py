@@ -532,10 +532,24 @@ class Gefen(torch.optim.Optimizer):
             rows["g"] = g_ptr
             rows["flags"] = flags
             device = table["device"]
+            # set by a ZeRO-1 wrapper whose parameter and gradient buffers are mapped between the ranks'
+            # GPUs: byte distances to the peers' parameter copies, which the kernels then store to as
+            # well, and to all ranks' gradient buffers, which the kernels then average themselves
+            peers = getattr(self, "_peer_param_deltas", None)
+            grad_srcs = getattr(self, "_grad_src_deltas", None)
             with _lib.device_guard(device):
-                _lib.check(lib.gefen_b200_multi_tensor_step(
-                    rows.ctypes.data, _lib.ptr(table["device_table"]), n, table["tag"], _lib.ptr(ws),
-                    _lib.current_stream(device)))
+                if (peers is not None and len(peers)) or (grad_srcs is not None and len(grad_srcs)):
+                    n_peers = 0 if peers is None else len(peers)
+                    n_srcs = 0 if grad_srcs is None else len(grad_srcs)
+                    _lib.check(lib.gefen_b200_multi_tensor_step_peers(
+                        rows.ctypes.data, _lib.ptr(table["device_table"]), n, table["tag"], _lib.ptr(ws),
+                        peers.ctypes.data if n_peers else None, n_peers,
+                        grad_srcs.ctypes.data if n_srcs else None, n_srcs, float(getattr(self, "_grad_src_scale", 1.0)),
+                        _lib.current_stream(device)))
+                else:
+                    _lib.check(lib.gefen_b200_multi_tensor_step(
+                        rows.ctypes.data, _lib.ptr(table["device_table"]), n, table["tag"], _lib.ptr(ws),
+                        _lib.current_stream(device)))
         for local_p, fused_p in copies:
             local_p.copy_(fused_p)
 

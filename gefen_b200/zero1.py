@@ -3,6 +3,11 @@ the optimizer state of one contiguous segment of a flat layout, and a step is
 
     reduce-scatter(gradients)  ->  Gefen step on the owned segment  ->  all-gather(parameters).
 
+On NCCL the parameter buffers of all ranks are mapped into every process (symmetric memory) and the
+step kernels store each updated parameter into all copies themselves, over NVLink, while they
+compute: the all-gather costs no launch and no second pass over the parameters, only a one-element
+all-reduce as the closing barrier. The gradient reduce-scatter is NCCL's.
+
 The reference has no communication code at all (its only distributed awareness is unwrapping
 DTensor shards, gefen.py:692-706); this module is the exchange step the data-parallel use of the
 optimizer needs. Two properties are kept so that N ranks reproduce one rank bit for bit:
@@ -18,6 +23,7 @@ import math
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 import torch.distributed as dist
 
@@ -173,7 +179,8 @@ class Zero1Gefen:
     """
 
     def __init__(self, named_params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, *, group=None,
-                 ops=None, average_gradients: bool = True):
+                 ops=None, average_gradients: bool = True, fused_all_gather: Optional[bool] = None,
+                 fused_reduce_scatter: Optional[bool] = None):
         self.group = group
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -188,8 +195,21 @@ class Zero1Gefen:
             if p.dtype != self.dtype or p.device != self.device:
                 raise ValueError("Zero1Gefen expects one dtype and device per instance, got {} for {}".format(p.dtype, n))
         self.layout = FlatLayout([tuple(p.shape) for _, p in self.named], self.world)
-        self.flat_param = torch.zeros(self.layout.total, dtype=self.dtype, device=self.device)
-        self.flat_grad = torch.zeros(self.layout.total, dtype=self.dtype, device=self.device)
+        self._token = None
+        self.flat_param, param_ptrs = self._allocate_flat(fused_all_gather, "GEFEN_B200_ZERO1_FUSED_AG", "all_gather")
+        # off unless asked for: a rank's step kernel then reads its gradients from every peer with
+        # plain loads, and NVLink's load latency leaves it slower than NCCL's reduce-scatter followed
+        # by the local kernel (measured on two B200s: 5.0 ms against 3.2 + 1.6 ms... with the
+        # all-gather fused in both cases the totals are 5.1 and 5.7 ms, but it does not scale to more
+        # sources per element); kept for its exactness property (fp32 sum in rank order)
+        self.flat_grad, grad_ptrs = self._allocate_flat(fused_reduce_scatter, "GEFEN_B200_ZERO1_FUSED_RS",
+                                                        "reduce_scatter", default="0")
+        # peers in ring order starting after this rank, so that concurrent ranks write to different GPUs
+        self._peer_deltas = None if param_ptrs is None else np.array(
+            [param_ptrs[(self.rank + k) % self.world] - param_ptrs[self.rank] for k in range(1, self.world)], dtype=np.int64)
+        # gradient buffers in rank order: the same summation order on every rank
+        self._grad_deltas = None if grad_ptrs is None else np.array(
+            [grad_ptrs[r] - grad_ptrs[self.rank] for r in range(self.world)], dtype=np.int64)
         with torch.no_grad():
             for t, (n, p) in enumerate(self.named):
                 off = self.layout.tensor_offset[t]
@@ -216,16 +236,94 @@ class Zero1Gefen:
             named_pieces.append(("{}#{}".format(self.named[pc.tensor][0], pc.row0), prm))
         self.local = self.ops.make_optimizer(named_pieces, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay) \
             if named_pieces else None
+        if self.local is not None and self._peer_deltas is not None:
+            self.local._peer_param_deltas = self._peer_deltas
         self.period_mismatches: List[Tuple[str, Dict[int, int]]] = []
         self._events = None
         self._calibrated = False
+
+    # ------------------------------------------------------------------ flat buffers
+    def _allocate_flat(self, requested: Optional[bool], env_name: str, what: str, default: str = "1"):
+        """One flat buffer of the layout's size. With NCCL and more than one rank it is symmetric memory
+        mapped into every rank, so that the step kernels can do the collective themselves
+        (`gefen_b200_multi_tensor_step_peers`): store each updated parameter into all copies
+        (no all-gather afterwards), read each gradient from all copies (no reduce-scatter before).
+        Returns (buffer, every rank's address of it or None). `requested=False`, or the environment
+        variable set to 0, keeps the NCCL collective; so does a failed mapping on any rank (the reason
+        is kept in `fused_errors[what]`)."""
+        import os
+
+        if not hasattr(self, "fused_errors"):
+            self.fused_errors = {}
+        want = requested
+        if want is None:
+            want = os.environ.get(env_name, default) != "0"
+        usable = (want and self.world > 1 and self.world - 1 <= 7 and self.device.type == "cuda"
+                  and self._backend() == "nccl" and self.dtype != torch.float64)
+        if not usable:
+            return torch.zeros(self.layout.total, dtype=self.dtype, device=self.device), None
+        buf, ptrs = None, None
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            group = self.group if self.group is not None else dist.group.WORLD
+            buf = symm_mem.empty(self.layout.total, dtype=self.dtype, device=self.device)
+            handle = symm_mem.rendezvous(buf, group)
+            ptrs = [int(x) for x in handle.buffer_ptrs]
+            if ptrs[self.rank] != buf.data_ptr():
+                raise RuntimeError("symmetric buffer is not at the address the mapping reports")
+            if any((x - ptrs[self.rank]) % 16 for x in ptrs):
+                raise RuntimeError("peer buffers are not 16-byte congruent")
+            setattr(self, "_symm_handle_" + what, handle)   # keeps the mapping alive
+            buf.zero_()
+        except Exception as exc:  # mapping is a property of the machine: fall back to the collective
+            self.fused_errors[what] = "{}: {}".format(type(exc).__name__, exc)
+            buf, ptrs = None, None
+        ok = [None] * self.world
+        dist.all_gather_object(ok, ptrs is not None, group=self.group)
+        if not all(ok):
+            self.fused_errors.setdefault(what, "another rank could not map its buffer")
+            return torch.zeros(self.layout.total, dtype=self.dtype, device=self.device), None
+        if self._token is None:
+            self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
+        return buf, ptrs
+
+    @property
+    def fused_all_gather_error(self):
+        return self.fused_errors.get("all_gather")
+
+    @property
+    def reduce_scatter_mode(self) -> str:
+        if self.world == 1:
+            return "none"
+        return "peer loads in the step kernels" if self._grad_deltas is not None else "nccl reduce_scatter"
+
+    @property
+    def all_gather_mode(self) -> str:
+        if self.world == 1:
+            return "none"
+        return "peer stores from the step kernels" if self._peer_deltas is not None else "nccl all_gather"
 
     # ------------------------------------------------------------------ collectives
     def _backend(self) -> str:
         return dist.get_backend(self.group) if dist.is_initialized() else "none"
 
+    def _rank_barrier(self) -> None:
+        """Orders the ranks' streams: a one-element all-reduce completes on a rank only after every
+        rank's earlier work on its stream has."""
+        dist.all_reduce(self._token, group=self.group)
+
     def _reduce_scatter(self) -> None:
         if self.world == 1:
+            return
+        fused = self._grad_deltas is not None and self._calibrated
+        if self.local is not None:
+            # the calibration step needs the averaged gradients in memory (periods, histogram), so it
+            # uses the collective; afterwards the step kernels average while they read
+            self.local._grad_src_deltas = self._grad_deltas if fused else None
+            self.local._grad_src_scale = (1.0 / self.world) if self.average else 1.0
+        if fused:
+            self._rank_barrier()   # every rank's gradients are final, nobody still reads old parameters
             return
         if self._backend() == "nccl":
             op = dist.ReduceOp.AVG if self.average else dist.ReduceOp.SUM
@@ -238,6 +336,14 @@ class Zero1Gefen:
     def _all_gather(self) -> None:
         if self.world == 1:
             return
+        if self._peer_deltas is not None:
+            # the kernels have already written every copy; what is left is the ordering: a rank may
+            # use its parameters only after all ranks' launches have finished (a one-element
+            # all-reduce on the same stream is that barrier)
+            self._rank_barrier()
+            return
+        # (with fused gradient averaging and this collective, the collective is also what tells a
+        # rank that the peers have finished reading its gradients)
         if self._backend() == "nccl":
             dist.all_gather_into_tensor(self.flat_param, self.my_param, group=self.group)
         else:

@@ -137,9 +137,32 @@ typedef struct gefen_b200_step_tensor {
     int32_t reserved_[2];
 } gefen_b200_step_tensor_t;
 
+#define GEFEN_B200_MAX_PEERS 7
+
 int gefen_b200_multi_tensor_step(gefen_b200_step_tensor_t* host_table, void* device_table,
                                  int n_tensors, int param_dtype, const void* codebook_ws,
                                  void* stream);
+/* The same launch for a rank of a ZeRO-1 group whose parameter (and gradient) buffers, one per GPU,
+ * are all mapped into this process (peer access). Two collectives ride on the kernel's own
+ * accesses over NVLink:
+ *  - all-gather: every updated parameter is stored to this GPU's buffer and to the same position of
+ *    `n_peers` (<= GEFEN_B200_MAX_PEERS) other buffers; peer_deltas[r] = (peer r's parameter buffer
+ *    base) - (this GPU's) in bytes, multiples of 16. Nothing is loaded from a peer for this.
+ *  - reduce-scatter (n_grad_srcs > 0): the gradient of an element is grad_scale * (sum over the
+ *    n_grad_srcs (<= GEFEN_B200_MAX_PEERS + 1) gradient buffers, fp32, in the order given: use rank
+ *    order, with 0 for this rank's own buffer), rounded to the gradient dtype; grad_deltas[r] =
+ *    (rank r's gradient buffer base) - (this GPU's) in bytes. The local gradient buffer is not
+ *    modified. Not with GEFEN_B200_F64.
+ * The caller orders the ranks with a barrier or collective on the same stream before the launch
+ * (every rank's gradients are final and nobody still reads the old parameters) and after it (all
+ * launches have finished: parameters complete, gradients free to be overwritten). The dense
+ * momentum written with GEFEN_B200_STEP_MUON stays local. No counterpart in the reference, which
+ * has no collective (gefen.py:1208-1333 runs per process). */
+int gefen_b200_multi_tensor_step_peers(gefen_b200_step_tensor_t* host_table, void* device_table,
+                                       int n_tensors, int param_dtype, const void* codebook_ws,
+                                       const int64_t* peer_deltas, int n_peers,
+                                       const int64_t* grad_deltas, int n_grad_srcs, double grad_scale,
+                                       void* stream);
 /* sizeof(gefen_b200_step_tensor_t) as compiled, for binding-side layout checks. */
 int gefen_b200_step_tensor_size(void);
 /* Kernel class the library would use for one table entry: 1..8 = vectorised path with that many

@@ -1,0 +1,88 @@
+"""ZeRO-1 on two GPUs of one machine. The step with the all-gather fused into the kernels (peer
+stores into the other rank's parameter buffer) must leave every rank with exactly the parameters
+that the NCCL all-gather leaves; with the reduce-scatter fused in as well (peer loads of the other
+rank's gradients) it must equal a run that is fed the rank-order fp32 mean of the gradients.
+Skipped with fewer than two GPUs."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
+    import torch.distributed as dist
+
+    from gefen_b200.zero1 import Zero1Gefen
+    from tests.util import make_grad, make_param
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dev = torch.device("cuda", rank)
+    shapes = [(96, 512), (64, 2048), (2048,), (40, 768), (33, 24), (7,), (128, 1024)]
+
+    def grad_of(r, i, s, step):
+        return make_grad(s, 5 + r, i, step, torch.bfloat16)
+
+    def averaged(i, s, step):   # what the fused reduce-scatter computes: fp32 sum in rank order, scaled, rounded
+        acc = torch.zeros(s, dtype=torch.float32)
+        for r in range(world):
+            acc += grad_of(r, i, s, step).float()
+        return (acc * (1.0 / world)).to(torch.bfloat16)
+
+    results = {}
+    # own gradients + NCCL / own gradients + fused all-gather / pre-averaged gradients + fused all-gather /
+    # own gradients + both collectives fused
+    for name, fused_ag, fused_rs, pre_averaged in (("nccl", False, False, False), ("fused_ag", True, False, False),
+                                                   ("averaged_inputs", True, False, True), ("fused_both", True, True, False)):
+        params = [torch.nn.Parameter(make_param(s, 5, i, torch.bfloat16).to(dev)) for i, s in enumerate(shapes)]
+        named = [("p{}".format(i), p) for i, p in enumerate(params)]
+        for i, (p, s) in enumerate(zip(params, shapes)):
+            p.grad = torch.zeros(s, dtype=torch.bfloat16, device=dev)
+        opt = Zero1Gefen(named, lr=1e-3, weight_decay=0.1, fused_all_gather=fused_ag, fused_reduce_scatter=fused_rs)
+        for step in range(4):
+            for i, (p, s) in enumerate(zip(params, shapes)):
+                g = averaged(i, s, step) if pre_averaged else grad_of(rank, i, s, step)
+                p.grad.copy_(g.to(dev))
+            opt.step()
+        torch.cuda.synchronize()
+        results[name] = (opt.all_gather_mode, opt.reduce_scatter_mode, dict(opt.fused_errors),
+                         opt.flat_param.detach().cpu().clone())
+    torch.save(results, os.path.join(out_dir, "rank{}.pt".format(rank)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_collectives_equal_nccl_collectives(tmp_path):
+    import torch.multiprocessing as mp
+
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    ranks = [torch.load(tmp_path / "rank{}.pt".format(r), weights_only=False) for r in range(world)]
+    for r in range(world):
+        res = ranks[r]
+        assert res["nccl"][:2] == ("nccl all_gather", "nccl reduce_scatter")
+        assert res["fused_ag"][:2] == ("peer stores from the step kernels", "nccl reduce_scatter"), res["fused_ag"][2]
+        assert res["fused_both"][:2] == ("peer stores from the step kernels", "peer loads in the step kernels"), \
+            res["fused_both"][2]
+        # the all-gather done by the kernels' peer stores leaves what NCCL's leaves
+        assert torch.equal(res["fused_ag"][3], res["nccl"][3])
+        # the average done by the kernels' peer loads is the fp32 rank-order mean rounded to bf16
+        assert torch.equal(res["fused_both"][3], res["averaged_inputs"][3])
+        # and it is close to NCCL's own bf16 average
+        assert (res["fused_both"][3].float() - res["nccl"][3].float()).abs().max() < 1e-2
+    for name in ("nccl", "fused_ag", "fused_both"):
+        assert torch.equal(ranks[0][name][3], ranks[1][name][3]), name
+    assert float(ranks[0]["fused_both"][3].float().abs().sum()) > 0
