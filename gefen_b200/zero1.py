@@ -197,11 +197,10 @@ class Zero1Gefen:
         self.layout = FlatLayout([tuple(p.shape) for _, p in self.named], self.world)
         self._token = None
         self.flat_param, param_ptrs = self._allocate_flat(fused_all_gather, "GEFEN_B200_ZERO1_FUSED_AG", "all_gather")
-        # off unless asked for: a rank's step kernel then reads its gradients from every peer with
-        # plain loads, and NVLink's load latency leaves it slower than NCCL's reduce-scatter followed
-        # by the local kernel (measured on two B200s: 5.0 ms against 3.2 + 1.6 ms... with the
-        # all-gather fused in both cases the totals are 5.1 and 5.7 ms, but it does not scale to more
-        # sources per element); kept for its exactness property (fp32 sum in rank order)
+        # Off unless asked for. With it a rank's step kernel reads its gradients from every peer with
+        # plain loads; NVLink's load latency then bounds the kernel (two B200s, 1.5 G parameters: one
+        # 5.0 ms kernel, against 3.2 ms of NCCL reduce-scatter plus a 2.5 ms kernel), and it gets
+        # worse with more sources per element. Kept for its exactness: fp32 sum in rank order.
         self.flat_grad, grad_ptrs = self._allocate_flat(fused_reduce_scatter, "GEFEN_B200_ZERO1_FUSED_RS",
                                                         "reduce_scatter", default="0")
         # peers in ring order starting after this rank, so that concurrent ranks write to different GPUs
