@@ -248,6 +248,43 @@ __device__ __forceinline__ float group_sum(float v, int lanes) {
     return v;
 }
 
+// First pass over U chunks of one lane (chunks c0, c0 + LANES, ...): all loads first, then the
+// moment update, the running absmax and sum of squares, and the staging of the updated momenta.
+template <typename S, int U, bool GUARD>
+__device__ __forceinline__ void first_pass_group(const S* g_blk, const uint2* codes_in, float4* stage_a, float4* stage_b,
+                                                 const float* rep, int c0, int LANES, int nchunks, float old_mag,
+                                                 float beta1, float omb1, float& absmax, float& sumsq) {
+    uint2 craw[U];
+    Chunk<S> graw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int c = c0 + LANES * u;
+        if (!GUARD || c < nchunks) {
+            craw[u] = codes_in[c];
+            graw[u].load(g_blk, c);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int c = c0 + LANES * u;
+        if (!GUARD || c < nchunks) {
+            float g[8], m[8];
+            graw[u].unpack(g);
+            const uint32_t cw[2] = {craw[u].x, craw[u].y};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t code = (cw[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+                const float cur = old_mag * rep[code * kRepCopies];
+                m[i] = ema_update(beta1, cur, omb1, g[i]);
+                absmax = max_abs_nan(absmax, m[i]);
+                sumsq = fmaf(g[i], g[i], sumsq);
+            }
+            stage_a[c] = make_float4(m[0], m[1], m[2], m[3]);
+            stage_b[c] = make_float4(m[4], m[5], m[6], m[7]);
+        }
+    }
+}
+
 // First pass of a block whose gradient is averaged over up to NSRC buffers. kSlots 16-byte (fp32:
 // 32-byte) loads per lane are in flight at a time: U chunks x a batch of BS sources; the sources of
 // a chunk are added batch after batch, in the order given.
@@ -380,37 +417,14 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
         else reduce_pass<S, 8>(L, g_blk, codes_in, stage_a, stage_b, rep, lane, LANES, nchunks, old_mag, beta1, omb1, absmax, sumsq);
     } else {
         constexpr int U = FULL ? 4 : 1;  // chunks in flight per lane (short blocks: one chunk per lane)
-        for (int c0 = lane; c0 < nchunks; c0 += LANES * U) {
-            uint2 craw[U];
-            Chunk<S> graw[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int c = c0 + LANES * u;
-                if (c < nchunks) {
-                    craw[u] = codes_in[c];
-                    graw[u].load(g_blk, c);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int c = c0 + LANES * u;
-                if (c < nchunks) {
-                    float g[8], m[8];
-                    graw[u].unpack(g);
-                    const uint32_t cw[2] = {craw[u].x, craw[u].y};
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const uint32_t code = (cw[i >> 2] >> (8 * (i & 3))) & 0xFFu;
-                        const float cur = old_mag * rep[code * kRepCopies];
-                        m[i] = ema_update(beta1, cur, omb1, g[i]);
-                        absmax = max_abs_nan(absmax, m[i]);
-                        sumsq = fmaf(g[i], g[i], sumsq);
-                    }
-                    stage_a[c] = make_float4(m[0], m[1], m[2], m[3]);
-                    stage_b[c] = make_float4(m[4], m[5], m[6], m[7]);
-                }
-            }
-        }
+        // groups of U chunks per lane that are complete for every lane run without bounds tests
+        const int whole = FULL ? (nchunks / (32 * U)) * (32 * U) : 0;
+        for (int c0 = lane; c0 < whole; c0 += 32 * U)
+            first_pass_group<S, U, false>(g_blk, codes_in, stage_a, stage_b, rep, c0, LANES, nchunks, old_mag, beta1, omb1,
+                                          absmax, sumsq);
+        for (int c0 = whole + lane; c0 < nchunks; c0 += LANES * U)
+            first_pass_group<S, U, true>(g_blk, codes_in, stage_a, stage_b, rep, c0, LANES, nchunks, old_mag, beta1, omb1,
+                                         absmax, sumsq);
     }
     absmax = group_max_nan(absmax, LANES);
 

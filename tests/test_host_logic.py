@@ -133,7 +133,7 @@ def test_flat_layout_invariants():
     from gefen_b200 import workloads
     from gefen_b200.zero1 import FlatLayout
 
-    for fn in (workloads.llama_1_5b, workloads.gpt2_125m, workloads.qwen3_1_7b_matrices):
+    for fn in (workloads.llama_1_5b, workloads.gpt2_125m, workloads.qwen3_1_7b_matrices, workloads.llama_32b):
         shapes = [s for _, s in fn()]
         total = sum(workloads.numel(s) for s in shapes)
         for world in (1, 2, 3, 4, 8):
