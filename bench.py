@@ -277,21 +277,20 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     result["launches_per_step"] = len(set(cls))
 
     # ---- end to end through the public API with HOST buffers: gradients come from pinned host
-    # memory every step and the updated parameters go back to pinned host memory.
+    # memory every step and the updated parameters go back to pinned host memory
+    # (gefen_b200.HostStreamedGefen: the same step, bucket by bucket, copies overlapped both ways).
     e2e = None
     if not args.no_e2e:
+        from gefen_b200.host_stream import HostStreamedGefen
+
         host_g = [torch.empty(g.shape, dtype=g.dtype, pin_memory=True) for g in grads]
         host_p = [torch.empty(p.shape, dtype=p.dtype, pin_memory=True) for p in params]
         for h, g in zip(host_g, grads):
             h.copy_(g)
-        dev_g = [p.grad for _, p in named]
+        streamed = HostStreamedGefen(opt, host_g, host_p, buckets=args.e2e_buckets)
 
         def e2e_step():
-            for d, h in zip(dev_g, host_g):
-                d.copy_(h, non_blocking=True)
-            step()
-            for h, (_, p) in zip(host_p, named):
-                h.copy_(p.detach(), non_blocking=True)
+            streamed.step()
 
         e2e_step()
         e2e_ms = timed(e2e_step, max(2, min(args.steps, 5)))
@@ -474,6 +473,7 @@ def main():
     ap.add_argument("--cpu-sample-elems", type=int, default=62_000_000,
                     help="size of the CPU baseline's sample of the workload, in elements")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--e2e-buckets", type=int, default=8)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--microbench", default=None, help="dtype:period:blocks, single-tensor step kernel only")
     args = ap.parse_args()

@@ -20,6 +20,9 @@
 // roles drain, TMEM is released and the kernel returns.
 #include "common.cuh"
 
+#include <stdio.h>
+#include <stdlib.h>
+
 #include <cuda.h>
 #include <mutex>
 
@@ -111,8 +114,10 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 // (MN-major operand), i.e. D = alpha * A * B + beta * C without any transposed copy of B.
 // A_MN: likewise A given as [K, M] row-major (D = alpha * A^T * B ...), used for the Gram matrix of a
 // tall matrix, Y^T Y, without transposing Y.
+// Variants whose ring is at most 96 KB run two CTAs per SM: the epilogue of one overlaps the main
+// loop of the other (each holds BN <= 256 of the 512 TMEM columns).
 template <int BN, int STAGES, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(kGemmThreads, 1) ns_gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a,
+__global__ void __launch_bounds__(kGemmThreads, (STAGES * (kBM + BN) * kBK * 2 <= 96 * 1024) ? 2 : 1) ns_gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                      const __grid_constant__ CUtensorMap map_b,
                                                                      const __grid_constant__ GemmArgs args) {
     constexpr int kABytes = kBM * kBK * 2;
@@ -407,7 +412,16 @@ static int ns_gemm(const void* a, bool a_is_km, const void* b, bool b_is_kn, con
     // 128 x 256 tiles have the better arithmetic intensity; 128 x 128 tiles are used for small problems
     // that would leave most SMs without a tile (measured: for 2048-wide outputs the wider tile wins
     // even when a symmetric result computes only 72 of them)
-    const int bn = (N >= 2048 || (static_cast<long long>((M + 127) / 128) * ((N + 255) / 256)) >= sm_count()) ? 256 : 128;
+    int bn = (N >= 2048 || (static_cast<long long>((M + 127) / 128) * ((N + 255) / 256)) >= sm_count()) ? 256 : 128;
+    // GEFEN_B200_NS_TILE=<bn>x<stages> picks a variant by hand (measurements): 256x4, 256x2, 128x6, 128x3
+    static int forced_bn = -1, forced_stages = 0;
+    if (forced_bn < 0) {
+        forced_bn = 0;
+        const char* e = getenv("GEFEN_B200_NS_TILE");
+        if (e != nullptr) sscanf(e, "%dx%d", &forced_bn, &forced_stages);
+    }
+    if (forced_bn == 256 || forced_bn == 128) bn = forced_bn;
+    const bool shallow = forced_stages == 2 || forced_stages == 3;
     CUtensorMap ma, mb;
     int rc = a_is_km ? make_map(&ma, a, K, M, lda, kBK) : make_map(&ma, a, M, K, lda, kBM);
     if (rc != GEFEN_B200_OK) return rc;
@@ -424,14 +438,20 @@ static int ns_gemm(const void* a, bool a_is_km, const void* b, bool b_is_kn, con
     args.symmetric = symmetric;
     args.status = status;
     if (a_is_km && b_is_kn) {
+        if (shallow) return bn == 256 ? launch_gemm<256, 2, true, true>(ma, mb, args, stream)
+                                      : launch_gemm<128, 3, true, true>(ma, mb, args, stream);
         if (bn == 256) return launch_gemm<256, 4, true, true>(ma, mb, args, stream);
         return launch_gemm<128, 6, true, true>(ma, mb, args, stream);
     }
     if (a_is_km) return fail(GEFEN_B200_EUNSUPPORTED, "A given as [K, M] is only combined with B given as [K, N].");
     if (b_is_kn) {
+        if (shallow) return bn == 256 ? launch_gemm<256, 2, false, true>(ma, mb, args, stream)
+                                      : launch_gemm<128, 3, false, true>(ma, mb, args, stream);
         if (bn == 256) return launch_gemm<256, 4, false, true>(ma, mb, args, stream);
         return launch_gemm<128, 6, false, true>(ma, mb, args, stream);
     }
+    if (shallow) return bn == 256 ? launch_gemm<256, 2, false, false>(ma, mb, args, stream)
+                                  : launch_gemm<128, 3, false, false>(ma, mb, args, stream);
     if (bn == 256) return launch_gemm<256, 4, false, false>(ma, mb, args, stream);
     return launch_gemm<128, 6, false, false>(ma, mb, args, stream);
 }

@@ -198,6 +198,7 @@ class Gefen(torch.optim.Optimizer):
         self._gefen_codebook = None
         self._gefen_global_step = 0
         self._plan = _StepPlan()
+        self._plans = {}
         if verbose:
             print("Initializing Gefen optimizer (fused={}).".format(self.fused))
         super().__init__(groups, dict(lr=lr, beta1=betas[0], beta2=betas[1], eps=eps))
@@ -431,9 +432,13 @@ class Gefen(torch.optim.Optimizer):
         """Builds (or reuses) the launch tables for `work`. Static columns are cached; the pointer
         and scalar columns are refreshed by the caller every step."""
         key = (muon,) + tuple(id(item[2]) for item in work)
-        plan = self._plan
-        if plan.key == key:
+        plan = self._plans.get(key)
+        if plan is not None:
+            self._plan = plan
             return plan.tables
+        if len(self._plans) >= 64:   # callers that keep changing the set of tensors: start over
+            self._plans.clear()
+        plan = self._plans[key] = self._plan = _StepPlan()
         lib = _lib.load()
         by_dtype = {}
         for idx, (group, name, p, local_p, grad) in enumerate(work):
@@ -486,8 +491,12 @@ class Gefen(torch.optim.Optimizer):
         plan.tables = tables
         return tables
 
-    def _step_multi_tensor(self) -> None:
+    def _step_multi_tensor(self, only=None) -> None:
+        """One multi-tensor launch per dtype and kernel class over every parameter with a gradient,
+        or over those whose id() is in `only` (callers that stream the model through in pieces)."""
         work = self._collect()
+        if only is not None:
+            work = [item for item in work if id(item[2]) in only]
         if not work:
             return
         if self._gefen_codebook is None:
@@ -575,6 +584,7 @@ class Gefen(torch.optim.Optimizer):
         self._gefen_global_step = global_step
         self._gefen_codebook = codebook
         self._plan = _StepPlan()
+        self._plans = {}
         id_map = dict(zip(chain.from_iterable(g["params"] for g in state_dict["param_groups"]),
                           chain.from_iterable(g["params"] for g in self.param_groups)))
         for param_id, saved in saved_state.items():

@@ -146,3 +146,38 @@ def test_loads_a_checkpoint_written_by_the_reference(cuda_device):
     # and back: the reference's loader only needs the same keys
     sd = opt.state_dict()
     assert set(sd["state"][0]) == set(ck["state_dict"]["state"][0])
+
+
+def test_host_streamed_step_equals_plain_step(cuda_device):
+    """Gradients from pinned host memory, parameters back to pinned host memory, bucket by bucket on
+    three streams: same results as copying everything, stepping, copying everything back."""
+    from gefen_b200 import Gefen, HostStreamedGefen
+
+    shapes = [(64, 512), (2048,), (96, 768), (40, 2048), (33, 24), (128, 1024), (7,), (256, 256)]
+
+    def build():
+        params = [torch.nn.Parameter(make_param(s, 3, i, torch.bfloat16).to(cuda_device)) for i, s in enumerate(shapes)]
+        for p in params:
+            p.grad = torch.zeros_like(p)
+        return params, Gefen([("p{}".format(i), p) for i, p in enumerate(params)], lr=1e-3, weight_decay=0.1)
+
+    plain_params, plain = build()
+    stream_params, streamed_opt = build()
+    host_g = [torch.empty(s, dtype=torch.bfloat16).pin_memory() for s in shapes]
+    host_p = [torch.empty(s, dtype=torch.bfloat16).pin_memory() for s in shapes]
+    streamed = HostStreamedGefen(streamed_opt, host_g, host_p, buckets=3)
+    assert len(streamed.buckets) == 3 and sorted(i for b in streamed.buckets for i in b) == list(range(len(shapes)))
+    for step in range(4):
+        grads = [make_grad(s, 3, i, step, torch.bfloat16) for i, s in enumerate(shapes)]
+        for p, g, h in zip(plain_params, grads, host_g):
+            p.grad.copy_(g.to(cuda_device))
+            h.copy_(g)
+        plain.step()
+        streamed.step()
+        torch.cuda.synchronize()
+        for p, q, h in zip(plain_params, stream_params, host_p):
+            assert torch.equal(p.detach(), q.detach())
+            assert torch.equal(h, p.detach().cpu())
+    for p, q in zip(plain_params, stream_params):
+        assert torch.equal(plain.state[p]["m_codebook"], streamed_opt.state[q]["m_codebook"])
+    assert plain._gefen_global_step == streamed_opt._gefen_global_step == 4
