@@ -417,12 +417,9 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
         else reduce_pass<S, 8>(L, g_blk, codes_in, stage_a, stage_b, rep, lane, LANES, nchunks, old_mag, beta1, omb1, absmax, sumsq);
     } else {
         constexpr int U = FULL ? 4 : 1;  // chunks in flight per lane (short blocks: one chunk per lane)
-        // groups of U chunks per lane that are complete for every lane run without bounds tests
-        const int whole = FULL ? (nchunks / (32 * U)) * (32 * U) : 0;
-        for (int c0 = lane; c0 < whole; c0 += 32 * U)
-            first_pass_group<S, U, false>(g_blk, codes_in, stage_a, stage_b, rep, c0, LANES, nchunks, old_mag, beta1, omb1,
-                                          absmax, sumsq);
-        for (int c0 = whole + lane; c0 < nchunks; c0 += LANES * U)
+        // (a separate loop without bounds tests for the complete groups was measured: slower, it
+        // costs registers)
+        for (int c0 = lane; c0 < nchunks; c0 += LANES * U)
             first_pass_group<S, U, true>(g_blk, codes_in, stage_a, stage_b, rep, c0, LANES, nchunks, old_mag, beta1, omb1,
                                          absmax, sumsq);
     }
