@@ -10,7 +10,9 @@
 //     Bm = b*G + c*G*G         A = B = C = G      (G is symmetric, so G*G = G*G^T)
 //     X' = a*X + Bm*X          A = Bm, B = X^T, C = X, Dt receives X'^T for the next iteration
 //
-// Structure (one 128 x BN output tile per CTA, 6 warps):
+// Structure (128 x BN output tiles, 6 warps; one tile per CTA, or - PERSIST - one CTA per SM that
+// walks over tiles with two accumulator buffers in TMEM, so that the epilogue of a tile runs while
+// the tensor cores already work on the next one):
 //   warp 4  : TMA producer. cp.async.bulk.tensor 2-D loads of 128x64 (A) and BNx64 (B) bf16 boxes,
 //             128-byte swizzle, into a STAGES-deep shared-memory ring, completion on mbarriers.
 //   warp 5  : allocates TMEM and issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=BN, K=16)
@@ -40,6 +42,7 @@ struct GemmArgs {
     int M, N, K;
     long long ldc, ldd, lddt;
     float alpha, beta;
+    int n_tiles;     // PERSIST: number of tiles to compute (see tile_coords)
     int symmetric;   // the result is known to be symmetric (M == N): compute the tiles that touch the upper
                      // triangle only and write every element above the diagonal to its mirror position too
     int* status;
@@ -110,13 +113,41 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Tile t of the persistent schedule: row-major over the tiles that are computed (all of them, or for
+// a symmetric result those that reach the upper triangle: n0 + bn > m0).
+__host__ __device__ inline bool tile_coords(int M, int N, int bn, int symmetric, long long t, int* m0, int* n0) {
+    const int tiles_m = (M + kBM - 1) / kBM, tiles_n = (N + bn - 1) / bn;
+    if (!symmetric) {
+        if (t >= static_cast<long long>(tiles_m) * tiles_n) return false;
+        *m0 = static_cast<int>(t / tiles_n) * kBM;
+        *n0 = static_cast<int>(t % tiles_n) * bn;
+        return true;
+    }
+    for (int mi = 0; mi < tiles_m; ++mi) {
+        const int row0 = mi * kBM;
+        const int first = row0 >= bn ? (row0 - bn) / bn + 1 : 0;
+        const int cnt = tiles_n - first;
+        if (t < cnt) {
+            *m0 = row0;
+            *n0 = (first + static_cast<int>(t)) * bn;
+            return true;
+        }
+        t -= cnt;
+    }
+    return false;
+}
+
 // B_MN = false: B is [N, K] row-major (K-major operand). B_MN = true: B is [K, N] row-major
 // (MN-major operand), i.e. D = alpha * A * B + beta * C without any transposed copy of B.
 // A_MN: likewise A given as [K, M] row-major (D = alpha * A^T * B ...), used for the Gram matrix of a
 // tall matrix, Y^T Y, without transposing Y.
 // Variants whose ring is at most 96 KB run two CTAs per SM: the epilogue of one overlaps the main
 // loop of the other (each holds BN <= 256 of the 512 TMEM columns).
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool PERSIST>
 __global__ void __launch_bounds__(kGemmThreads, (STAGES * (kBM + BN) * kBK * 2 <= 96 * 1024) ? 2 : 1) ns_gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                      const __grid_constant__ CUtensorMap map_b,
                                                                      const __grid_constant__ GemmArgs args) {
@@ -127,25 +158,36 @@ __global__ void __launch_bounds__(kGemmThreads, (STAGES * (kBM + BN) * kBK * 2 <
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     __shared__ uint64_t full_bar[STAGES];
     __shared__ uint64_t empty_bar[STAGES];
-    __shared__ uint64_t acc_bar;
+    __shared__ uint64_t acc_full[2];    // accumulator buffer complete (MMA -> epilogue)
+    __shared__ uint64_t acc_empty[2];   // accumulator buffer drained (4 epilogue warps -> MMA); PERSIST only
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * kBM;
-    const int n0 = blockIdx.x * BN;
+    constexpr int kTmemCols = PERSIST ? 2 * BN : BN;
     const int k_blocks = (args.K + kBK - 1) / kBK;
-    if (args.symmetric && n0 + BN <= m0) return;   // tile entirely below the diagonal: its mirror image computes it
+    if (!PERSIST && args.symmetric && static_cast<int>(blockIdx.x) * BN + BN <= static_cast<int>(blockIdx.y) * kBM)
+        return;   // tile entirely below the diagonal: its mirror image computes it
+    // li-th tile of this CTA
+    auto my_tile = [&](int li, int* m0, int* n0) -> bool {
+        if (!PERSIST) {
+            *m0 = blockIdx.y * kBM;
+            *n0 = blockIdx.x * BN;
+            return li == 0;
+        }
+        const long long t = static_cast<long long>(blockIdx.x) + static_cast<long long>(li) * gridDim.x;
+        return t < args.n_tiles && tile_coords(args.M, args.N, BN, args.symmetric, t, m0, n0);
+    };
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        mbar_init(&acc_bar, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
         fence_mbar_init();
     }
     if (warp == 5) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -158,10 +200,14 @@ __global__ void __launch_bounds__(kGemmThreads, (STAGES * (kBM + BN) * kBK * 2 <
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t parity = ((kb / STAGES) & 1) ^ 1;
-                if (!wait_or_abort(&empty_bar[s], parity, &abort_flag)) break;
+            uint32_t it = 0;   // k-blocks issued so far, over all tiles: ring slot and phase
+            bool ok = true;
+            int m0, n0;
+            for (int li = 0; ok && my_tile(li, &m0, &n0); ++li)
+            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t parity = ((it / STAGES) & 1) ^ 1;
+                if (!wait_or_abort(&empty_bar[s], parity, &abort_flag)) { ok = false; break; }
                 mbar_expect_tx(&full_bar[s], kStageBytes);
                 unsigned char* a_dst = smem + s * kStageBytes;
                 if (!A_MN) {
@@ -188,9 +234,19 @@ __global__ void __launch_bounds__(kGemmThreads, (STAGES * (kBM + BN) * kBK * 2 <
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (A_MN ? (1u << 15) : 0u) | (B_MN ? (1u << 16) : 0u) |
                                        (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
             bool ok = true;
-            for (int kb = 0; kb < k_blocks && ok; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t parity = (kb / STAGES) & 1;
+            uint32_t it = 0;
+            int m0, n0;
+            for (int li = 0; ok && my_tile(li, &m0, &n0); ++li) {
+            const int buf = PERSIST ? (li & 1) : 0;
+            const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(buf * BN);
+            if (PERSIST) {   // the epilogue has drained this buffer (passes at once for the first two tiles)
+                ok = wait_or_abort(&acc_empty[buf], ((li >> 1) & 1) ^ 1, &abort_flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t parity = (it / STAGES) & 1;
                 ok = wait_or_abort(&full_bar[s], parity, &abort_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -202,15 +258,19 @@ __global__ void __launch_bounds__(kGemmThreads, (STAGES * (kBM + BN) * kBK * 2 <
                 for (int k = 0; k < kBK / 16; ++k) {
                     // K-major: 16 bf16 along K = 32 bytes inside the swizzle row (+2 in the address field);
                     // MN-major: 16 K-rows of 128 bytes = 2048 bytes (+128)
-                    umma_bf16(tmem_base, desc_a + (A_MN ? 128 : 2) * k, desc_b + (B_MN ? 128 : 2) * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_bf16(tmem_acc, desc_a + (A_MN ? 128 : 2) * k, desc_b + (B_MN ? 128 : 2) * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(&empty_bar[s]);   // the slot is free once these MMAs have read it
             }
-            umma_commit(&acc_bar);            // accumulators complete (or abandoned)
+            umma_commit(&acc_full[buf]);      // accumulators complete (or abandoned)
+            }
         }
         __syncwarp();
     } else {
         // ---------------- epilogue: warp w owns TMEM lanes (rows) 32w .. 32w+31
+        int m0, n0;
+        for (int li = 0; my_tile(li, &m0, &n0); ++li) {
+        const int buf = PERSIST ? (li & 1) : 0;
         const int row = m0 + warp * 32 + lane;
         const bool row_ok = row < args.M;
         // C does not depend on the accumulators: the first chunk's row segment is fetched while the main
@@ -227,13 +287,14 @@ __global__ void __launch_bounds__(kGemmThreads, (STAGES * (kBM + BN) * kBK * 2 <
             }
         };
         fetch_c(0);
-        const bool ok = wait_or_abort(&acc_bar, 0, &abort_flag);
+        const bool ok = wait_or_abort(&acc_full[buf], PERSIST ? ((li >> 1) & 1) : 0, &abort_flag);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok && !abort_flag) {
+        if (!ok || abort_flag) break;
+        {
 #pragma unroll 1
             for (int j = 0; j < BN / 32; ++j) {
                 uint32_t r[32];
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(j * 32);
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(buf * BN + j * 32);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -331,12 +392,18 @@ __global__ void __launch_bounds__(kGemmThreads, (STAGES * (kBM + BN) * kBK * 2 <
                 }
             }
         }
+        if (PERSIST) {   // this warp has read its rows of the buffer: one arrival per warp
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+        }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     __syncthreads();
     if (warp == 5) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
     if (threadIdx.x == 0 && abort_flag && args.status != nullptr) atomicExch(args.status, 1);
 }
@@ -375,21 +442,53 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
     return GEFEN_B200_OK;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN>
-static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, cudaStream_t stream) {
+// Tiles a launch computes (see tile_coords).
+static int count_tiles(int M, int N, int bn, int symmetric) {
+    const int tiles_m = (M + kBM - 1) / kBM, tiles_n = (N + bn - 1) / bn;
+    if (!symmetric) return tiles_m * tiles_n;
+    int total = 0;
+    for (int mi = 0; mi < tiles_m; ++mi) {
+        const int row0 = mi * kBM;
+        total += tiles_n - (row0 >= bn ? (row0 - bn) / bn + 1 : 0);
+    }
+    return total;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool PERSIST>
+static int launch_gemm_variant(const CUtensorMap& ma, const CUtensorMap& mb, GemmArgs args, cudaStream_t stream) {
     constexpr int smem = STAGES * (kBM * kBK * 2 + BN * kBK * 2) + 1024;
     static bool configured[64];
     int dev = 0;
     GEFEN_CHECK_CUDA(cudaGetDevice(&dev));
-    auto kernel = ns_gemm_tn_kernel<BN, STAGES, A_MN, B_MN>;
+    auto kernel = ns_gemm_tn_kernel<BN, STAGES, A_MN, B_MN, PERSIST>;
     if (dev < 64 && !configured[dev]) {
         GEFEN_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         configured[dev] = true;
     }
+    args.n_tiles = count_tiles(args.M, args.N, BN, args.symmetric);
     dim3 grid((args.N + BN - 1) / BN, (args.M + kBM - 1) / kBM);
+    if (PERSIST) grid = dim3(args.n_tiles < sm_count() ? args.n_tiles : sm_count(), 1);
     kernel<<<grid, kGemmThreads, smem, stream>>>(ma, mb, args);
     GEFEN_CHECK_CUDA(cudaGetLastError());
     return GEFEN_B200_OK;
+}
+
+// More tiles than SMs: one persistent CTA per SM with two accumulator buffers, so that a tile's
+// epilogue overlaps the next tile's main loop. Otherwise one CTA per tile.
+// GEFEN_B200_NS_PERSIST=0/1 forces the choice (measurements).
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, cudaStream_t stream) {
+    static int forced = -2;
+    if (forced == -2) {
+        const char* e = getenv("GEFEN_B200_NS_PERSIST");
+        forced = e == nullptr ? -1 : (e[0] == '0' ? 0 : 1);
+    }
+    bool persist = count_tiles(args.M, args.N, BN, args.symmetric) > sm_count();
+    if (forced >= 0) persist = forced == 1;
+    if constexpr (STAGES * (kBM + BN) * kBK * 2 > 96 * 1024) {   // the two-CTAs-per-SM variants stay one tile per CTA
+        if (persist) return launch_gemm_variant<BN, STAGES, A_MN, B_MN, true>(ma, mb, args, stream);
+    }
+    return launch_gemm_variant<BN, STAGES, A_MN, B_MN, false>(ma, mb, args, stream);
 }
 
 }  // namespace gefen

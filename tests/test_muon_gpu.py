@@ -63,7 +63,9 @@ def test_newton_schulz_orthogonalises(cuda_device):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 512, 1024), (384, 640, 200), (2048, 2048, 512), (96, 72, 136),
-                                   (1024, 1024, 2048)])
+                                   (1024, 1024, 2048),
+                                   # more tiles than SMs: persistent CTAs, two accumulator buffers, ragged last round
+                                   (2048, 5120, 192), (2200, 4104, 72)])
 def test_tcgen05_gemm_against_fp32_matmul(cuda_device, M, N, K):
     """The tensor-core GEMM against an fp32 torch reference on the same bf16 inputs: one rounding to
     bf16 of an fp32-accumulated result, so the error is half a bf16 ulp of the result plus fp32
@@ -121,7 +123,7 @@ def test_tcgen05_gemm_with_row_major_b(cuda_device, M, N, K):
     assert float((out.float() - want).abs().max()) <= 1e-2 * float(want.abs().max())
 
 
-@pytest.mark.parametrize("m,k", [(128, 256), (384, 200), (2048, 1024), (1000, 512)])
+@pytest.mark.parametrize("m,k", [(128, 256), (384, 200), (2048, 1024), (1000, 512), (4224, 128), (6144, 64)])
 def test_tcgen05_gemm_symmetric_output(cuda_device, m, k):
     """Gram matrix with only the upper-triangle tiles computed and mirrored: bit-identical to the full product."""
     from gefen_b200.newton_schulz import check_status, gemm_tn
