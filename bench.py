@@ -243,7 +243,35 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
         result["breakdown"]["reduce_scatter_mode"] = opt.reduce_scatter_mode
         if opt.fused_errors:
             result["breakdown"]["fused_errors"] = dict(opt.fused_errors)
-        return result, None
+        # end to end at N ranks: every rank's gradients come from its own pinned host buffer and the
+        # full updated parameters go back to it (flat buffers, one copy each way per rank and step)
+        e2e = None
+        if not args.no_e2e:
+            host_g = host_p = None
+            try:
+                host_g = torch.empty(opt.flat_grad.shape, dtype=opt.flat_grad.dtype, pin_memory=True)
+                host_p = torch.empty(opt.flat_param.shape, dtype=opt.flat_param.dtype, pin_memory=True)
+                host_g.copy_(opt.flat_grad)
+            except RuntimeError as exc:   # e.g. the host cannot pin 6 GB per rank
+                host_g = None
+                result["breakdown"]["e2e_skipped"] = str(exc)[:200]
+            everyone = torch.tensor([1.0 if host_g is not None else 0.0], device=device)
+            dist.all_reduce(everyone, op=dist.ReduceOp.MIN)
+            if float(everyone) > 0:
+                def e2e_step():
+                    opt.flat_grad.copy_(host_g, non_blocking=True)
+                    step()
+                    host_p.copy_(opt.flat_param, non_blocking=True)
+
+                e2e_step()
+                dist.barrier()
+                e2e_ms = timed(e2e_step, max(2, min(args.steps, 5)))
+                t = torch.tensor([e2e_ms], device=device)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                nbytes = opt.flat_grad.numel() * opt.flat_grad.element_size()
+                e2e = {"value": float(t), "unit": "ms", "h2d_bytes_per_step": nbytes * world,
+                       "d2h_bytes_per_step": nbytes * world, "note": "per rank {} bytes each way".format(nbytes)}
+        return result, e2e
 
     # ---- roofline of the dominant kernel: the staged vector step over all its tensors, one launch
     from gefen_b200 import _lib
