@@ -332,6 +332,49 @@ def ns_flops(shape, steps=5):
     return steps * (4 * m * m * n + 2 * m ** 3)
 
 
+def run_muon_sharded_arm(args, cfg, rank, world, local_rank):
+    """GefenMuon with whole matrices assigned to the ranks (Zero1GefenMuon): reduce-scatter of the
+    gradients, GefenMuon on the owned matrices, all-gather of the parameters."""
+    import torch.distributed as dist
+
+    from gefen_b200 import newton_schulz as ns
+    from gefen_b200.zero1 import Zero1GefenMuon
+
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    shapes, params, grads = build_model(cfg, device)
+    named = [(name, torch.nn.Parameter(p)) for (name, _), p in zip(shapes, params)]
+    for (_, p), g in zip(named, grads):
+        p.grad = g
+    opt = Zero1GefenMuon(named, lr=cfg["lr"], weight_decay=cfg["wd"], momentum=0.95, ns_steps=5)
+    calibration_ms = timed(opt.step, 1)
+    for _ in range(max(args.warmup - 1, 2)):
+        opt.step()
+    sampler = ClockSampler(local_rank)
+    dist.barrier()
+    sampler.start()
+    ms = timed(opt.step, args.steps)
+    clocks = sampler.stop()
+    ns.check_status(device)
+    t = torch.tensor([ms], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    breakdown = opt.last_breakdown_ms()
+    if rank != 0:
+        return
+    elems = sum(workloads.numel(s) for _, s in shapes)
+    owned = len(opt.pieces)
+    print(json.dumps({
+        "metric": "optimizer_step_ms", "value": float(t), "unit": "ms", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": float(t), "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload, "optimizer": "GefenMuon(momentum=0.95, ns_steps=5)", "lr": cfg["lr"],
+                   "weight_decay": cfg["wd"], "matrices": len(shapes), "elements": elems,
+                   "parallelism": "zero1-dp{} (whole matrices per rank)".format(world)},
+        "calibration_first_step_ms": calibration_ms, "clocks": clocks, "breakdown_ms": breakdown,
+        "gpu_launches": args.steps * (owned * 15 + 8),
+    }))
+
+
 def run_muon_arm(args, cfg):
     """GefenMuon on the Qwen3-1.7B-shaped matrices, one GPU: whole step, then Newton-Schulz alone on
     this library's tcgen05 GEMM and on torch's (cuBLAS) GEMMs for the same inputs."""
@@ -521,6 +564,15 @@ def main():
     if cfg.get("muon"):
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device")
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            try:
+                run_muon_sharded_arm(args, cfg, rank, world, local_rank)
+            finally:
+                dist.destroy_process_group()
+            return
         run_muon_arm(args, cfg)
         return
     if not torch.cuda.is_available():

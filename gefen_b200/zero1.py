@@ -124,6 +124,36 @@ class FlatLayout:
         return [p for p in self.pieces if p.rank == rank]
 
 
+class WholeTensorLayout:
+    """Assigns WHOLE tensors to ranks (largest first, each to the least loaded rank) and places every
+    rank's tensors, in parameter order, in its segment of the flat buffer. For optimizers whose update
+    of a matrix needs the whole matrix (GefenMuon's Newton-Schulz)."""
+
+    def __init__(self, shapes: Sequence[Tuple[int, ...]], world: int):
+        self.world = world
+        self.shapes = [tuple(s) for s in shapes]
+        dims = [(s[0], int(math.prod(s[1:]))) if len(s) >= 2 else (1, int(math.prod(s)) if len(s) else 1)
+                for s in self.shapes]
+        load = [0] * world
+        owner = [0] * len(dims)
+        for t in sorted(range(len(dims)), key=lambda i: (-dims[i][0] * dims[i][1], i)):
+            r = min(range(world), key=lambda q: (load[q], q))
+            owner[t] = r
+            load[r] += _round_up(dims[t][0] * dims[t][1], ALIGN)
+        self.segment = _round_up(max(max(load), 1), ALIGN)
+        self.total = self.segment * world
+        fill = [0] * world
+        self.pieces: List[Piece] = []
+        for t, (rows, cols) in enumerate(dims):
+            r = owner[t]
+            self.pieces.append(Piece(t, 0, rows, cols, r, r * self.segment + fill[r]))
+            fill[r] += _round_up(rows * cols, ALIGN)
+        self.tensor_offset = [p.offset for p in self.pieces]
+
+    def owned(self, rank: int) -> List[Piece]:
+        return [p for p in self.pieces if p.rank == rank]
+
+
 class GpuOps:
     """Device work of the calibration, on the library's kernels."""
 
@@ -194,7 +224,7 @@ class Zero1Gefen:
         for n, p in self.named:
             if p.dtype != self.dtype or p.device != self.device:
                 raise ValueError("Zero1Gefen expects one dtype and device per instance, got {} for {}".format(p.dtype, n))
-        self.layout = FlatLayout([tuple(p.shape) for _, p in self.named], self.world)
+        self.layout = self._make_layout([tuple(p.shape) for _, p in self.named])
         self._token = None
         self.flat_param, param_ptrs = self._allocate_flat(fused_all_gather, "GEFEN_B200_ZERO1_FUSED_AG", "all_gather")
         # Off unless asked for. With it a rank's step kernel reads its gradients from every peer with
@@ -233,13 +263,19 @@ class Zero1Gefen:
             prm.grad = self.flat_grad[pc.offset:pc.offset + pc.numel].view(shape)
             self.piece_params.append(prm)
             named_pieces.append(("{}#{}".format(self.named[pc.tensor][0], pc.row0), prm))
-        self.local = self.ops.make_optimizer(named_pieces, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay) \
+        self.local = self._make_local(named_pieces, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay) \
             if named_pieces else None
         if self.local is not None and self._peer_deltas is not None:
             self.local._peer_param_deltas = self._peer_deltas
         self.period_mismatches: List[Tuple[str, Dict[int, int]]] = []
         self._events = None
         self._calibrated = False
+
+    def _make_layout(self, shapes):
+        return FlatLayout(shapes, self.world)
+
+    def _make_local(self, named_pieces, **kwargs):
+        return self.ops.make_optimizer(named_pieces, **kwargs)
 
     # ------------------------------------------------------------------ flat buffers
     def _allocate_flat(self, requested: Optional[bool], env_name: str, what: str, default: str = "1"):
@@ -431,7 +467,7 @@ class Zero1Gefen:
         m = self._events
         launches = 0
         if self.local is not None and getattr(self.local, "_plan", None) is not None:
-            launches = sum(len(set(t.get("classes", [1]))) for t in self.local._plan.tables)
+            launches = sum(len(set(t.get("classes", [1]))) for t in (self.local._plan.tables or []))
         return {"reduce_scatter": m[0].elapsed_time(m[1]), "local_step": m[1].elapsed_time(m[2]),
                 "all_gather": m[2].elapsed_time(m[3]), "kernel_launches_per_step": launches}
 
@@ -451,3 +487,33 @@ class Zero1Gefen:
             self.codebook = self.local._gefen_codebook
             self._calibrated = self.codebook is not None
         self.periods = sd.get("periods")
+
+
+class Zero1GefenMuon(Zero1Gefen):
+    """GefenMuon over ZeRO-1 sharded state. Newton-Schulz needs whole matrices, so whole tensors are
+    assigned to ranks (`WholeTensorLayout`); the step is reduce-scatter of the gradients, GefenMuon on
+    the owned matrices, all-gather of the parameters (NCCL: the final update is not one of this
+    library's kernels, so there is nothing to ride the all-gather on). N ranks reproduce one rank bit
+    for bit: every matrix is processed whole by the same kernels, and the codebook is fitted from the
+    gathered histogram."""
+
+    def __init__(self, named_params, lr=1e-3, weight_decay=0.1, momentum=0.95, nesterov=True,
+                 ns_coefficients=(3.4445, -4.7750, 2.0315), eps=1e-7, ns_steps=5, adjust_lr_fn=None, *, group=None,
+                 ops=None, average_gradients: bool = True):
+        self._muon_kwargs = dict(lr=lr, weight_decay=weight_decay, momentum=momentum, nesterov=nesterov,
+                                 ns_coefficients=ns_coefficients, eps=eps, ns_steps=ns_steps, adjust_lr_fn=adjust_lr_fn)
+        super().__init__(named_params, lr=lr, eps=eps, weight_decay=weight_decay, group=group, ops=ops,
+                         average_gradients=average_gradients, fused_all_gather=False, fused_reduce_scatter=False)
+
+    def _make_layout(self, shapes):
+        for s in shapes:
+            if len(s) != 2:
+                raise ValueError("GefenMuon only supports 2D parameters whereas we found a parameter with size: {}".format(s))
+        return WholeTensorLayout(shapes, self.world)
+
+    def _make_local(self, named_pieces, **kwargs):
+        if hasattr(self.ops, "make_muon_optimizer"):
+            return self.ops.make_muon_optimizer(named_pieces, **self._muon_kwargs)
+        from .gefen_muon import GefenMuon
+
+        return GefenMuon(named_pieces, **self._muon_kwargs)

@@ -151,3 +151,24 @@ def test_flat_layout_invariants():
                     assert a.offset + a.numel == b.offset and a.row0 + a.rows == b.row0
             loads = [sum(p.numel for p in layout.owned(r)) for r in range(world)]
             assert max(loads) <= total / world * 1.01 + 8192
+
+
+def test_whole_tensor_layout_invariants():
+    from gefen_b200 import workloads
+    from gefen_b200.zero1 import WholeTensorLayout
+
+    shapes = [s for _, s in workloads.qwen3_1_7b_matrices()] + [(7, 3), (1, 8)]
+    total = sum(workloads.numel(s) for s in shapes)
+    for world in (1, 2, 3, 8):
+        layout = WholeTensorLayout(shapes, world)
+        assert layout.total == layout.segment * world
+        spans = []
+        for t, pc in enumerate(layout.pieces):
+            assert pc.tensor == t and pc.row0 == 0 and pc.numel == workloads.numel(shapes[t])
+            assert pc.offset % 8 == 0
+            assert pc.rank * layout.segment <= pc.offset and pc.offset + pc.numel <= (pc.rank + 1) * layout.segment
+            spans.append((pc.offset, pc.offset + pc.numel))
+        spans.sort()
+        assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:]))
+        loads = [sum(p.numel for p in layout.owned(r)) for r in range(world)]
+        assert sum(loads) == total and max(loads) - min(loads) <= max(workloads.numel(s) for s in shapes)

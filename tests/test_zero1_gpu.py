@@ -86,3 +86,55 @@ def test_fused_collectives_equal_nccl_collectives(tmp_path):
     for name in ("nccl", "fused_ag", "fused_both"):
         assert torch.equal(ranks[0][name][3], ranks[1][name][3]), name
     assert float(ranks[0]["fused_both"][3].float().abs().sum()) > 0
+
+
+def _muon_worker(rank: int, world: int, port: int, out_dir: str) -> None:
+    import torch.distributed as dist
+
+    from gefen_b200 import GefenMuon
+    from gefen_b200.zero1 import Zero1GefenMuon
+    from tests.util import make_grad, make_param
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dev = torch.device("cuda", rank)
+    shapes = [(256, 512), (512, 256), (384, 384), (128, 1024), (640, 128)]
+
+    def build():
+        params = [torch.nn.Parameter(make_param(s, 9, i, torch.bfloat16).to(dev)) for i, s in enumerate(shapes)]
+        for p in params:
+            p.grad = torch.zeros_like(p)
+        return params, [("w{}".format(i), p) for i, p in enumerate(params)]
+
+    sharded_params, named = build()
+    sharded = Zero1GefenMuon(named, lr=0.02, weight_decay=0.1)
+    single_params, named1 = build()
+    single = GefenMuon(named1, lr=0.02, weight_decay=0.1)
+    for step in range(3):
+        for i, s in enumerate(shapes):   # the same gradient on every rank: its average is itself
+            g = make_grad(s, 9, i, step, torch.bfloat16).to(dev)
+            sharded_params[i].grad.copy_(g)
+            single_params[i].grad.copy_(g)
+        sharded.step()
+        single.step()
+    torch.cuda.synchronize()
+    same = all(torch.equal(a.detach(), b.detach()) for a, b in zip(sharded_params, single_params))
+    owned = sorted(pc.tensor for pc in sharded.pieces)
+    torch.save({"same": same, "owned": owned}, os.path.join(out_dir, "muon_rank{}.pt".format(rank)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sharded_muon_equals_single_process(tmp_path):
+    import torch.multiprocessing as mp
+
+    world = 2
+    mp.spawn(_muon_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    ranks = [torch.load(tmp_path / "muon_rank{}.pt".format(r), weights_only=False) for r in range(world)]
+    assert all(r["same"] for r in ranks)
+    assert sorted(ranks[0]["owned"] + ranks[1]["owned"]) == list(range(5))
+    assert ranks[0]["owned"] and ranks[1]["owned"]
