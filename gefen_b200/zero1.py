@@ -488,6 +488,92 @@ class Zero1Gefen:
             self._calibrated = self.codebook is not None
         self.periods = sd.get("periods")
 
+    # ------------------------------------------------------------------ world-size independent checkpoint
+    def _piece_blocks(self, pc: Piece, period: int) -> Tuple[int, int]:
+        """Range of the tensor's partition blocks that lie in piece `pc` (blocks never straddle pieces)."""
+        first, last = pc.row0 * pc.cols, (pc.row0 + pc.rows) * pc.cols
+        if first % period or last % period:
+            raise ValueError("period {} does not tile the piece at row {}".format(period, pc.row0))
+        return first // period, last // period
+
+    def full_state_dict(self):
+        """Collective. The optimizer state of the WHOLE model on every rank, per tensor and in the layout
+        a single process keeps (reference: gefen.py:1039-1062, 1343-1349): the pieces' codes, magnitudes
+        and second moments concatenated in row order (CPU tensors). It can be loaded at any other world
+        size with `load_full_state_dict`, and `state` has the reference's per-parameter schema."""
+        mine = {}
+        for pc, prm in zip(self.pieces, self.piece_params):
+            st = self.local.state[prm] if self.local is not None else {}
+            mine[(pc.tensor, pc.row0)] = {k: (v.detach().cpu() if torch.is_tensor(v) else v) for k, v in st.items()}
+        everyone = {}
+        for d in self._gather_objects(mine):
+            everyone.update(d)
+        state = {}
+        for t in range(len(self.named)):
+            parts = [everyone[k] for k in sorted(k for k in everyone if k[0] == t)]
+            parts = [p for p in parts if p]
+            if not parts:
+                continue
+            if len(parts) == 1:
+                state[t] = dict(parts[0])
+                continue
+            if any(p.get("automatic_period") == 1 for p in parts):
+                raise NotImplementedError("a tensor with period 1 that is split between ranks keeps rank-local "
+                                          "magnitude blocks and cannot be consolidated")
+            merged = {}
+            for key, value in parts[0].items():
+                if torch.is_tensor(value) and value.dim() >= 1:
+                    merged[key] = torch.cat([p[key] for p in parts], dim=0)
+                else:
+                    merged[key] = value
+            if "m_codebook_shape" in merged:
+                merged["m_codebook_shape"] = tuple(merged["m_codebook"].shape)
+            state[t] = merged
+        codebook = getattr(self, "codebook", None)
+        return {"format": "gefen_b200.zero1.full/1", "names": [n for n, _ in self.named],
+                "shapes": [tuple(p.shape) for _, p in self.named], "state": state,
+                "periods": dict(getattr(self, "periods", None) or {}),
+                "gefen_codebook": None if codebook is None else codebook.detach().cpu(),
+                "gefen_global_step": max([int(st.get("step", 0)) for st in state.values()] or [0])}
+
+    def load_full_state_dict(self, full) -> None:
+        """Takes this rank's share of a `full_state_dict` (saved at any world size)."""
+        if [tuple(s) for s in full["shapes"]] != [tuple(p.shape) for _, p in self.named]:
+            raise ValueError("the checkpoint was written for different parameter shapes")
+        self.periods = {int(k): int(v) for k, v in full["periods"].items()}
+        codebook = full["gefen_codebook"]
+        self.codebook = None if codebook is None else codebook.to(self.device)
+        if self.local is None:
+            self._calibrated = self.codebook is not None
+            return
+        for pc, prm in zip(self.pieces, self.piece_params):
+            whole = full["state"].get(pc.tensor)
+            target = self.local.state[prm]
+            target.clear()
+            if not whole:
+                continue
+            period = int(whole["automatic_period"])
+            whole_rows = self.layout.shapes[pc.tensor][0] if len(self.layout.shapes[pc.tensor]) >= 2 else 1
+            if pc.rows == whole_rows or len(self.layout.shapes[pc.tensor]) < 2:
+                piece_state = dict(whole)
+            else:
+                if period == 1:
+                    raise NotImplementedError("a tensor with period 1 cannot be split between ranks on load")
+                b0, b1 = self._piece_blocks(pc, period)
+                nb = whole["m_codebook"].shape[0]
+                piece_state = {k: (v[b0:b1].clone() if torch.is_tensor(v) and v.dim() >= 1 and v.shape[0] == nb else v)
+                               for k, v in whole.items()}
+                if "m_codebook_shape" in piece_state:
+                    piece_state["m_codebook_shape"] = tuple(piece_state["m_codebook"].shape)
+            for k, v in piece_state.items():
+                target[k] = v.to(self.device) if torch.is_tensor(v) else v
+        self.local._gefen_codebook = None if self.codebook is None else self.codebook.contiguous()
+        if hasattr(self.local, "_gefen_global_step"):
+            self.local._gefen_global_step = int(full.get("gefen_global_step", 0))
+        if hasattr(self.local, "_plans"):
+            self.local._plans = {}
+        self._calibrated = self.codebook is not None
+
 
 class Zero1GefenMuon(Zero1Gefen):
     """GefenMuon over ZeRO-1 sharded state. Newton-Schulz needs whole matrices, so whole tensors are

@@ -181,3 +181,45 @@ def test_host_streamed_step_equals_plain_step(cuda_device):
     for p, q in zip(plain_params, stream_params):
         assert torch.equal(plain.state[p]["m_codebook"], streamed_opt.state[q]["m_codebook"])
     assert plain._gefen_global_step == streamed_opt._gefen_global_step == 4
+
+
+class _ShardedParam(torch.nn.Parameter):
+    """Stands in for a DTensor parameter: the optimizer must go through to_local() (and may get a
+    non-contiguous local shard, which only objects with `placements` are allowed to hand over)."""
+    placements = ("Shard(0)",)
+
+    def to_local(self):
+        return self._local_view
+
+
+class _AsyncGrad(torch.Tensor):
+    """Stands in for a gradient that is still the handle of an asynchronous collective."""
+
+    def wait(self):
+        return self.as_subclass(torch.Tensor)
+
+
+def test_dtensor_like_parameters_and_async_gradients(cuda_device):
+    """reference: gefen.py:692-706, 1287-1322. Duck-typed unwrapping of DTensor-like parameters
+    (to_local, non-contiguous local shard copied in and out) and of gradients with wait()."""
+    from gefen_b200 import Gefen
+
+    shape = (48, 512)
+    base = make_param(shape, 4, 0, torch.bfloat16).to(cuda_device)
+    plain = torch.nn.Parameter(base.clone())
+    # the "local shard" is a transposed view of a [512, 48] buffer: same values, not contiguous
+    storage = base.clone().t().contiguous()
+    sharded = _ShardedParam(torch.zeros(shape, device=cuda_device, dtype=torch.bfloat16))   # its own data is never used
+    sharded._local_view = storage.t()
+    assert not sharded._local_view.is_contiguous()
+    opt_plain = Gefen([("w", plain)], lr=1e-3, weight_decay=0.1)
+    opt_sharded = Gefen([("w", sharded)], lr=1e-3, weight_decay=0.1)
+    for step in range(3):
+        g = make_grad(shape, 4, 0, step, torch.bfloat16).to(cuda_device)
+        plain.grad = g.clone()
+        sharded.grad = g.clone().as_subclass(_AsyncGrad)
+        opt_plain.step()
+        opt_sharded.step()
+    torch.cuda.synchronize()
+    assert torch.equal(sharded.to_local(), plain.detach())
+    assert torch.equal(opt_sharded.state[sharded]["m_codebook"], opt_plain.state[plain]["m_codebook"])

@@ -117,3 +117,68 @@ def test_two_ranks_reproduce_one_process(tmp_path, oracle):
     # both ranks own something, and at least one tensor is split between them
     owned = [set(t for t, _, _ in out["pieces"]) for out in outs]
     assert owned[0] and owned[1] and (owned[0] & owned[1])
+
+
+def _reshard_worker(rank, world, port, out_dir):
+    sys.path.insert(0, str(ROOT))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from gefen_b200.zero1 import Zero1Gefen
+    from tests.util import make_param
+
+    params = [torch.nn.Parameter(make_param(s, 0, i) if len(s) == 2 else torch.ones(s)) for i, s in enumerate(SHAPES)]
+    opt = Zero1Gefen([("p{}".format(i), p) for i, p in enumerate(params)], lr=1e-3, weight_decay=0.1, ops=OracleOps())
+    for step in range(3):
+        for p, g in zip(params, _grads(step, rank, world)):
+            p.grad.copy_(g)
+        opt.step()
+    full = opt.full_state_dict()
+    params_at_three = [p.detach().clone() for p in params]
+    for step in range(3, 5):
+        for p, g in zip(params, _grads(step, rank, world)):
+            p.grad.copy_(g)
+        opt.step()
+    torch.save({"full": full, "params_at_three": params_at_three, "params_at_five": [p.detach().clone() for p in params]},
+               os.path.join(out_dir, "reshard{}.pt".format(rank)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_full_state_moves_between_world_sizes(tmp_path, oracle):
+    """State saved by two ranks (whole-model layout, identical on both) is loaded by a single process,
+    which then reaches the same parameters as the two ranks did; and loading it back into the pieces of
+    the single process reproduces the pieces' state."""
+    from gefen_b200.zero1 import Zero1Gefen
+
+    world = 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_reshard_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    outs = [torch.load(tmp_path / "reshard{}.pt".format(r), weights_only=False) for r in range(world)]
+    full = outs[0]["full"]
+    other = outs[1]["full"]
+    assert full["periods"] == other["periods"] and torch.equal(full["gefen_codebook"], other["gefen_codebook"])
+    assert sorted(full["state"]) == list(range(len(SHAPES)))
+    for t in full["state"]:
+        for k, v in full["state"][t].items():
+            if torch.is_tensor(v):
+                assert torch.equal(v, other["state"][t][k])
+        n = 1
+        for d in SHAPES[t]:
+            n *= d
+        assert full["state"][t]["m_codebook"].numel() == n and full["state"][t]["step"] == 3
+    # one process (no process group) continues from the two ranks' checkpoint
+    params = [torch.nn.Parameter(p.clone()) for p in outs[0]["params_at_three"]]
+    single = Zero1Gefen([("p{}".format(i), p) for i, p in enumerate(params)], lr=1e-3, weight_decay=0.1, ops=OracleOps())
+    single.load_full_state_dict(full)
+    for step in range(3, 5):
+        per_rank = [_grads(step, r, world) for r in range(world)]
+        for p, a, b in zip(params, *per_rank):
+            p.grad.copy_((a + b) / world)
+        single.step()
+    for p, want in zip(params, outs[0]["params_at_five"]):
+        assert torch.equal(p.detach(), want)
+    again = single.full_state_dict()
+    assert again["gefen_global_step"] == 5
