@@ -26,6 +26,7 @@ STEP_WEIGHT_DECAY = 2
 STEP_PERIOD1 = 4
 STEP_MUON = 8
 STEP_NESTEROV = 16
+STEP_PACKED = 32
 
 # numpy mirror of gefen_b200_step_tensor_t (include/gefen_b200.h)
 STEP_TENSOR_DTYPE = np.dtype(

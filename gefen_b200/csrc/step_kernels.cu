@@ -644,7 +644,12 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
         const bool nesterov = (flags & GEFEN_B200_STEP_NESTEROV) != 0;
         const S* g = static_cast<const S*>(tp->g) + start;
         S* prm = static_cast<S*>(tp->p) + start;
-        uint8_t* codes = tp->codes + start;
+        // 4-bit codes (reference: automatic_gefen_fused_kernel.cu:14-57): two per byte over the whole
+        // tensor, low nibble first. The period is even here, so a block starts on a byte and a thread
+        // that owns an element pair owns its byte: no atomics.
+        const bool packed = (flags & GEFEN_B200_STEP_PACKED) != 0;
+        const int per = packed ? 2 : 1;
+        uint8_t* codes = tp->codes + (packed ? start / 2 : start);
         void* mag_ptr = tp->mag;
         void* v_ptr = tp->v;
         const int mag_dtype = tp->mag_dtype, v_dtype = tp->v_dtype;
@@ -659,16 +664,21 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
         // period-1 tensors update their per-element second moment here
         // (reference: automatic_gefen_fused_kernel.cu:350-366).
         float absmax = 0.0f, sumsq = 0.0f;
-        for (int i = tig; i < period; i += GROUP) {
-            const float gi = gradient_element(g + i, L);
-            if (period1) {
-                const float prev = load_state(v_ptr, start + i, v_dtype);
-                store_state(v_ptr, start + i, v_dtype, fmaf(beta2, prev, (omb2 * gi) * gi));
+        for (int i0 = tig * per; i0 < period; i0 += GROUP * per) {
+            const uint32_t byte = codes[packed ? i0 / 2 : i0];
+            for (int e = 0; e < per; ++e) {
+                const int i = i0 + e;
+                const uint32_t old_code = packed ? ((byte >> (4 * e)) & 0xFu) : byte;
+                const float gi = gradient_element(g + i, L);
+                if (period1) {
+                    const float prev = load_state(v_ptr, start + i, v_dtype);
+                    store_state(v_ptr, start + i, v_dtype, fmaf(beta2, prev, (omb2 * gi) * gi));
+                }
+                const float cur = old_mag * s.cb[old_code];
+                const float u = period1 ? ema_update_period1(beta1, cur, omb1, gi) : ema_update(beta1, cur, omb1, gi);
+                absmax = fmaxf(absmax, fabsf(u));
+                sumsq = fmaf(gi, gi, sumsq);
             }
-            const float cur = old_mag * s.cb[codes[i]];
-            const float u = period1 ? ema_update_period1(beta1, cur, omb1, gi) : ema_update(beta1, cur, omb1, gi);
-            absmax = fmaxf(absmax, fabsf(u));
-            sumsq = fmaf(gi, gi, sumsq);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) absmax = fmaxf(absmax, __shfl_xor_sync(0xffffffffu, absmax, o));
@@ -709,14 +719,19 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
         const bool do_update = muon || period1 || lr != 0.0f;
 
         // pass 2: re-encode and update
-        for (int i = tig; i < period; i += GROUP) {
+        for (int i0 = tig * per; i0 < period; i0 += GROUP * per) {
+            const uint32_t byte = codes[packed ? i0 / 2 : i0];
+            uint32_t new_byte = 0u;
+            for (int e = 0; e < per; ++e) {
+            const int i = i0 + e;
+            const uint32_t old_code = packed ? ((byte >> (4 * e)) & 0xFu) : byte;
             const float gi = gradient_element(g + i, L);
-            const float cur = old_mag * s.cb[codes[i]];
+            const float cur = old_mag * s.cb[old_code];
             const float u = period1 ? ema_update_period1(beta1, cur, omb1, gi) : ema_update(beta1, cur, omb1, gi);
             float x = 0.0f;
             if (absmax > 0.0f) x = u / absmax;
             const uint32_t code = static_cast<uint32_t>(entry_exact(x, s.thr, s.cb, s.k));
-            codes[i] = static_cast<uint8_t>(code);
+            new_byte |= packed ? ((code & 0xFu) << (4 * e)) : code;
             const float q = s.cb[code] * absmax;
             if (muon) {
                 float out = q;
@@ -731,6 +746,8 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
                 ScalarIO<S>::store(prm + i, updated);
                 for (int r = 0; r < L.n_peers; ++r) ScalarIO<S>::store(peer_ptr(prm + i, L.peer_delta[r]), updated);
             }
+            }
+            codes[packed ? i0 / 2 : i0] = static_cast<uint8_t>(new_byte);
         }
     }
 }
@@ -863,7 +880,8 @@ static int launch_generic(bool cta_per_block, const StepLaunch& L, const gefen_b
 static int tensor_class(const gefen_b200_step_tensor_t& t, int dtype) {
     const bool vec_dtype = dtype == GEFEN_B200_F32 || dtype == GEFEN_B200_BF16 || dtype == GEFEN_B200_F16;
     const bool period1 = (t.flags & GEFEN_B200_STEP_PERIOD1) != 0;
-    if (vec_dtype && !period1 && t.period % 8 == 0 && t.period <= kFastMaxPeriod && aligned16(t.g) && aligned16(t.p) &&
+    const bool packed = (t.flags & GEFEN_B200_STEP_PACKED) != 0;
+    if (vec_dtype && !period1 && !packed && t.period % 8 == 0 && t.period <= kFastMaxPeriod && aligned16(t.g) && aligned16(t.p) &&
         (reinterpret_cast<uintptr_t>(t.codes) & 7u) == 0) {
         return 1;
     }
@@ -895,10 +913,9 @@ static int check_common(const void* g, uint8_t* codes, void* mag, int mag_dtype,
                     "Expected m_magnitude to have dtype float32, float16, or bfloat16.");
     GEFEN_CHECK_ARG(num_blocks >= 0 && period > 0, "Expected a positive period and a non-negative block count.");
     GEFEN_CHECK_ARG(period <= 0x7FFFFFFFLL, "Period %lld is too large.", period);
-    if (packed_indices) {
+    if (packed_indices && period % 2 != 0) {
         return fail(GEFEN_B200_EUNSUPPORTED,
-                    "packed_indices=True (4-bit codes) is not implemented; every caller in the optimizer "
-                    "passes False.");
+                    "packed_indices=True (4-bit codes) needs an even period: with an odd one two blocks share a byte.");
     }
     return GEFEN_B200_OK;
 }
@@ -976,7 +993,7 @@ int gefen_b200_automatic_gefen_fused_update_from_vmean(
     t.num_blocks = num_blocks; t.period = period;
     t.beta1 = static_cast<float>(beta1); t.lr = static_cast<float>(lr);
     t.bc1 = static_cast<float>(bias_correction_1); t.bc2 = static_cast<float>(bias_correction_2);
-    t.eps = static_cast<float>(eps); t.wd_mul = 1.0f; t.flags = 0;
+    t.eps = static_cast<float>(eps); t.wd_mul = 1.0f; t.flags = packed_indices ? GEFEN_B200_STEP_PACKED : 0u;
     t.mag_dtype = magnitude_dtype; t.v_dtype = vmean_dtype;
     return run_single(t, param_dtype, nullptr, codebook, codebook_size, codebook_ws, static_cast<cudaStream_t>(stream));
 }
@@ -992,7 +1009,7 @@ int gefen_b200_automatic_gefen_fused_update(
     t.p = p; t.g = grad_view; t.codes = m_sign; t.mag = m_magnitude; t.v = nullptr;
     t.num_blocks = num_blocks; t.period = period;
     t.beta1 = static_cast<float>(beta1); t.lr = static_cast<float>(lr);
-    t.bc1 = 1.0f; t.bc2 = 1.0f; t.eps = 0.0f; t.wd_mul = 1.0f; t.flags = 0;
+    t.bc1 = 1.0f; t.bc2 = 1.0f; t.eps = 0.0f; t.wd_mul = 1.0f; t.flags = packed_indices ? GEFEN_B200_STEP_PACKED : 0u;
     t.mag_dtype = magnitude_dtype; t.v_dtype = GEFEN_B200_F32;
     return run_single(t, param_dtype, stepsize, codebook, codebook_size, codebook_ws, static_cast<cudaStream_t>(stream));
 }
@@ -1034,7 +1051,7 @@ int gefen_b200_automatic_gefen_muon_momentum(
     t.p = momentum_update; t.g = grad_view; t.codes = m_sign; t.mag = m_magnitude; t.v = nullptr;
     t.num_blocks = num_blocks; t.period = period;
     t.beta1 = static_cast<float>(beta1); t.lr = 0.0f; t.bc1 = 1.0f; t.bc2 = 1.0f; t.wd_mul = 1.0f;
-    t.flags = GEFEN_B200_STEP_MUON;
+    t.flags = GEFEN_B200_STEP_MUON | (packed_indices ? GEFEN_B200_STEP_PACKED : 0u);
     t.mag_dtype = magnitude_dtype; t.v_dtype = GEFEN_B200_F32;
     return run_single(t, grad_dtype, nullptr, codebook, codebook_size, codebook_ws, static_cast<cudaStream_t>(stream));
 }
@@ -1141,6 +1158,8 @@ int gefen_b200_multi_tensor_step_peers(gefen_b200_step_tensor_t* host_table, voi
         GEFEN_CHECK_ARG(is_state_dtype(t.mag_dtype) && is_state_dtype(t.v_dtype),
                         "Tensor %d of the table has a bad state dtype.", i);
         GEFEN_CHECK_ARG((t.flags & GEFEN_B200_STEP_MUON) || t.v != nullptr, "Tensor %d has a null vmean.", i);
+        GEFEN_CHECK_ARG(!(t.flags & GEFEN_B200_STEP_PACKED) || (t.period % 2 == 0 && !(t.flags & GEFEN_B200_STEP_PERIOD1)),
+                        "Tensor %d: 4-bit codes need an even period and are not defined for period-1 tensors.", i);
         t.reserved_[0] = tensor_class(t, param_dtype);
     }
     for (int begin = 0; begin < n_tensors;) {

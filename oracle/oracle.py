@@ -68,6 +68,42 @@ def nearest_indices(codebook: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
     return out.view(x.shape)
 
 
+def _unpack_nibbles(m_sign: torch.Tensor, numel: int) -> torch.Tensor:
+    """4-bit codes, two per byte, low nibble first (reference: automatic_gefen_fused_kernel.cu:14-27)."""
+    flat = m_sign.reshape(-1)
+    both = torch.stack([flat & 0x0F, (flat >> 4) & 0x0F], dim=1).reshape(-1)
+    return both[:numel].contiguous()
+
+
+def _pack_nibbles(codes: torch.Tensor, m_sign: torch.Tensor) -> None:
+    """Writes the codes back in place; an odd tail leaves the unused high nibble as it was."""
+    flat = m_sign.reshape(-1)
+    c = codes.reshape(-1)
+    pairs = c.numel() // 2
+    flat[:pairs] = (c[0:2 * pairs:2] & 0x0F) | ((c[1:2 * pairs:2] & 0x0F) << 4)
+    if c.numel() % 2:
+        flat[pairs] = (flat[pairs] & 0xF0) | (c[-1] & 0x0F)
+
+
+class _Codes:
+    """Byte-per-code view of m_sign for the C kernels, packed back on exit when needed."""
+
+    def __init__(self, m_sign, shape, packed):
+        self.m_sign, self.packed = m_sign, packed
+        numel = 1
+        for d in shape:
+            numel *= d
+        self.codes = _unpack_nibbles(m_sign, numel).view(shape) if packed else m_sign
+
+    def __enter__(self):
+        return self.codes
+
+    def __exit__(self, *exc):
+        if self.packed:
+            _pack_nibbles(self.codes, self.m_sign)
+        return False
+
+
 def automatic_vmean_update(vmean, grad_view, beta2):
     nb, period = grad_view.shape
     lib().oracle_vmean_update(_ptr(vmean), _DT[vmean.dtype], _ptr(grad_view), _DT[grad_view.dtype], _i64(nb),
@@ -76,20 +112,20 @@ def automatic_vmean_update(vmean, grad_view, beta2):
 
 def automatic_gefen_fused_update_from_vmean(p, grad_view, m_sign, m_magnitude, vmean, codebook, packed_indices,
                                             beta1, lr, bias_correction_1, bias_correction_2, eps):
-    assert not packed_indices
     nb, period = grad_view.shape
-    lib().oracle_fused_update_from_vmean(_ptr(p), _ptr(grad_view), _DT[p.dtype], _ptr(m_sign), _ptr(m_magnitude),
-                                         _DT[m_magnitude.dtype], _ptr(vmean), _DT[vmean.dtype], _ptr(codebook),
-                                         ctypes.c_int(codebook.numel()), _i64(nb), _i64(period), _d(beta1), _d(lr),
-                                         _d(bias_correction_1), _d(bias_correction_2), _d(eps))
+    with _Codes(m_sign, (nb, period), packed_indices) as codes:
+        lib().oracle_fused_update_from_vmean(_ptr(p), _ptr(grad_view), _DT[p.dtype], _ptr(codes), _ptr(m_magnitude),
+                                             _DT[m_magnitude.dtype], _ptr(vmean), _DT[vmean.dtype], _ptr(codebook),
+                                             ctypes.c_int(codebook.numel()), _i64(nb), _i64(period), _d(beta1), _d(lr),
+                                             _d(bias_correction_1), _d(bias_correction_2), _d(eps))
 
 
 def automatic_gefen_fused_update(p, grad_view, m_sign, m_magnitude, stepsize, codebook, packed_indices, beta1, lr):
-    assert not packed_indices
     nb, period = grad_view.shape
-    lib().oracle_fused_update(_ptr(p), _ptr(grad_view), _DT[p.dtype], _ptr(m_sign), _ptr(m_magnitude),
-                              _DT[m_magnitude.dtype], _ptr(stepsize), _ptr(codebook), ctypes.c_int(codebook.numel()),
-                              _i64(nb), _i64(period), _d(beta1), _d(lr))
+    with _Codes(m_sign, (nb, period), packed_indices) as codes:
+        lib().oracle_fused_update(_ptr(p), _ptr(grad_view), _DT[p.dtype], _ptr(codes), _ptr(m_magnitude),
+                                  _DT[m_magnitude.dtype], _ptr(stepsize), _ptr(codebook), ctypes.c_int(codebook.numel()),
+                                  _i64(nb), _i64(period), _d(beta1), _d(lr))
 
 
 def automatic_gefen_period1_update(p, grad_flat, m_sign, m_magnitude, vmean, codebook, period_one_divisor, beta1,
@@ -101,11 +137,11 @@ def automatic_gefen_period1_update(p, grad_flat, m_sign, m_magnitude, vmean, cod
 
 
 def automatic_gefen_muon_momentum(grad_view, m_sign, m_magnitude, codebook, momentum_update, packed_indices, beta1):
-    assert not packed_indices
     nb, period = grad_view.shape
-    lib().oracle_muon_momentum(_ptr(grad_view), _DT[grad_view.dtype], _ptr(m_sign), _ptr(m_magnitude),
-                               _DT[m_magnitude.dtype], _ptr(codebook), ctypes.c_int(codebook.numel()),
-                               _ptr(momentum_update), _i64(nb), _i64(period), _d(beta1))
+    with _Codes(m_sign, (nb, period), packed_indices) as codes:
+        lib().oracle_muon_momentum(_ptr(grad_view), _DT[grad_view.dtype], _ptr(codes), _ptr(m_magnitude),
+                                   _DT[m_magnitude.dtype], _ptr(codebook), ctypes.c_int(codebook.numel()),
+                                   _ptr(momentum_update), _i64(nb), _i64(period), _d(beta1))
 
 
 def weight_decay(p, lr, wd):

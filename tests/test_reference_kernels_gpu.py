@@ -108,3 +108,38 @@ def test_calibration_kernels_against_the_reference_kernels(ref_ext, oracle, cuda
     assert torch.equal(v_cpu, v_ref.cpu())                  # the oracle restates the kernel's summation order
     tol = 2e-6 if dtype == torch.float32 else 8e-3
     assert torch.allclose(v_mine.float(), v_ref.float(), rtol=tol, atol=0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nb,period", [(64, 512), (33, 24), (5, 4096), (17, 130)])
+def test_packed_4bit_codes_against_the_reference_kernels(ref_ext, oracle, cuda_device, dtype, nb, period):
+    """packed_indices=True: two 4-bit codes per byte, a 16-entry codebook (reference:
+    automatic_gefen_fused_kernel.cu:14-57). Bit-identical codes, magnitudes and parameters for the
+    AdamW step and for GefenMuon's momentum."""
+    from gefen_b200.kernels.automatic_gefen_fused import (
+        automatic_gefen_fused_update_from_vmean_cuda,
+        automatic_gefen_muon_momentum_cuda,
+    )
+
+    cb = torch.sort(torch.tanh(torch.linspace(-2.0, 2.0, 16))).values.float().contiguous()
+    cb[0], cb[-1] = -1.0, 1.0
+    dcb = cb.to(cuda_device)
+    p, g, _, mag, v = _state(nb, period, dtype, seed=nb * 7 + period)
+    gen = torch.Generator().manual_seed(nb + period)
+    packed = torch.randint(0, 256, (nb * period // 2,), dtype=torch.uint8, generator=gen)
+    args = (0.9, 3e-4, 1 - 0.9 ** 3, 1 - 0.999 ** 3, 1e-8)
+    rp, rg, rc, rm, rv = (t.clone().to(cuda_device) for t in (p, g, packed, mag, v))
+    mp, mg, mc, mm, mv = (t.clone().to(cuda_device) for t in (p, g, packed, mag, v))
+    op, oc, om = p.clone(), packed.clone(), mag.clone()
+    for _ in range(3):
+        ref_ext.automatic_gefen_fused_update_from_vmean_cuda(rp, rg, rc, rm, rv, dcb, True, *args)
+        automatic_gefen_fused_update_from_vmean_cuda(mp, mg, mc, mm, mv, dcb, True, *args)
+        oracle.automatic_gefen_fused_update_from_vmean(op, g, oc, om, v, cb, True, *args)
+        torch.cuda.synchronize()
+        assert torch.equal(mc, rc) and torch.equal(mm, rm) and torch.equal(mp, rp)
+        assert torch.equal(oc, rc.cpu()) and torch.equal(om, rm.cpu()) and torch.equal(op, rp.cpu())
+    out_r, out_m = torch.empty_like(rg), torch.empty_like(mg)
+    ref_ext.automatic_gefen_muon_momentum_cuda(rg, rc, rm, dcb, out_r, True, 0.95)
+    automatic_gefen_muon_momentum_cuda(mg, mc, mm, dcb, out_m, True, 0.95)
+    torch.cuda.synchronize()
+    assert torch.equal(mc, rc) and torch.equal(mm, rm) and torch.equal(out_m, out_r)
