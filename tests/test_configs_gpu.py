@@ -69,15 +69,16 @@ def test_config3_flat_tensor_against_oracle(oracle, cuda_device, log2n):
     assert rel_l2(p_gpu.detach().cpu(), p_cpu) <= 1e-6
 
 
-def test_config3_flat_2pow28_properties(cuda_device):
-    """2^28 elements: too slow for the CPU oracle, so the invariants of one step are checked with torch
+@pytest.mark.parametrize("log2n", [28, 30])
+def test_config3_flat_large_properties(cuda_device, log2n):
+    """2^28 and 2^30 elements: too slow for the CPU oracle, so the invariants of one step are checked with torch
     on the GPU: stored magnitude == absmax of beta1*0 + (1-beta1)*g per block (first step), codes
     dequantise to within half a codebook gap of the normalised momentum, parameters move against the
     sign of the gradient."""
     from gefen_b200 import Gefen
 
-    n = 1 << 28
-    gen = torch.Generator(device=cuda_device).manual_seed(28)
+    n = 1 << log2n
+    gen = torch.Generator(device=cuda_device).manual_seed(log2n)
     scale = torch.exp(torch.randn(n // 4096, 1, generator=gen, device=cuda_device))
     grad = (torch.randn(n // 4096, 4096, generator=gen, device=cuda_device) * scale).reshape(-1)
     p = torch.nn.Parameter(torch.zeros(n, device=cuda_device))
@@ -89,12 +90,16 @@ def test_config3_flat_2pow28_properties(cuda_device):
     m = (1.0 - torch.tensor(0.9, dtype=torch.float32)).item() * grad.view(-1, 2048)
     assert torch.equal(st["m_magnitude"].view(-1), m.abs().amax(dim=1))
     cb = opt._gefen_codebook
-    deq = cb[st["m_codebook"].long()]
-    gap = (cb[1:] - cb[:-1]).max()
-    assert float((deq - m / st["m_magnitude"]).abs().max()) <= 0.5 * float(gap) + 1e-6
+    gap = float((cb[1:] - cb[:-1]).max())
     moved = p.detach().view(-1, 2048)
-    big = m.abs() > 0.3 * st["m_magnitude"]
-    assert bool((torch.sign(moved[big]) == -torch.sign(m[big])).all())
+    rows = m.shape[0]
+    for r0 in range(0, rows, 1 << 15):          # in slices: the int64 index tensor of 2^30 codes would not fit
+        sl = slice(r0, min(rows, r0 + (1 << 15)))
+        deq = cb[st["m_codebook"][sl].long()]
+        x = m[sl] / st["m_magnitude"][sl]
+        assert float((deq - x).abs().max()) <= 0.5 * gap + 1e-6
+        big = m[sl].abs() > 0.3 * st["m_magnitude"][sl]
+        assert bool((torch.sign(moved[sl][big]) == -torch.sign(m[sl][big])).all())
 
 
 def test_config2_llama_layer_multi_tensor_equals_per_tensor(cuda_device):
@@ -121,3 +126,31 @@ def test_config2_llama_layer_multi_tensor_equals_per_tensor(cuda_device):
         assert torch.equal(sa["m_codebook"], sb["m_codebook"])
         assert torch.equal(sa["m_magnitude"], sb["m_magnitude"])
         assert rel_l2(pa.detach().float().cpu(), pb.detach().float().cpu()) <= 2e-3
+
+
+def test_config4_llama_32b_layer_multi_tensor_equals_per_tensor(cuda_device):
+    """One layer of the Llama-32B set (6656-wide projections, 17920-wide MLP: periods 1664 and 1120, not
+    powers of two) plus its norms, bf16: the multi-tensor launch against the per-tensor entry points."""
+    from gefen_b200 import Gefen
+
+    shapes = workloads.llama_32b()[1:10]
+    params_a = [torch.nn.Parameter(workloads.init_param(n, s, i, torch.bfloat16, cuda_device)) for i, (n, s) in enumerate(shapes)]
+    params_b = [torch.nn.Parameter(p.detach().clone()) for p in params_a]
+    fused = Gefen(params_a, lr=1.5e-4, weight_decay=0.1, fused=True)
+    per_tensor = Gefen(params_b, lr=1.5e-4, weight_decay=0.1, fused=False)
+    for step in range(2):
+        for i, (pa, pb, (_, s)) in enumerate(zip(params_a, params_b, shapes)):
+            g = workloads.make_grad(s, i, step, torch.bfloat16, cuda_device)
+            pa.grad, pb.grad = g, g.clone()
+        fused.step()
+        per_tensor.step()
+    assert torch.equal(fused._gefen_codebook, per_tensor._gefen_codebook)
+    periods = set()
+    for pa, pb in zip(params_a, params_b):
+        sa, sb = fused.state[pa], per_tensor.state[pb]
+        periods.add(sa["automatic_period"])
+        assert sa["automatic_period"] == sb["automatic_period"]
+        assert torch.equal(sa["m_codebook"], sb["m_codebook"])
+        assert torch.equal(sa["m_magnitude"], sb["m_magnitude"])
+        assert rel_l2(pa.detach().float().cpu(), pb.detach().float().cpu()) <= 2e-3
+    assert periods & {1664, 1120, 3328, 2240, 6656, 8960, 17920} or max(periods) > 1024
