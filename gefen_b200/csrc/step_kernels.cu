@@ -11,17 +11,21 @@
 //   p_i  -= cb[code'_i] * mag' * step * lr,   step = (1/bc1) / (sqrt(v/bc2) + eps)
 //
 // Two kernels:
-//  * step_vec_kernel  - the fast path. One warp owns one block. Codes and gradients are read once
+//  * step_vec_kernel  - the fast path. One warp owns one block (several blocks when they are
+//    shorter than 256 elements). Codes and gradients are read once
 //    (128-bit loads), the updated momenta wait in the warp's slice of shared memory while the
 //    block's absmax is reduced with shuffles, then they are re-encoded and the parameters updated:
 //    codes, gradients and params cross HBM exactly once (8 B/element in bf16, 14 B/element in
 //    fp32). Codebook, thresholds and the quantisation table arrive in shared memory by one bulk
 //    (TMA) copy per CTA. No __syncthreads after set-up; the loops are short so the code stays in
 //    the instruction cache.
-//  * step_generic_kernel - any period, alignment and dtype (fp64 included): two passes with
-//    scalar accesses, the second pass re-reading from L1/L2.
+//  * step_generic_kernel - any period, alignment and dtype (fp64 included), period-1 tensors and
+//    4-bit packed codes: two passes with scalar accesses, the second pass re-reading from L1/L2.
 // Both take their tensors from a descriptor table (one launch for many tensors); a single-tensor
-// call passes a one-row table inside the kernel parameters.
+// call passes a one-row table inside the kernel parameters. For data-parallel ranks whose buffers
+// are mapped into each other's address space the kernels can also store every updated parameter
+// to the peers' copies (the all-gather) and average the gradients over the peers' copies while
+// reading them (the reduce-scatter): see StepLaunch.
 #include "common.cuh"
 
 #include <mutex>

@@ -166,8 +166,8 @@ int gefen_b200_multi_tensor_step_peers(gefen_b200_step_tensor_t* host_table, voi
                                        void* stream);
 /* sizeof(gefen_b200_step_tensor_t) as compiled, for binding-side layout checks. */
 int gefen_b200_step_tensor_size(void);
-/* Kernel class the library would use for one table entry: 1..8 = vectorised path with that many
- * 8-element chunks per lane, 0 = generic warp-per-block, -1 = generic CTA-per-block. Rows of equal
+/* Kernel class the library would use for one table entry: 1 = vectorised staged path,
+ * 0 = generic warp-per-block, -1 = generic CTA-per-block. Rows of equal
  * class that are adjacent in the table share one launch. */
 int gefen_b200_step_tensor_class(const gefen_b200_step_tensor_t* host_entry, int param_dtype);
 
