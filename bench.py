@@ -209,18 +209,24 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     # first step = calibration (period scan, histogram, exact-DP codebook) + one optimizer step
     calibration_ms = timed(step, 1)
     warm = max(args.warmup - 1, 2)
+    sampler = ClockSampler(local_rank)
+    sampler.start()   # nvidia-smi needs a moment to start: begin before the warm-up
     for _ in range(warm):
         step()
-    sampler = ClockSampler(local_rank)
     if world > 1:
         dist.barrier()
-    sampler.start()
     ms = timed(step, args.steps)
-    clocks = sampler.stop()
     if world > 1:
         t = torch.tensor([ms], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t)
+    # the timed region is a few tens of milliseconds, shorter than the sampling period: keep the same
+    # load running (untimed, the same count on every rank) until the sampler has seen it
+    for _ in range(int(400.0 / max(ms, 0.05)) + 1):
+        step()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    if world > 1:
         dist.barrier()
 
     if world > 1:
