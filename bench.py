@@ -440,7 +440,7 @@ def run_microbench(spec: str, steps: int, warmup: int):
     Small enough for profiler captures; prints one JSON line."""
     from gefen_b200.kernels.automatic_gefen_fused import automatic_gefen_fused_update_from_vmean_cuda
 
-    if spec.split(":")[0] in ("gemm", "hist", "scan", "ns"):
+    if spec.split(":")[0] in ("gemm", "gram", "hist", "scan", "ns"):
         return run_microbench_other(spec, steps, warmup)
     name, period, blocks = spec.split(":")
     period, blocks = int(period), int(blocks)
@@ -492,6 +492,24 @@ def run_microbench_other(spec: str, steps: int, warmup: int):
         flops = ns_flops((rows, cols))
         out.update({"ms": res["tcgen05"], "tflops": flops / res["tcgen05"] / 1e9, "torch_ms": res["torch"],
                     "torch_tflops": flops / res["torch"] / 1e9})
+        print(json.dumps(out))
+        return
+    if parts[0] == "gram":
+        # gram:M:K - the two symmetric products of a Newton-Schulz step: G = X X^T and b G + c G G
+        from gefen_b200.newton_schulz import check_status, gemm_tn
+
+        M, K = (int(x) for x in parts[1:])
+        x = (torch.randn(M, K, generator=gen, device=dev) / K ** 0.5).bfloat16()
+        g = torch.empty(M, M, dtype=torch.bfloat16, device=dev)
+        poly = torch.empty(M, M, dtype=torch.bfloat16, device=dev)
+        for _ in range(max(warmup, 3)):
+            gemm_tn(x, x, out=g, symmetric=True)
+            gemm_tn(g, g, c=g, alpha=2.0315, beta=-4.775, out=poly, symmetric=True)
+        ms1 = timed(lambda: gemm_tn(x, x, out=g, symmetric=True), steps)
+        ms2 = timed(lambda: gemm_tn(g, g, c=g, alpha=2.0315, beta=-4.775, out=poly, symmetric=True), steps)
+        check_status(dev)
+        out.update({"gram_ms": ms1, "gram_tflops": 2.0 * M * M * K / ms1 / 1e9, "poly_ms": ms2,
+                    "poly_tflops": 2.0 * M * M * M / ms2 / 1e9})
         print(json.dumps(out))
         return
     if parts[0] == "gemm":

@@ -291,7 +291,7 @@ __global__ void __launch_bounds__(kGemmThreads, (STAGES * (kBM + BN) * kBK * 2 <
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (!ok || abort_flag) break;
         {
-#pragma unroll 1
+#pragma unroll 2
             for (int j = 0; j < BN / 32; ++j) {
                 uint32_t r[32];
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(buf * BN + j * 32);
