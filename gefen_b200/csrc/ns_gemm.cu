@@ -26,7 +26,9 @@
 #include <stdlib.h>
 
 #include <cuda.h>
+#include <map>
 #include <mutex>
+#include <tuple>
 
 namespace gefen {
 
@@ -557,11 +559,8 @@ static int ns_gemm(const void* a, bool a_is_km, const void* b, bool b_is_kn, con
 
 // The whole Newton-Schulz iteration of one matrix, enqueued from native code (fifteen GEMM launches
 // for five steps) so that the host cost per product is a tensor-map encode and a launch.
-extern "C" int gefen_b200_newton_schulz(void* x0, void* x1, void* gram, void* poly, int rows, int cols, int steps,
-                                        double a, double b, double c, int* status, void* stream) {
-    GEFEN_CHECK_ARG(x0 && x1 && gram && poly, "Expected non-null buffers.");
-    GEFEN_CHECK_ARG(rows > 0 && cols > 0 && rows % 8 == 0 && cols % 8 == 0, "Expected dimensions that are multiples of 8.");
-    GEFEN_CHECK_ARG(steps >= 0 && steps < 100, "Number of steps must be less than 100.");
+static int enqueue_newton_schulz(void* x0, void* x1, void* gram, void* poly, int rows, int cols, int steps, double a,
+                                 double b, double c, int* status, void* stream) {
     const int m = rows < cols ? rows : cols;
     void* cur = x0;
     void* nxt = x1;
@@ -586,6 +585,81 @@ extern "C" int gefen_b200_newton_schulz(void* x0, void* x1, void* gram, void* po
         }
         void* t = cur; cur = nxt; nxt = t;
     }
+    return GEFEN_B200_OK;
+}
+
+// The chain is the same fifteen launches whenever buffers, shape and coefficients repeat (an optimizer
+// calls it for every matrix of a shape with the same scratch buffers, every step): from the second
+// identical call on it is replayed as one CUDA graph, which shortens the gaps between the dependent
+// launches. The first call runs eagerly (it also configures the kernels); the capture happens on a
+// private stream in thread-local mode, and the graph is launched into the caller's stream.
+// GEFEN_B200_NS_GRAPH=0 keeps every call eager.
+namespace {
+struct ChainKey {
+    int dev, rows, cols, steps;
+    void *x0, *x1, *gram, *poly, *status;
+    double a, b, c;
+    bool operator<(const ChainKey& o) const {
+        return std::tie(dev, rows, cols, steps, x0, x1, gram, poly, status, a, b, c) <
+               std::tie(o.dev, o.rows, o.cols, o.steps, o.x0, o.x1, o.gram, o.poly, o.status, o.a, o.b, o.c);
+    }
+};
+std::mutex g_chain_mutex;
+std::map<ChainKey, cudaGraphExec_t> g_chain_graphs;   // nullptr: seen once, not captured yet
+cudaStream_t g_capture_stream[64];
+constexpr size_t kMaxChainGraphs = 64;
+}  // namespace
+
+extern "C" int gefen_b200_newton_schulz(void* x0, void* x1, void* gram, void* poly, int rows, int cols, int steps,
+                                        double a, double b, double c, int* status, void* stream) {
+    GEFEN_CHECK_ARG(x0 && x1 && gram && poly, "Expected non-null buffers.");
+    GEFEN_CHECK_ARG(rows > 0 && cols > 0 && rows % 8 == 0 && cols % 8 == 0, "Expected dimensions that are multiples of 8.");
+    GEFEN_CHECK_ARG(steps >= 0 && steps < 100, "Number of steps must be less than 100.");
+    static int use_graphs = -1;
+    if (use_graphs < 0) {
+        const char* e = getenv("GEFEN_B200_NS_GRAPH");
+        use_graphs = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    int dev = 0;
+    GEFEN_CHECK_CUDA(cudaGetDevice(&dev));
+    if (!use_graphs || steps == 0 || dev < 0 || dev >= 64)
+        return enqueue_newton_schulz(x0, x1, gram, poly, rows, cols, steps, a, b, c, status, stream);
+
+    const ChainKey key{dev, rows, cols, steps, x0, x1, gram, poly, status, a, b, c};
+    std::lock_guard<std::mutex> lock(g_chain_mutex);
+    auto it = g_chain_graphs.find(key);
+    if (it == g_chain_graphs.end()) {
+        if (g_chain_graphs.size() >= kMaxChainGraphs) {   // callers whose buffers keep moving: start over
+            for (auto& kv : g_chain_graphs)
+                if (kv.second != nullptr) cudaGraphExecDestroy(kv.second);
+            g_chain_graphs.clear();
+        }
+        g_chain_graphs[key] = nullptr;
+        return enqueue_newton_schulz(x0, x1, gram, poly, rows, cols, steps, a, b, c, status, stream);
+    }
+    if (it->second == nullptr) {
+        if (g_capture_stream[dev] == nullptr)
+            GEFEN_CHECK_CUDA(cudaStreamCreateWithFlags(&g_capture_stream[dev], cudaStreamNonBlocking));
+        cudaStream_t cs = g_capture_stream[dev];
+        cudaGraph_t graph = nullptr;
+        cudaGraphExec_t exec = nullptr;
+        bool ok = cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+        if (ok) {
+            const int rc = enqueue_newton_schulz(x0, x1, gram, poly, rows, cols, steps, a, b, c, status, cs);
+            const cudaError_t end = cudaStreamEndCapture(cs, &graph);
+            ok = rc == GEFEN_B200_OK && end == cudaSuccess && graph != nullptr;
+        }
+        if (ok) ok = cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess;
+        if (graph != nullptr) cudaGraphDestroy(graph);
+        if (!ok) {   // leave this chain eager for good
+            cudaGetLastError();
+            g_chain_graphs.erase(it);
+            use_graphs = 0;
+            return enqueue_newton_schulz(x0, x1, gram, poly, rows, cols, steps, a, b, c, status, stream);
+        }
+        it->second = exec;
+    }
+    GEFEN_CHECK_CUDA(cudaGraphLaunch(it->second, static_cast<cudaStream_t>(stream)));
     return GEFEN_B200_OK;
 }
 

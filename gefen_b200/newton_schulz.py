@@ -129,15 +129,18 @@ def zeropower_via_newtonschulz(grad: torch.Tensor, ns_coefficients: Tuple[float,
             x = torch.addmm(x, gram_update, x, beta=a)
         return x.T if transposed else x
 
-    # bf16 norm and quotient, as the reference's div_ (the Frobenius norm does not care about orientation)
-    x = (x / x.norm().clamp(min=eps)).contiguous()
+    # bf16 norm and quotient, as the reference's div_ (the Frobenius norm does not care about orientation).
+    # Both iterates live in the per-device scratch: the same addresses for every matrix of a shape, which
+    # lets the native driver replay the chain of products as one graph.
     m = min(rows, cols)
-    scratch = _scratch(x.device, 2 * m * m + rows * cols)
+    scratch = _scratch(x.device, 2 * m * m + 2 * rows * cols)
     gram = scratch[: m * m]
     poly = scratch[m * m: 2 * m * m]
-    nxt = scratch[2 * m * m:].view(rows, cols)
+    nxt = scratch[2 * m * m: 2 * m * m + rows * cols].view(rows, cols)
+    first = scratch[2 * m * m + rows * cols: 2 * m * m + 2 * rows * cols].view(rows, cols)
+    x = torch.div(x, x.norm().clamp(min=eps), out=first)
     with _lib.device_guard(x.device):
         _lib.check(_lib.load().gefen_b200_newton_schulz(
             _lib.ptr(x), _lib.ptr(nxt), _lib.ptr(gram), _lib.ptr(poly), rows, cols, int(ns_steps), float(a), float(b),
             float(c), _lib.ptr(_status(x.device)), _lib.current_stream(x.device)))
-    return x if ns_steps % 2 == 0 else nxt.clone()
+    return (x if ns_steps % 2 == 0 else nxt).clone()
