@@ -128,12 +128,13 @@ __device__ __forceinline__ int find_tensor(const gefen_b200_step_tensor_t* table
 }
 
 // --------------------------------------------------------------------------- vector IO
-// A "chunk" is 8 consecutive elements: 8 code bytes, 16 B of bf16/f16 or 32 B of fp32.
+// A "chunk" is 8 consecutive elements: 8 code bytes, 16 B of bf16/f16 or 32 B of fp32. Everything is
+// read once per step: the loads carry the streaming (evict-first) hint.
 template <typename S> struct Chunk;
 template <> struct Chunk<__nv_bfloat16> {
     uint4 raw;
     __device__ __forceinline__ void load(const void* base, long long chunk) {
-        raw = reinterpret_cast<const uint4*>(base)[chunk];
+        raw = __ldcs(reinterpret_cast<const uint4*>(base) + chunk);
     }
     __device__ __forceinline__ void store(void* base, long long chunk) const {
         reinterpret_cast<uint4*>(base)[chunk] = raw;
@@ -159,7 +160,7 @@ template <> struct Chunk<__nv_bfloat16> {
 template <> struct Chunk<__half> {
     uint4 raw;
     __device__ __forceinline__ void load(const void* base, long long chunk) {
-        raw = reinterpret_cast<const uint4*>(base)[chunk];
+        raw = __ldcs(reinterpret_cast<const uint4*>(base) + chunk);
     }
     __device__ __forceinline__ void store(void* base, long long chunk) const {
         reinterpret_cast<uint4*>(base)[chunk] = raw;
@@ -186,12 +187,12 @@ template <> struct Chunk<__half> {
 template <> struct Chunk<float> {
     float4 lo, hi;
     __device__ __forceinline__ void load(const void* base, long long chunk) {
-        lo = reinterpret_cast<const float4*>(base)[2 * chunk];
-        hi = reinterpret_cast<const float4*>(base)[2 * chunk + 1];
+        lo = __ldcs(reinterpret_cast<const float4*>(base) + 2 * chunk);
+        hi = __ldcs(reinterpret_cast<const float4*>(base) + 2 * chunk + 1);
     }
     __device__ __forceinline__ void store(void* base, long long chunk) const {
-        reinterpret_cast<float4*>(base)[2 * chunk] = lo;
-        reinterpret_cast<float4*>(base)[2 * chunk + 1] = hi;
+        __stcs(reinterpret_cast<float4*>(base) + 2 * chunk, lo);   // measured: streaming stores pay for fp32 only
+        __stcs(reinterpret_cast<float4*>(base) + 2 * chunk + 1, hi);
     }
     __device__ __forceinline__ void unpack(float (&f)[8]) const {
         f[0] = lo.x; f[1] = lo.y; f[2] = lo.z; f[3] = lo.w;
@@ -264,7 +265,7 @@ __device__ __forceinline__ void first_pass_group(const S* g_blk, const uint2* co
     for (int u = 0; u < U; ++u) {
         const int c = c0 + LANES * u;
         if (!GUARD || c < nchunks) {
-            craw[u] = codes_in[c];
+            craw[u] = __ldcs(codes_in + c);
             graw[u].load(g_blk, c);
         }
     }
