@@ -304,9 +304,9 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     result["roofline"] = {"bound": "hbm", "kernel": "step_vec_kernel<bf16>" if elem_bytes == 2 else "step_vec_kernel<f32>",
                           "achieved": achieved, "peak": peak, "peak_kind": peak_kind + " copy bandwidth, burst",
                           "unit": "GB/s", "frac": achieved / peak,
-                          # dram read+write of one launch: 1.044 x algorithmic, scaled from the ncu capture of a
+                          # dram read+write of one launch: 0.971 x algorithmic, scaled from the ncu capture of a
                           # 134 M-element launch of the same kernel (profiles/step_vec_kernel_bf16_period2048.md)
-                          "traffic": 1.044 * vec_bytes if elem_bytes == 2 else None,
+                          "traffic": 0.971 * vec_bytes if elem_bytes == 2 else None,
                           "algorithmic_bytes_per_launch": vec_bytes, "launch_ms": vec_ms}
     result["launches_per_step"] = len(set(cls))
 
