@@ -286,9 +286,17 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     table = next(t for t in opt._plan.tables)
     rows = table["rows"]
     cls = [lib.gefen_b200_step_tensor_class(rows[r:r + 1].ctypes.data, table["tag"]) for r in range(len(rows))]
-    vec_rows = rows[[r for r, c in enumerate(cls) if c == 1]].copy()
-    vec_bytes = int(sum(int(r["num_blocks"]) * int(r["period"]) * (3 * elem_bytes + 2) + int(r["num_blocks"]) * 4 * elem_bytes
-                        for r in vec_rows))
+    def row_bytes(r):
+        return int(r["num_blocks"]) * int(r["period"]) * (3 * elem_bytes + 2) + int(r["num_blocks"]) * 4 * elem_bytes
+
+    # the dominant kernel = the launch (one per kernel class) that moves the most bytes
+    by_class = {}
+    for r, c in enumerate(cls):
+        if c >= 1:
+            by_class[c] = by_class.get(c, 0) + row_bytes(rows[r])
+    top_class = max(by_class, key=by_class.get)
+    vec_rows = rows[[r for r, c in enumerate(cls) if c == top_class]].copy()
+    vec_bytes = int(sum(row_bytes(r) for r in vec_rows))
     dev_table = torch.empty(vec_rows.nbytes, dtype=torch.uint8, device=device)
     ws = _lib.codebook_workspace(opt._gefen_codebook)
 

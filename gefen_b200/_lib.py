@@ -75,6 +75,8 @@ def _declare(lib):
         "gefen_b200_multi_tensor_step_peers": (i32, [vp, vp, i32, i32, vp, vp, i32, vp, i32, dbl, vp]),
         "gefen_b200_step_tensor_size": (i32, []),
         "gefen_b200_step_tensor_class": (i32, [vp, i32]),
+        "gefen_b200_step_status": (i32, [vp, i32]),
+        "gefen_b200_debug_set_stage_spin_limit": (i32, [i64]),
         "gefen_b200_exact_histogram": (i32, [vp, i32, i64, i64, vp, i32, vp]),
         "gefen_b200_average_within_block_variance": (i32, [vp, i32, i64, i64, i32, vp, vp]),
         "gefen_b200_average_within_block_coefficient_of_variation": (i32, [vp, i32, i64, i64, i32, vp, vp]),
@@ -132,6 +134,22 @@ def check(rc: int) -> None:
 
 def ptr(t):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def step_status(device, clear: bool = True) -> int:
+    """Status word of the step kernels on `device` (synchronises it): non-zero when a bounded wait
+    inside a step kernel ran out since the last clear, i.e. a step was left incomplete."""
+    value = ctypes.c_int(0)
+    with device_guard(device):
+        check(load().gefen_b200_step_status(ctypes.byref(value), int(clear)))
+    return int(value.value)
+
+
+def check_step_status(device) -> None:
+    """Raises GefenB200Error if a step kernel on `device` gave up a bounded wait (synchronises)."""
+    if step_status(device, clear=True) != 0:
+        raise GefenB200Error("a Gefen step kernel gave up waiting for its staged codebook tables; the optimizer "
+                             "state and parameters of that step are incomplete")
 
 
 def current_stream(device) -> ctypes.c_void_p:

@@ -64,7 +64,16 @@ struct StepLaunch {
     int n_grad_srcs;
     float grad_scale;
     long long grad_delta[GEFEN_B200_MAX_PEERS + 1];
+    // register-resident path: warps that share one block (see step_reg_kernel)
+    int warps_per_block;
+    // iteration limit of the wait for the staged tables (g_stage_spin_limit on the host)
+    unsigned int spin_limit;
 };
+
+// Set (never cleared by a kernel) when a bounded wait ran out and the CTA left without doing its
+// share of the step: bit 0 = the table staging of a step kernel. Read and cleared by
+// gefen_b200_step_status on the host.
+__device__ int g_step_status;
 
 template <typename T> __device__ __forceinline__ T* peer_ptr(T* p, long long delta) {
     return reinterpret_cast<T*>(reinterpret_cast<uintptr_t>(p) + delta);
@@ -87,8 +96,12 @@ struct SmemView {
 };
 
 // Stages the workspace with one bulk copy. Returns false (uniformly for the CTA) if the copy did
-// not land within the bounded wait.
-__device__ __forceinline__ bool stage_tables(const unsigned char* ws, unsigned char* smem, SmemView& view) {
+// not land within `spin_limit` polls of its barrier; the status word is raised then, and the CTA
+// still gives the copy a second, long bounded wait before it returns, so that it does not leave
+// while a copy into its shared memory is in flight.
+constexpr unsigned int kStageDrainLimit = 4000000u;
+__device__ __forceinline__ bool stage_tables(const unsigned char* ws, unsigned char* smem, SmemView& view,
+                                             unsigned int spin_limit) {
     __shared__ uint64_t bar;
     __shared__ int ok;
     if (threadIdx.x == 0) {
@@ -99,7 +112,11 @@ __device__ __forceinline__ bool stage_tables(const unsigned char* ws, unsigned c
     if (threadIdx.x == 0) {
         mbar_expect_tx(&bar, kSmemWs);
         bulk_copy_g2s(smem, ws, kSmemWs, &bar);
-        ok = mbar_wait_bounded(&bar, 0) ? 1 : 0;
+        ok = mbar_wait_bounded(&bar, 0, spin_limit) ? 1 : 0;
+        if (!ok) {
+            atomicOr(&g_step_status, 1);
+            mbar_wait_bounded(&bar, 0, kStageDrainLimit);
+        }
     }
     __syncthreads();
     view.cb = reinterpret_cast<const float*>(smem + kWsCodebookOff);
@@ -563,7 +580,7 @@ __global__ void __launch_bounds__(vec_max_threads<S, REDUCE>(), 1) step_vec_kern
                                                            const __grid_constant__ gefen_b200_step_tensor_t single) {
     extern __shared__ __align__(128) unsigned char smem[];
     SmemView s;
-    if (!stage_tables(L.ws, smem, s)) return;
+    if (!stage_tables(L.ws, smem, s, L.spin_limit)) return;
     const gefen_b200_step_tensor_t* table = L.table != nullptr ? L.table : &single;
 
     const int lane = threadIdx.x & 31;
@@ -603,6 +620,338 @@ __global__ void __launch_bounds__(vec_max_threads<S, REDUCE>(), 1) step_vec_kern
     }
 }
 
+// --------------------------------------------------------------------------- register-resident path
+// Blocks of 512 to 8192 elements (a multiple of 8). W = ceil(period / 512) consecutive warps of a
+// CTA own one block; every lane holds two chunks (16 elements) of it, and the updated momenta stay
+// in registers between the absmax reduction and the re-encoding: nothing is staged in shared
+// memory, so the warps per SM are bound by registers only, and the loops are two chunks long. The
+// warps of a block meet once per block at a named barrier after exchanging their partial absmax
+// and sum of squares through shared memory. Codes, gradients and the old magnitude of the group's
+// NEXT block are requested before the current block is worked on (2-byte types), so that a block
+// never starts on a global-load wait.
+// The codebook is replicated per lane in rows of 256 bytes (entry e of lane l at byte 256 e + 4 l):
+// the byte offset of a lookup is one byte permute of the code with the lane's offset.
+constexpr int kRegChunksPerLane = 2;
+constexpr int kRegRowBytes = 256;
+constexpr int kSmemWsPadded = (kSmemWs + 255) / 256 * 256;
+constexpr int kSmemRepWide = kMaxCodebook * kRegRowBytes;
+constexpr int kRegMaxWarpsPerBlock = 16;
+constexpr int kRegMaxGroups = 12;       // groups that exchange through shared memory (W >= 2)
+constexpr int kRegMinPeriod = 512;
+constexpr int kRegMaxPeriod = 512 * kRegMaxWarpsPerBlock;
+
+__host__ __device__ __forceinline__ int reg_warps_per_block(long long period) {
+    return static_cast<int>((period + 511) / 512);
+}
+
+__device__ __forceinline__ void group_barrier(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// cb[code] for this lane: `word` holds the code in byte `BYTE`, lane4 = 4 * lane.
+template <int BYTE>
+__device__ __forceinline__ float rep_lookup(const unsigned char* rep, uint32_t word, uint32_t lane4) {
+    const uint32_t off = __byte_perm(word, lane4, 0x5504u | (static_cast<uint32_t>(BYTE) << 4));
+    return *reinterpret_cast<const float*>(rep + off);
+}
+
+__device__ __forceinline__ float round_state(float value, int dtype) {
+    if (dtype == GEFEN_B200_F32) return value;
+    if (dtype == GEFEN_B200_BF16) return __bfloat162float(__float2bfloat16_rn(value));
+    return __half2float(__float2half_rn(value));
+}
+
+// What a warp holds of a block before it works on it.
+template <typename S>
+struct RegBlockInputs {
+    uint2 codes[kRegChunksPerLane];
+    Chunk<S> grads[kRegChunksPerLane];
+    float old_mag;
+};
+
+template <typename S>
+__device__ __forceinline__ void reg_request(const gefen_b200_step_tensor_t& t, long long b, int wg, int lane,
+                                            RegBlockInputs<S>& in) {
+    const int period = static_cast<int>(t.period);
+    const int nchunks = period >> 3;
+    const long long elem0 = b * static_cast<long long>(period);
+    const uint2* codes = reinterpret_cast<const uint2*>(t.codes + elem0);
+    const S* g_blk = static_cast<const S*>(t.g) + elem0;
+#pragma unroll
+    for (int u = 0; u < kRegChunksPerLane; ++u) {
+        const int c = (wg * kRegChunksPerLane + u) * 32 + lane;
+        if (c < nchunks) {
+            in.codes[u] = __ldcs(codes + c);
+            in.grads[u].load(g_blk, c);
+        }
+    }
+    in.old_mag = load_state(t.mag, b, t.mag_dtype);
+}
+
+template <typename S>
+__device__ __forceinline__ void reg_block_step(const gefen_b200_step_tensor_t& t, long long b, const StepLaunch& L,
+                                               const unsigned char* smem, const SmemView& s,
+                                               const RegBlockInputs<S>& in, int W, int wg, int grp, int lane,
+                                               float2 (*xchg)[kRegMaxWarpsPerBlock], float (*xchg_exact)[kRegMaxWarpsPerBlock]) {
+    constexpr int CPL = kRegChunksPerLane;
+    const unsigned char* const rep = smem + kSmemWsPadded;
+    const unsigned char* const lut = smem + kWsLutOff;
+    const uint32_t lane4 = static_cast<uint32_t>(lane) << 2;
+    const int period = static_cast<int>(t.period);
+    const int nchunks = period >> 3;
+    const long long elem0 = b * static_cast<long long>(period);
+    uint2* const codes_out = reinterpret_cast<uint2*>(t.codes + elem0);
+    const S* const g_blk = static_cast<const S*>(t.g) + elem0;
+    S* const p_blk = static_cast<S*>(t.p) + elem0;
+    const uint32_t flags = t.flags;
+    const bool muon = (flags & GEFEN_B200_STEP_MUON) != 0;
+    const float beta1 = t.beta1;
+    const float omb1 = 1.0f - beta1;
+    const float lr = t.lr;
+    const bool do_update = muon || lr != 0.0f;
+    const bool load_p = !muon && do_update;
+    const float old_mag = in.old_mag;
+
+    int chunk[CPL];
+    bool ok[CPL];
+    Chunk<S> praw[CPL];
+#pragma unroll
+    for (int u = 0; u < CPL; ++u) {
+        chunk[u] = (wg * CPL + u) * 32 + lane;
+        ok[u] = chunk[u] < nchunks;
+        if (load_p && ok[u]) praw[u].load(p_blk, chunk[u]);
+    }
+    float v_in = 1.0f;
+    if (!muon) v_in = L.stepsize != nullptr ? L.stepsize[b] : load_state(t.v, b, t.v_dtype);
+
+    // ---- moment update; the momenta stay in registers
+    float m[CPL * 8];
+    float absmax = 0.0f, sumsq = 0.0f;
+#pragma unroll
+    for (int u = 0; u < CPL; ++u) {
+        if (ok[u]) {
+            float g[8];
+            in.grads[u].unpack(g);
+            const uint32_t c0 = in.codes[u].x, c1 = in.codes[u].y;
+            const float cbv[8] = {rep_lookup<0>(rep, c0, lane4), rep_lookup<1>(rep, c0, lane4), rep_lookup<2>(rep, c0, lane4),
+                                  rep_lookup<3>(rep, c0, lane4), rep_lookup<0>(rep, c1, lane4), rep_lookup<1>(rep, c1, lane4),
+                                  rep_lookup<2>(rep, c1, lane4), rep_lookup<3>(rep, c1, lane4)};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float cur = old_mag * cbv[i];
+                const float mi = ema_update(beta1, cur, omb1, g[i]);
+                m[u * 8 + i] = mi;
+                absmax = max_abs_nan(absmax, mi);
+                sumsq = fmaf(g[i], g[i], sumsq);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) m[u * 8 + i] = 0.0f;
+        }
+    }
+    absmax = warp_max_nan(absmax);
+    sumsq = warp_sum(sumsq);
+    if (W > 1) {
+        // partial results of the block's warps, combined in warp order by everyone. Two slots in turn:
+        // a warp can be at most one barrier ahead of the slowest warp of its group.
+        float2* slot = xchg[grp];
+        if (lane == 0) slot[wg] = make_float2(absmax, sumsq);
+        group_barrier(grp + 1, W * 32);
+        absmax = 0.0f;
+        sumsq = 0.0f;
+        for (int w = 0; w < W; ++w) {
+            const float2 part = slot[w];
+            asm("max.NaN.f32 %0, %1, %2;" : "=f"(absmax) : "f"(absmax), "f"(part.x));
+            sumsq += part.y;
+        }
+    }
+
+    // ---- second moment (optionally fused) and the step size
+    float step = 0.0f;
+    if (!muon) {
+        if (L.stepsize != nullptr) {
+            step = v_in;
+        } else {
+            float v = v_in;
+            if (flags & GEFEN_B200_STEP_FUSE_VMEAN) {
+                const float mean_sq = sumsq / static_cast<float>(period);
+                const float nv = fmaf(t.beta2, v_in, (1.0f - t.beta2) * mean_sq);
+                v = round_state(nv, t.v_dtype);
+                if (wg == 0 && lane == 0) store_state(t.v, b, t.v_dtype, nv);
+            }
+            step = adam_step_size(v, t.bc1, t.bc2, t.eps);
+        }
+    }
+
+    // ---- rare: a NaN or Inf in the block. The reference's max ignores NaN; redo it that way and
+    // let the exact (threshold) quantiser handle non-finite quotients. The test is uniform over the
+    // block's warps: they all hold the same absmax.
+    bool exact_path = false;
+    if (!(absmax <= 3.0e38f)) {
+        float mx = 0.0f;
+#pragma unroll
+        for (int i = 0; i < CPL * 8; ++i) mx = fmaxf(mx, fabsf(m[i]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (W > 1) {
+            float* slot = xchg_exact[grp];
+            if (lane == 0) slot[wg] = mx;
+            group_barrier(grp + 1, W * 32);
+            mx = 0.0f;
+            for (int w = 0; w < W; ++w) mx = fmaxf(mx, slot[w]);
+        }
+        absmax = mx;
+        exact_path = true;
+    }
+    if (wg == 0 && lane == 0) store_state(t.mag, b, t.mag_dtype, absmax);
+
+    const bool nonzero = absmax > 0.0f;
+    const bool fastdiv = !exact_path && div_range_ok(absmax);
+    const float rinv = fastdiv ? 1.0f / absmax : 0.0f;
+    const bool wd = (flags & GEFEN_B200_STEP_WEIGHT_DECAY) != 0;
+    const bool nesterov = (flags & GEFEN_B200_STEP_NESTEROV) != 0;
+    const float wd_mul = t.wd_mul;
+    const float nesterov_alpha = t.beta2;
+    const int n_peers = L.n_peers;
+
+    // ---- re-encode and update
+#pragma unroll
+    for (int u = 0; u < CPL; ++u) {
+        if (!ok[u]) continue;
+        uint32_t code[8];
+        if (fastdiv) {
+            uint32_t any = 0u;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float x = div_by_block_constant(m[u * 8 + i], absmax, rinv);
+                code[i] = lut_query_fast(x, lut);
+                any |= code[i];
+            }
+            if (any & kLutSlowBit) {   // rare: a cell with two thresholds, or values above the last entry
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    if (code[i] & kLutSlowBit) {
+                        const float x = div_by_block_constant(m[u * 8 + i], absmax, rinv);
+                        code[i] = static_cast<uint32_t>(entry_exact(x, s.thr, s.cb, s.k));
+                    }
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float x = 0.0f;
+                if (nonzero) x = m[u * 8 + i] / absmax;
+                code[i] = static_cast<uint32_t>(entry_exact(x, s.thr, s.cb, s.k));
+            }
+        }
+        float q[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = rep_lookup<0>(rep, code[i], lane4) * absmax;
+        uint2 cw;
+        cw.x = __byte_perm(__byte_perm(code[0], code[1], 0x0040), __byte_perm(code[2], code[3], 0x0040), 0x5410);
+        cw.y = __byte_perm(__byte_perm(code[4], code[5], 0x0040), __byte_perm(code[6], code[7], 0x0040), 0x5410);
+        codes_out[chunk[u]] = cw;
+        if (muon) {
+            if (nesterov) {
+                // torch: m.mul_(momentum).add_(g, alpha=1-momentum) on the rounded momentum
+                // (reference: gefen_muon.py:312-314); alpha travels in t.beta2.
+                Chunk<S> g2;
+                g2.load(g_blk, chunk[u]);
+                float g[8];
+                g2.unpack(g);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float m1 = ScalarIO<S>::round(ScalarIO<S>::round(q[i]) * beta1);
+                    q[i] = fmaf(nesterov_alpha, g[i], m1);
+                }
+            }
+            Chunk<S> out;
+            out.pack(q);
+            out.store(p_blk, chunk[u]);
+        } else if (do_update) {
+            float pv[8];
+            praw[u].unpack(pv);
+            if (wd) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) pv[i] *= wd_mul;
+                Chunk<S> rounded;       // the separate multiply of the reference rounds to the parameter dtype
+                rounded.pack(pv);
+                rounded.unpack(pv);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) pv[i] = fmaf(-(q[i] * step), lr, pv[i]);
+            Chunk<S> out;
+            out.pack(pv);
+            out.store(p_blk, chunk[u]);
+            for (int r = 0; r < n_peers; ++r) out.store(peer_ptr(p_blk, L.peer_delta[r]), chunk[u]);
+        }
+    }
+}
+
+template <typename S, int MAXW>
+__global__ void __launch_bounds__(MAXW * 32, 1) step_reg_kernel(const __grid_constant__ StepLaunch L,
+                                                                const __grid_constant__ gefen_b200_step_tensor_t single) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ float2 xchg[2][kRegMaxGroups][kRegMaxWarpsPerBlock];
+    __shared__ float xchg_exact[kRegMaxGroups][kRegMaxWarpsPerBlock];
+    SmemView s;
+    if (!stage_tables(L.ws, smem, s, L.spin_limit)) return;
+    const gefen_b200_step_tensor_t* table = L.table != nullptr ? L.table : &single;
+    {
+        float* rep = reinterpret_cast<float*>(smem + kSmemWsPadded);
+        for (int i = threadIdx.x; i < kMaxCodebook * 32; i += blockDim.x) rep[(i >> 5) * (kRegRowBytes / 4) + (i & 31)] = s.cb[i >> 5];
+        __syncthreads();
+    }
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int W = L.warps_per_block;
+    const int grp = warp / W;
+    const int wg = warp - grp * W;
+    const int groups = static_cast<int>(blockDim.x >> 5) / W;
+    const long long stride = static_cast<long long>(gridDim.x) * groups;
+    long long gb = static_cast<long long>(blockIdx.x) * groups + grp;
+    if (gb >= L.total_blocks) return;   // the whole group leaves together
+
+    // the tensor that owns a global block index; consecutive blocks of a group mostly share it
+    const gefen_b200_step_tensor_t* tp = table;
+    long long t_first = tp->first_block, t_count = tp->num_blocks;
+    auto locate = [&](long long block) {
+        if (block < t_first || block >= t_first + t_count) {
+            tp = table + find_tensor(table, L.n_tensors, block);
+            t_first = tp->first_block;
+            t_count = tp->num_blocks;
+        }
+    };
+    constexpr bool kAhead = sizeof(S) == 2;   // request the next block's inputs one block ahead
+    locate(gb);
+    const gefen_b200_step_tensor_t* cur = tp;
+    long long b = gb - t_first;
+    RegBlockInputs<S> in;
+    reg_request<S>(*cur, b, wg, lane, in);
+    int turn = 0;
+    for (;;) {
+        const long long gb_next = gb + stride;
+        const bool has_next = gb_next < L.total_blocks;
+        const gefen_b200_step_tensor_t* nxt = cur;
+        long long b_next = 0;
+        RegBlockInputs<S> ahead;
+        if (has_next) {
+            locate(gb_next);
+            nxt = tp;
+            b_next = gb_next - t_first;
+            if (kAhead) reg_request<S>(*nxt, b_next, wg, lane, ahead);
+        }
+        reg_block_step<S>(*cur, b, L, smem, s, in, W, wg, grp, lane, xchg[turn], xchg_exact);
+        if (!has_next) break;
+        if (kAhead) in = ahead;
+        else reg_request<S>(*nxt, b_next, wg, lane, in);
+        cur = nxt;
+        b = b_next;
+        gb = gb_next;
+        turn ^= 1;
+    }
+}
+
 // One gradient element as the step sees it: the local value, or the rounded average over the
 // ranks' buffers (see StepLaunch::grad_delta).
 template <typename S>
@@ -625,7 +974,7 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
     __shared__ float red_max[kWarps];
     __shared__ float red_sum[kWarps];
     SmemView s;
-    if (!stage_tables(L.ws, smem, s)) return;
+    if (!stage_tables(L.ws, smem, s, L.spin_limit)) return;
     const gefen_b200_step_tensor_t* table = L.table != nullptr ? L.table : &single;
 
     const int lane = threadIdx.x & 31;
@@ -811,27 +1160,59 @@ constexpr int kFastMaxPeriod = 8192;
 constexpr int kStaticSmemSlack = 256;   // static __shared__ of the kernels (counted against the per-CTA limit)
 constexpr int kCtaReservedSmem = 1024;  // what the hardware sets aside per resident CTA (not part of the limit)
 
-// GEFEN_B200_STEP_WARPS=n caps the warps per CTA of the staged kernel (for measurements).
+// Per-device launch configuration (cudaFuncSetAttribute) is done once per kernel and device, under
+// this lock; device ordinals beyond the table are refused with a clear error.
+constexpr int kMaxDevices = 64;
+static std::mutex g_config_mutex;
+static int current_device(int* dev) {
+    GEFEN_CHECK_CUDA(cudaGetDevice(dev));
+    GEFEN_CHECK_ARG(*dev >= 0 && *dev < kMaxDevices, "Unsupported device ordinal %d (at most %d devices).", *dev, kMaxDevices);
+    return GEFEN_B200_OK;
+}
+
+static int env_int(const char* name) {
+    const char* e = getenv(name);
+    const int v = e != nullptr ? atoi(e) : 0;
+    return v < 0 ? 0 : v;
+}
+// GEFEN_B200_STEP_WARPS=n caps the warps per CTA of the staged kernel, GEFEN_B200_STEP_REG_WARPS=n
+// picks the warps per CTA of the register-resident kernel (16, 20 or 24), GEFEN_B200_STEP_PATH=staged
+// keeps every block on the staged kernel (all three for measurements; read once).
 static int warps_override() {
-    static int cached = -1;
-    if (cached < 0) {
-        const char* e = getenv("GEFEN_B200_STEP_WARPS");
-        cached = e != nullptr ? atoi(e) : 0;
-        if (cached < 0) cached = 0;
-    }
+    static const int cached = env_int("GEFEN_B200_STEP_WARPS");
     return cached;
 }
+static int reg_warps_override() {
+    static const int cached = env_int("GEFEN_B200_STEP_REG_WARPS");
+    return cached;
+}
+static bool reg_path_enabled() {
+    static const bool cached = [] {
+        const char* e = getenv("GEFEN_B200_STEP_PATH");
+        return !(e != nullptr && e[0] == 's');
+    }();
+    return cached;
+}
+
+// Iteration limit of the step kernels' wait for their staged tables. gefen_b200_debug_set_stage_spin_limit
+// lowers it so that a test can watch the time-out path (status word, kernel returns) without a fault.
+constexpr unsigned int kDefaultStageSpinLimit = 4000000u;
+static unsigned int g_stage_spin_limit = kDefaultStageSpinLimit;
 
 template <typename S, bool REDUCE>
 static int launch_vec_variant(StepLaunch L, const gefen_b200_step_tensor_t& single, long long max_period,
                               cudaStream_t stream) {
-    static bool configured[64];
-    int dev = 0;
-    GEFEN_CHECK_CUDA(cudaGetDevice(&dev));
+    static bool configured[kMaxDevices];
     auto kernel = step_vec_kernel<S, REDUCE>;
-    if (dev < 64 && !configured[dev]) {
-        GEFEN_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem - kStaticSmemSlack));
-        configured[dev] = true;
+    {
+        int dev = 0;
+        const int rc = current_device(&dev);
+        if (rc != GEFEN_B200_OK) return rc;
+        std::lock_guard<std::mutex> lock(g_config_mutex);
+        if (!configured[dev]) {
+            GEFEN_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem - kStaticSmemSlack));
+            configured[dev] = true;
+        }
     }
     // a warp stages one long block, or the 32 / lanes short blocks (at most 256 elements together) of a unit
     const long long stage_bytes = (max_period > 256 ? max_period : 256) * 4;
@@ -858,17 +1239,58 @@ static int launch_vec(StepLaunch L, const gefen_b200_step_tensor_t& single, long
     return launch_vec_variant<S, false>(L, single, max_period, stream);
 }
 
+template <typename S, int MAXW>
+static int launch_reg_variant(StepLaunch L, const gefen_b200_step_tensor_t& single, cudaStream_t stream) {
+    constexpr int smem = kSmemWsPadded + kSmemRepWide;
+    static bool configured[kMaxDevices];
+    auto kernel = step_reg_kernel<S, MAXW>;
+    {
+        int dev = 0;
+        const int rc = current_device(&dev);
+        if (rc != GEFEN_B200_OK) return rc;
+        std::lock_guard<std::mutex> lock(g_config_mutex);
+        if (!configured[dev]) {
+            GEFEN_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            configured[dev] = true;
+        }
+    }
+    const int W = L.warps_per_block;
+    int groups = MAXW / W;
+    if (groups < 1) groups = 1;
+    // few blocks: fewer groups per CTA, so that the blocks spread over the SMs
+    const long long per_sm = (L.total_blocks + sm_count() - 1) / sm_count();
+    if (per_sm < groups) groups = per_sm < 1 ? 1 : static_cast<int>(per_sm);
+    const int grid = grid_for(L.total_blocks, groups, 1);
+    kernel<<<grid, groups * W * 32, smem, stream>>>(L, single);
+    GEFEN_CHECK_CUDA(cudaGetLastError());
+    return GEFEN_B200_OK;
+}
+
+// Warps per CTA of the register-resident kernel (the register budget per thread follows from it).
+template <typename S>
+static int launch_reg(const StepLaunch& L, const gefen_b200_step_tensor_t& single, cudaStream_t stream) {
+    int warps = reg_warps_override();
+    if (warps == 0) warps = sizeof(S) == 2 ? 20 : 16;
+    if (L.warps_per_block > 12 || warps <= 16) return launch_reg_variant<S, 16>(L, single, stream);
+    if (warps >= 24) return launch_reg_variant<S, 24>(L, single, stream);
+    return launch_reg_variant<S, 20>(L, single, stream);
+}
+
 template <typename S>
 static int launch_generic(bool cta_per_block, const StepLaunch& L, const gefen_b200_step_tensor_t& single,
                           cudaStream_t stream) {
     constexpr int smem = kSmemWs;
-    static bool configured[64];
-    int dev = 0;
-    GEFEN_CHECK_CUDA(cudaGetDevice(&dev));
-    if (dev < 64 && !configured[dev]) {
-        GEFEN_CHECK_CUDA(cudaFuncSetAttribute(step_generic_kernel<S, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        GEFEN_CHECK_CUDA(cudaFuncSetAttribute(step_generic_kernel<S, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        configured[dev] = true;
+    static bool configured[kMaxDevices];
+    {
+        int dev = 0;
+        const int rc = current_device(&dev);
+        if (rc != GEFEN_B200_OK) return rc;
+        std::lock_guard<std::mutex> lock(g_config_mutex);
+        if (!configured[dev]) {
+            GEFEN_CHECK_CUDA(cudaFuncSetAttribute(step_generic_kernel<S, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            GEFEN_CHECK_CUDA(cudaFuncSetAttribute(step_generic_kernel<S, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            configured[dev] = true;
+        }
     }
     if (cta_per_block) {
         const int grid = grid_for(L.total_blocks, 1, 3);
@@ -881,20 +1303,35 @@ static int launch_generic(bool cta_per_block, const StepLaunch& L, const gefen_b
     return GEFEN_B200_OK;
 }
 
-// Class of a tensor: 1 = vectorised staged path, 0 = generic warp per block, -1 = generic CTA per block.
+// Class of a tensor: kRegClassBase + W = register-resident path with W warps per block, 1 = vectorised
+// staged path, 0 = generic warp per block, -1 = generic CTA per block.
+constexpr int kRegClassBase = 100;
 static int tensor_class(const gefen_b200_step_tensor_t& t, int dtype) {
     const bool vec_dtype = dtype == GEFEN_B200_F32 || dtype == GEFEN_B200_BF16 || dtype == GEFEN_B200_F16;
     const bool period1 = (t.flags & GEFEN_B200_STEP_PERIOD1) != 0;
     const bool packed = (t.flags & GEFEN_B200_STEP_PACKED) != 0;
     if (vec_dtype && !period1 && !packed && t.period % 8 == 0 && t.period <= kFastMaxPeriod && aligned16(t.g) && aligned16(t.p) &&
         (reinterpret_cast<uintptr_t>(t.codes) & 7u) == 0) {
+        if (t.period >= kRegMinPeriod && t.period <= kRegMaxPeriod && reg_path_enabled())
+            return kRegClassBase + reg_warps_per_block(t.period);
         return 1;
     }
     return t.period > 2048 ? -1 : 0;
 }
+// Units of a tensor in its launch's index space: passes of a warp on the staged path, blocks elsewhere.
+static long long class_units(const gefen_b200_step_tensor_t& t, int cls) {
+    return cls == 1 ? vec_units(t.num_blocks, t.period) : t.num_blocks;
+}
 
 static int launch_class(int cls, int dtype, const StepLaunch& L, const gefen_b200_step_tensor_t& single,
                         long long max_period, cudaStream_t stream) {
+    if (cls > kRegClassBase) {
+        StepLaunch R = L;
+        R.warps_per_block = cls - kRegClassBase;
+        if (dtype == GEFEN_B200_BF16) return launch_reg<__nv_bfloat16>(R, single, stream);
+        if (dtype == GEFEN_B200_F16) return launch_reg<__half>(R, single, stream);
+        return launch_reg<float>(R, single, stream);
+    }
     if (cls >= 1) {
         if (dtype == GEFEN_B200_BF16) return launch_vec<__nv_bfloat16>(L, single, max_period, stream);
         if (dtype == GEFEN_B200_F16) return launch_vec<__half>(L, single, max_period, stream);
@@ -937,12 +1374,14 @@ static int run_single(gefen_b200_step_tensor_t& t, int param_dtype, const float*
     L.n_tensors = 1;
     L.stage_floats = 0;
     const int cls = tensor_class(t, param_dtype);
-    L.total_blocks = cls >= 1 ? vec_units(t.num_blocks, t.period) : t.num_blocks;
+    L.total_blocks = class_units(t, cls);
     L.ws = static_cast<const unsigned char*>(ws);
     L.stepsize = stepsize;
     L.n_peers = 0;
     L.n_grad_srcs = 0;
     L.grad_scale = 1.0f;
+    L.warps_per_block = 1;
+    L.spin_limit = g_stage_spin_limit;
     return launch_class(cls, param_dtype, L, t, t.period, stream);
 }
 
@@ -1082,12 +1521,12 @@ static __device__ __align__(256) unsigned char g_static_codebook_ws[GEFEN_B200_C
 // In host code the array's name is only a handle: the device address comes from the runtime, once
 // per device, with that device current.
 static std::mutex g_static_ws_mutex;
-static void* g_static_ws_address[64];
+static void* g_static_ws_address[kMaxDevices];
 
 static int static_codebook_ws(void** out) {
     int dev = 0;
-    GEFEN_CHECK_CUDA(cudaGetDevice(&dev));
-    GEFEN_CHECK_ARG(dev >= 0 && dev < 64, "Unsupported device ordinal %d.", dev);
+    const int rc_dev = current_device(&dev);
+    if (rc_dev != GEFEN_B200_OK) return rc_dev;
     std::lock_guard<std::mutex> lock(g_static_ws_mutex);
     if (g_static_ws_address[dev] == nullptr) {
         void* address = nullptr;
@@ -1106,8 +1545,17 @@ int gefen_b200_automatic_gefen_fused_update_from_vmean_static_ws(
     GEFEN_CHECK_ARG(codebook != nullptr, "Expected a codebook pointer.");
     GEFEN_CHECK_ARG(codebook_size >= 1 && codebook_size <= kMaxCodebook,
                     "The built-in workspace holds tables for at most 256 codebook entries, got %d.", codebook_size);
+    // every argument is checked before the shared array is touched: a refused call leaves it as it was
+    int rc = check_common(grad_view, m_sign, m_magnitude, magnitude_dtype, param_dtype, packed_indices, num_blocks, period);
+    if (rc != GEFEN_B200_OK) return rc;
+    GEFEN_CHECK_ARG(p != nullptr && vmean != nullptr, "Expected non-null p and vmean.");
+    GEFEN_CHECK_ARG(is_state_dtype(vmean_dtype), "Expected vmean to have dtype float32, float16, or bfloat16.");
+    GEFEN_CHECK_ARG(bias_correction_1 > 0.0, "Expected bias_correction_1 to be positive.");
+    GEFEN_CHECK_ARG(bias_correction_2 > 0.0, "Expected bias_correction_2 to be positive.");
+    GEFEN_CHECK_ARG(eps >= 0.0, "Expected eps to be non-negative.");
+    if (num_blocks == 0) return GEFEN_B200_OK;
     void* ws = nullptr;
-    int rc = static_codebook_ws(&ws);
+    rc = static_codebook_ws(&ws);
     if (rc != GEFEN_B200_OK) return rc;
     rc = launch_codebook_prepare(codebook, codebook_size, ws, static_cast<cudaStream_t>(stream));
     if (rc != GEFEN_B200_OK) return rc;
@@ -1121,6 +1569,23 @@ int gefen_b200_step_tensor_size(void) { return static_cast<int>(sizeof(gefen_b20
 int gefen_b200_step_tensor_class(const gefen_b200_step_tensor_t* host_entry, int param_dtype) {
     if (host_entry == nullptr) return -2;
     return tensor_class(*host_entry, param_dtype);
+}
+
+int gefen_b200_step_status(int* host_status, int clear) {
+    GEFEN_CHECK_ARG(host_status != nullptr, "Expected a host pointer for the status.");
+    int value = 0;
+    GEFEN_CHECK_CUDA(cudaMemcpyFromSymbol(&value, g_step_status, sizeof(int)));   // synchronises the device
+    if (value != 0 && clear) {
+        const int zero = 0;
+        GEFEN_CHECK_CUDA(cudaMemcpyToSymbol(g_step_status, &zero, sizeof(int)));
+    }
+    *host_status = value;
+    return GEFEN_B200_OK;
+}
+
+int gefen_b200_debug_set_stage_spin_limit(int64_t limit) {
+    g_stage_spin_limit = (limit < 0 || limit > 0xFFFFFFFFll) ? kDefaultStageSpinLimit : static_cast<unsigned int>(limit);
+    return GEFEN_B200_OK;
 }
 
 int gefen_b200_multi_tensor_step(gefen_b200_step_tensor_t* host_table, void* device_table, int n_tensors,
@@ -1165,15 +1630,18 @@ int gefen_b200_multi_tensor_step_peers(gefen_b200_step_tensor_t* host_table, voi
         GEFEN_CHECK_ARG((t.flags & GEFEN_B200_STEP_MUON) || t.v != nullptr, "Tensor %d has a null vmean.", i);
         GEFEN_CHECK_ARG(!(t.flags & GEFEN_B200_STEP_PACKED) || (t.period % 2 == 0 && !(t.flags & GEFEN_B200_STEP_PERIOD1)),
                         "Tensor %d: 4-bit codes need an even period and are not defined for period-1 tensors.", i);
-        t.reserved_[0] = tensor_class(t, param_dtype);
+        GEFEN_CHECK_ARG(n_grad_srcs == 0 || !(t.flags & GEFEN_B200_STEP_MUON),
+                        "Tensor %d: the momentum-only step does not average gradients over ranks.", i);
+        int cls = tensor_class(t, param_dtype);
+        if (cls > kRegClassBase && n_grad_srcs > 0) cls = 1;   // gradient averaging lives on the staged kernel
+        t.reserved_[0] = cls;
     }
     for (int begin = 0; begin < n_tensors;) {
         int end = begin;
         long long first = 0;
         while (end < n_tensors && host_table[end].reserved_[0] == host_table[begin].reserved_[0]) {
-            host_table[end].first_block = first;   // in work units on the vector path, in blocks elsewhere
-            first += host_table[end].reserved_[0] >= 1 ? vec_units(host_table[end].num_blocks, host_table[end].period)
-                                                       : host_table[end].num_blocks;
+            host_table[end].first_block = first;   // in work units on the staged path, in blocks elsewhere
+            first += class_units(host_table[end], host_table[end].reserved_[0]);
             ++end;
         }
         host_table[begin].reserved_[1] = end - begin;  // run length, read back below
@@ -1184,8 +1652,7 @@ int gefen_b200_multi_tensor_step_peers(gefen_b200_step_tensor_t* host_table, voi
     for (int begin = 0; begin < n_tensors;) {
         const int run = host_table[begin].reserved_[1];
         const gefen_b200_step_tensor_t& last = host_table[begin + run - 1];
-        const long long total = last.first_block + (last.reserved_[0] >= 1 ? vec_units(last.num_blocks, last.period)
-                                                                            : last.num_blocks);
+        const long long total = last.first_block + class_units(last, last.reserved_[0]);
         long long max_period = 0;
         for (int i = begin; i < begin + run; ++i) max_period = host_table[i].period > max_period ? host_table[i].period : max_period;
         if (total > 0) {
@@ -1201,6 +1668,8 @@ int gefen_b200_multi_tensor_step_peers(gefen_b200_step_tensor_t* host_table, voi
             L.n_grad_srcs = n_grad_srcs;
             L.grad_scale = static_cast<float>(grad_scale);
             for (int r = 0; r < n_grad_srcs; ++r) L.grad_delta[r] = grad_deltas[r];
+            L.warps_per_block = 1;
+            L.spin_limit = g_stage_spin_limit;
             const int rc = launch_class(host_table[begin].reserved_[0], param_dtype, L, host_table[begin], max_period, stream);
             if (rc != GEFEN_B200_OK) return rc;
         }

@@ -562,12 +562,22 @@ class Gefen(torch.optim.Optimizer):
         for local_p, fused_p in copies:
             local_p.copy_(fused_p)
 
+    def check(self) -> None:
+        """Raises if a kernel of an earlier step gave up one of its bounded waits, which leaves that
+        step incomplete (synchronises the devices of the parameters). The kernels never trap or spin
+        for ever; this is where such a time-out becomes an exception. No counterpart in the reference,
+        whose kernels wait on nothing."""
+        devices = {p.device for g in self.param_groups for p in g["params"] if p.device.type == "cuda"}
+        for device in devices:
+            _lib.check_step_status(device)
+
     def _optimizer_state_memory_bytes(self) -> int:
         return sum(v.numel() * v.element_size() for s in self.state.values() for v in s.values() if torch.is_tensor(v))
 
     # ------------------------------------------------------------------ checkpoint
     def state_dict(self):
         """torch's dict plus the global step and the codebook (reference :1343-1349)."""
+        self.check()   # a checkpoint of a half-done step must not look like a good one
         sd = super().state_dict()
         sd["gefen_global_step"] = self._gefen_global_step
         sd["gefen_codebook"] = self._gefen_codebook

@@ -51,7 +51,12 @@ def exact_dp(histogram_stats: dict, num_codebooks: int, force_endpoints: bool = 
         _lib.check(lib.gefen_b200_exact_dp(
             _lib.ptr(prefix_dev[0]), _lib.ptr(prefix_dev[1]), _lib.ptr(prefix_dev[2]), n, int(num_codebooks),
             int(bool(force_endpoints)), _lib.ptr(scratch), _lib.ptr(out), _lib.current_stream(device)))
-    codebook = out.cpu()
+    # the last 16 bytes of the scratch hold the status word of the backtrack (0 = a complete path)
+    tail = torch.cat([out.view(torch.uint8), scratch[-16:]]).cpu()
+    codebook = tail[: num_codebooks * 4].view(torch.float32).clone()
+    status = int(tail[num_codebooks * 4:].view(torch.int32)[0])
+    if status != 0:
+        raise RuntimeError("exact DP could not trace a complete partition back (status {})".format(status))
     if not bool(torch.isfinite(codebook).all()):
         raise RuntimeError("exact DP produced a non-finite codebook")
     return codebook.sort().values

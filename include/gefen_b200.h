@@ -166,10 +166,23 @@ int gefen_b200_multi_tensor_step_peers(gefen_b200_step_tensor_t* host_table, voi
                                        void* stream);
 /* sizeof(gefen_b200_step_tensor_t) as compiled, for binding-side layout checks. */
 int gefen_b200_step_tensor_size(void);
-/* Kernel class the library would use for one table entry: 1 = vectorised staged path,
+/* Kernel class the library would use for one table entry: 100 + W = register-resident path with W
+ * warps per block (periods of 512 to 8192 elements), 1 = vectorised staged path,
  * 0 = generic warp-per-block, -1 = generic CTA-per-block. Rows of equal
  * class that are adjacent in the table share one launch. */
 int gefen_b200_step_tensor_class(const gefen_b200_step_tensor_t* host_entry, int param_dtype);
+
+/* Error status of the step kernels on the CURRENT device. Every wait inside them is bounded; a CTA
+ * whose wait for its staged tables runs out leaves without doing its share of the step and raises
+ * bit 0 of a status word. This call synchronises the device, writes the word to *host_status and,
+ * with clear != 0, resets it. Non-zero means that a step since the last clear was incomplete. The
+ * reference has no counterpart: its kernels do not wait on anything (errors there are exceptions
+ * from C10_CUDA_KERNEL_LAUNCH_CHECK). */
+int gefen_b200_step_status(int* host_status, int clear);
+/* Test hook: the number of polls the step kernels grant the table staging (negative = default).
+ * With 0 the wait runs out at once, the kernels return without touching their tensors and the
+ * status word is set; nothing faults or hangs. Process-wide, not thread-safe. */
+int gefen_b200_debug_set_stage_spin_limit(int64_t limit);
 
 /* Replaces gefen_exact_histogram_cuda (gefen_cuda_binding.cpp:65-69;
  * exact_histogram_fused_kernel.cu:131-160): bin_counts[bin] += #elements, int64, exact. */

@@ -143,3 +143,31 @@ def test_packed_4bit_codes_against_the_reference_kernels(ref_ext, oracle, cuda_d
     automatic_gefen_muon_momentum_cuda(mg, mc, mm, dcb, out_m, True, 0.95)
     torch.cuda.synchronize()
     assert torch.equal(mc, rc) and torch.equal(mm, rm) and torch.equal(out_m, out_r)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,period", [(200, 1024), (64, 96), (3, 12000)])
+def test_lloyd_kernels_against_the_reference_kernels(ref_ext, cuda_device, dtype, rows, period):
+    """Lloyd-Max E-step and logging MSE (reference: lloyd_max_fused_kernel.cu:50-195): the per-entry
+    counts are integers and must be identical; the per-entry sums and the two squared errors are fp32
+    atomics in the reference (order-dependent there too): 1e-5 relative to the largest sum."""
+    from gefen_b200.kernels.lloyd_max_fused import gefen_lloyd_accumulate_cuda, gefen_lloyd_mse_cuda
+
+    cb = reference_like_codebook().to(cuda_device)
+    new_cb = (cb * 0.99).contiguous()
+    g = make_grad((rows, period), 11, 0, 0, dtype).to(cuda_device).reshape(-1).contiguous()
+    want_sums = torch.zeros(256, device=cuda_device)
+    want_counts = torch.zeros(256, dtype=torch.int64, device=cuda_device)
+    got_sums, got_counts = torch.zeros_like(want_sums), torch.zeros_like(want_counts)
+    ref_ext.gefen_lloyd_accumulate_cuda(g, cb, period, want_sums, want_counts)
+    gefen_lloyd_accumulate_cuda(g, cb, period, got_sums, got_counts)
+    assert torch.equal(got_counts, want_counts)
+    assert int(got_counts.sum()) == g.numel()
+    scale = float(want_sums.abs().max())
+    assert float((got_sums - want_sums).abs().max()) <= 1e-5 * scale
+    want = [torch.zeros(1, device=cuda_device) for _ in range(2)]
+    got = [torch.zeros(1, device=cuda_device) for _ in range(2)]
+    ref_ext.gefen_lloyd_mse_cuda(g, cb, new_cb, period, want[0], want[1])
+    gefen_lloyd_mse_cuda(g, cb, new_cb, period, got[0], got[1])
+    for a, b in zip(got, want):
+        assert float(a) == pytest.approx(float(b), rel=1e-4)

@@ -14,6 +14,9 @@ DTYPES = [torch.float32, torch.bfloat16, torch.float16]
 # warp path (odd / tiny periods) and the generic CTA path (period > 2048)
 SHAPES = [(64, 512), (33, 768), (20, 1152), (16, 2048), (9, 1120), (7, 1664), (5, 8), (40, 24), (11, 12),
           (301, 1), (13, 37), (6, 4096), (3, 3000), (2, 10007),
+          # register-resident path: 1 to 16 warps per block, full and ragged last warps, more blocks than
+          # one wave of groups (the prefetch of the next block crosses the end of the tensor)
+          (700, 512), (333, 2048), (5, 5000), (4, 6144), (3, 8192), (2, 7688), (50, 520), (9, 1536),
           # blocks shorter than 256 elements share a warp (32, 16, 8, 4, 2 blocks per pass), ragged last pass
           (37, 128), (101, 64), (1001, 16), (67, 8), (3, 256), (50, 40), (21, 104), (1, 8)]
 
@@ -168,16 +171,19 @@ def test_vmean_update(oracle, cuda_device, dtype, nb, period):
     assert torch.allclose(dv.cpu().float(), v.float(), rtol=tol, atol=0)
 
 
-def test_nonfinite_gradients_follow_the_reference(oracle, cuda_device):
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("period", [128, 512, 2048, 3000])   # staged path; one, four and six warps per block
+def test_nonfinite_gradients_follow_the_reference(oracle, cuda_device, dtype, period):
     from gefen_b200.kernels.automatic_gefen_fused import automatic_gefen_fused_update_from_vmean_cuda
 
     cb = reference_like_codebook()
-    nb, period = 6, 512
-    p, g, codes, mag, v = _state(nb, period, torch.float32, torch.float32, seed=8)
+    nb = 6
+    p, g, codes, mag, v = _state(nb, period, dtype, dtype, seed=8)
     g[1, 5] = float("nan")
     g[3, 7] = float("inf")
     g[4, 0] = float("-inf")
     g[4, 9] = float("nan")
+    g[5, period - 1] = float("nan")      # the last warp of the block holds it
     dp, dg, dc, dm, dv = (t.to(cuda_device) for t in (p, g, codes, mag, v))
     args = dict(beta1=0.9, lr=1e-3, bias_correction_1=0.1, bias_correction_2=0.001, eps=1e-8)
     oracle.automatic_gefen_fused_update_from_vmean(p, g, codes, mag, v, cb, False, **args)
