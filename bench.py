@@ -112,18 +112,33 @@ def build_model(cfg, device, limit_elems=None):
 
 
 # --------------------------------------------------------------------------- CPU arm (oracle port)
-def cpu_port_step_ms(cfg, steps: int, warmup: int, sample_elems: int):
-    """Times the CPU oracle's restatement of the reference step (calibration excluded) on a
-    layer-shaped sample of the workload, all host threads, and scales by element count."""
+def workload_config(args, cfg, world, n_tensors, total_elems, periods, by_period, algo_bytes):
+    """The `config` object of the JSON line: the same for the GPU arm and the reference arm."""
+    return {"workload": args.workload, "optimizer": "Gefen(fused=True)", "lr": cfg["lr"],
+            "weight_decay": cfg["wd"], "betas": [0.9, 0.999], "eps": 1e-8,
+            "tensors": n_tensors, "elements": total_elems,
+            "parallelism": "zero1-dp{}".format(world) if world > 1 else "single-gpu",
+            "l2": "inputs ({:.1f} GB per step) are larger than L2".format(algo_bytes / 1e9),
+            "periods": sorted(set(periods)), "elements_by_period": {str(k): by_period[k] for k in sorted(by_period)}}
+
+
+def period_census(shapes, per_tensor):
+    by_period = {}
+    for (_, shape), period in zip(shapes, per_tensor):
+        by_period[period] = by_period.get(period, 0) + workloads.numel(shape)
+    return by_period
+
+
+def cpu_port_run(cfg, steps: int, warmup: int, sample_elems):
+    """The CPU oracle's restatement of the reference step on the host cores (C with OpenMP, all
+    threads): the oracle's own calibration (period search, histogram, exact-DP codebook), then
+    `warmup` untimed and `steps` timed steady-state steps. sample_elems=None: the whole workload;
+    otherwise a prefix of whole layer tensors of about that many elements."""
     from oracle.ref_loop import OracleGefen
 
     device = torch.device("cpu")
     shapes, params, grads = build_model(cfg, device, limit_elems=sample_elems)
     opt = OracleGefen(params, lr=cfg["lr"], betas=(0.9, 0.999), eps=1e-8, weight_decay=cfg["wd"])
-    # calibration is not part of the steady-state step: fix the periods by the documented rule
-    # (run length, capped above 1024 by its smallest divisor > 1024) and fit the codebook once
-    for st, (name, shape) in zip(opt.state, shapes):
-        st["automatic_period"] = expected_period(shape)
     t0 = time.perf_counter()
     opt.calibrate(grads)
     calib_s = time.perf_counter() - t0
@@ -134,39 +149,39 @@ def cpu_port_step_ms(cfg, steps: int, warmup: int, sample_elems: int):
         dt = time.perf_counter() - t0
         if i >= warmup:
             times.append(dt)
-    sample = sum(workloads.numel(s) for _, s in shapes)
-    total = sum(workloads.numel(s) for _, s in cfg["shapes"]())
-    ms = 1e3 * sum(times) / len(times) * total / sample
-    return ms, sample, total, calib_s, os.cpu_count()
+    periods = [st["automatic_period"] for st in opt.state]
+    return {"ms": 1e3 * sum(times) / len(times), "shapes": shapes, "periods": periods, "calibration_s": calib_s,
+            "elements": sum(workloads.numel(s) for _, s in shapes), "cores": os.cpu_count(), "timed_steps": len(times)}
 
 
-def expected_period(shape):
-    if len(shape) == 1:
-        return 1
-    run = shape[1]
-    if run <= 1024:
-        return run
-    n = shape[0] * shape[1]
-    from gefen_b200.partitioning import divisors
-
-    return min(q for q in divisors(n) if 1024 < q <= run and run % q == 0)
+REFERENCE_ARM_MAX_STEPS = 3   # a CPU step of the 1.5 B set takes seconds: the arm times at most this many
 
 
-def run_reference_arm(args, cfg, rank):
+def run_reference_arm(args, cfg, rank, world):
+    """`--impl reference`: the whole workload through the CPU port, nothing sampled or scaled."""
     if rank != 0:
         return
     torch.set_num_threads(os.cpu_count() or 1)
-    ms, sample, total, calib_s, cores = cpu_port_step_ms(cfg, max(1, args.steps), max(1, min(args.warmup, 2)),
-                                                        args.cpu_sample_elems)
+    timed_steps = max(1, min(args.steps, REFERENCE_ARM_MAX_STEPS))
+    run = cpu_port_run(cfg, timed_steps, 1, None)
+    shapes, periods = run["shapes"], run["periods"]
+    elem_bytes = 2 if cfg["dtype"] == torch.bfloat16 else 4
+    algo_bytes = workloads.step_bytes(shapes, periods, elem_bytes, elem_bytes)
+    ms = run["ms"]
     line = {
         "impl": "reference", "metric": "optimizer_step_ms", "value": ms, "unit": "ms", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False,
         "scaling": "strong", "vs_baseline": ms / PUBLISHED_LLAMA_1_5B_MS if args.workload == "llama_1_5b" else None,
         "dtype": "bf16" if cfg["dtype"] == torch.bfloat16 else "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "optimizer": "Gefen", "lr": cfg["lr"], "weight_decay": cfg["wd"]},
-        "cpu_baseline": {"value": ms, "unit": "ms", "cores": cores, "kind": "port",
-                         "sample": "{} of {} elements (one transformer layer's tensors, whole tensors), steady-state "
-                                   "step of the C oracle with OpenMP, scaled by element count".format(sample, total)},
+        "config": workload_config(args, cfg, world, len(shapes), run["elements"], periods, period_census(shapes, periods),
+                                  algo_bytes),
+        "timed_steps": run["timed_steps"], "timed_warmup": 1,
+        "timed_steps_note": "a CPU step of this workload takes seconds: {} steady-state steps are timed after one "
+                            "untimed step, whatever --steps asks for; nothing is sampled or scaled".format(run["timed_steps"]),
+        "calibration_s": run["calibration_s"],
+        "cpu_baseline": {"value": ms, "unit": "ms", "cores": run["cores"], "kind": "port",
+                         "sample": "the whole workload ({} elements, {} tensors): the C oracle with OpenMP, its own "
+                                   "calibration, steady-state steps".format(run["elements"], len(shapes))},
         "e2e": {"value": ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -186,9 +201,123 @@ def timed(fn, steps: int, stream=None):
     return e0.elapsed_time(e1) / steps
 
 
-def run_gpu_arm(args, cfg, rank, world, local_rank):
+def run_sharded_arm(args, cfg, rank, world, local_rank):
+    """N > 1: the parameter set ZeRO-1 sharded over the ranks (gefen_b200.Zero1Gefen). The flat buffers are
+    created first and the synthetic parameters and gradients are written straight into them, so that a
+    model exists once per GPU (the 32 B set: 65 GB of parameters + 65 GB of gradients per rank)."""
     import torch.distributed as dist
 
+    from gefen_b200.zero1 import Zero1Gefen
+
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    shapes = cfg["shapes"]()
+    opt = Zero1Gefen(shapes, lr=cfg["lr"], betas=(0.9, 0.999), eps=1e-8, weight_decay=cfg["wd"], device=device,
+                     dtype=cfg["dtype"])
+    with torch.no_grad():
+        for i, ((name, shape), (_, p)) in enumerate(zip(shapes, opt.named)):
+            p.data.copy_(workloads.init_param(name, shape, i, cfg["dtype"], device))
+            # every rank its own gradients (seeded by rank), as data-parallel ranks have
+            p.grad.copy_(workloads.make_grad(shape, i, rank, cfg["dtype"], device, cfg["sigma"], cfg["tau"]))
+    step = opt.step
+    calibration_ms = timed(step, 1)
+    warm = max(args.warmup - 1, 2)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for _ in range(warm):
+        step()
+    dist.barrier()
+    ms = timed(step, args.steps)
+    t = torch.tensor([ms], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t)
+    breakdown = opt.last_breakdown_ms()
+    for _ in range(int(400.0 / max(ms, 0.05)) + 1):   # the same load until the clock sampler has seen it
+        step()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    dist.barrier()
+
+    per_tensor = [opt.periods[t] for t in range(len(shapes))]
+    elem_bytes = opt.flat_param.element_size()
+    total_elems = sum(workloads.numel(s) for _, s in shapes)
+    algo_bytes = workloads.step_bytes(shapes, per_tensor, elem_bytes, elem_bytes)
+    result = {"ms": ms, "calibration_ms": calibration_ms, "clocks": clocks, "algo_bytes": algo_bytes,
+              "total_elems": total_elems, "n_tensors": len(shapes), "periods": per_tensor, "shapes": shapes}
+    breakdown["all_gather_mode"] = opt.all_gather_mode
+    breakdown["reduce_scatter_mode"] = opt.reduce_scatter_mode
+    if opt.fused_errors:
+        breakdown["fused_errors"] = dict(opt.fused_errors)
+    # what each rank moves over NVLink per step, and what the links could do at best: every rank must send
+    # (N-1)/N of its gradients and receive (N-1)/N of the parameters; with the switch's multicast the other
+    # direction of each collective shrinks to 1/N of the buffer
+    flat_bytes = opt.flat_param.numel() * elem_bytes
+    frac = (world - 1) / world
+    mc_rs = opt.reduce_scatter_mode.startswith("multimem")
+    mc_ag = opt.all_gather_mode.startswith("multimem")
+    egress = flat_bytes * frac + (flat_bytes / world if mc_ag else flat_bytes * frac)
+    ingress = (flat_bytes / world if mc_rs else flat_bytes * frac) + (flat_bytes if mc_ag else flat_bytes * frac)
+    breakdown["wire_bytes_per_rank"] = {"egress": int(egress), "ingress": int(ingress)}
+    breakdown["link_floor_ms"] = {"at_770_gbs_measured_peer_copy": max(egress, ingress) / 770e6,
+                                  "at_900_gbs_nominal": max(egress, ingress) / 900e6}
+    breakdown["achieved_link_gbs"] = max(egress, ingress) / ms / 1e6
+
+    # the 1/N part: this rank's share of the step with nothing crossing NVLink (max over ranks)
+    local_ms = None
+    if opt.local is not None:
+        saved = {k: getattr(opt.local, k, None) for k in ("_peer_param_deltas", "_grad_src_deltas", "_param_multicast_delta",
+                                                         "_grad_multicast_delta")}
+        for k in saved:
+            setattr(opt.local, k, None)
+        opt.local.step()
+        local_ms = timed(opt.local.step, max(2, min(args.steps, 5)))
+        for k, v in saved.items():
+            setattr(opt.local, k, v)
+    lt = torch.tensor([local_ms if local_ms is not None else 0.0], device=device)
+    dist.all_reduce(lt, op=dist.ReduceOp.MAX)
+    breakdown["local_compute_ms"] = float(lt)
+    # the local steps above touched only the owned segments: bring every copy back in line before the check
+    opt.step()
+    result["n_vs_1"] = opt.verify_against_single_process(steps=2)
+    result["breakdown"] = breakdown
+
+    e2e = None
+    if not args.no_e2e:
+        # end to end at N ranks: every rank's gradients come from its own pinned host buffer and the full
+        # updated parameters go back to it (flat buffers, one copy each way per rank and step)
+        host_g = host_p = None
+        try:
+            host_g = torch.empty(opt.flat_grad.shape, dtype=opt.flat_grad.dtype, pin_memory=True)
+            host_p = torch.empty(opt.flat_param.shape, dtype=opt.flat_param.dtype, pin_memory=True)
+            host_g.copy_(opt.flat_grad)
+        except RuntimeError as exc:   # e.g. the host cannot pin the buffers of every rank
+            host_g = None
+            breakdown["e2e_skipped"] = str(exc)[:200]
+        everyone = torch.tensor([1.0 if host_g is not None else 0.0], device=device)
+        dist.all_reduce(everyone, op=dist.ReduceOp.MIN)
+        if float(everyone) > 0:
+            def e2e_step():
+                opt.flat_grad.copy_(host_g, non_blocking=True)
+                step()
+                host_p.copy_(opt.flat_param, non_blocking=True)
+
+            e2e_step()
+            dist.barrier()
+            e2e_ms = timed(e2e_step, max(2, min(args.steps, 5)))
+            t = torch.tensor([e2e_ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            nbytes = opt.flat_grad.numel() * opt.flat_grad.element_size()
+            e2e = {"value": float(t), "unit": "ms", "h2d_bytes_per_step": nbytes * world,
+                   "d2h_bytes_per_step": nbytes * world, "note": "per rank {} bytes each way".format(nbytes)}
+    return result, e2e
+
+
+# DRAM bytes (read + write) per algorithmic byte of one launch of the staged step kernel, from an ncu
+# capture of a 134 M-element launch of the same kernel (traffic grows in proportion to the elements).
+STEP_KERNEL_DRAM_BYTES_PER_ALGORITHMIC_BYTE = {2: 0.971}
+
+
+def run_gpu_arm(args, cfg, rank, world, local_rank):
     from gefen_b200 import Gefen
 
     device = torch.device("cuda", local_rank)
@@ -197,14 +326,8 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     named = [(name, torch.nn.Parameter(p)) for (name, _), p in zip(shapes, params)]
     for (_, p), g in zip(named, grads):
         p.grad = g
-    if world > 1:
-        from gefen_b200.zero1 import Zero1Gefen
-
-        opt = Zero1Gefen(named, lr=cfg["lr"], betas=(0.9, 0.999), eps=1e-8, weight_decay=cfg["wd"])
-        step = opt.step
-    else:
-        opt = Gefen(named, lr=cfg["lr"], betas=(0.9, 0.999), eps=1e-8, weight_decay=cfg["wd"])
-        step = opt.step
+    opt = Gefen(named, lr=cfg["lr"], betas=(0.9, 0.999), eps=1e-8, weight_decay=cfg["wd"])
+    step = opt.step
 
     # first step = calibration (period scan, histogram, exact-DP codebook) + one optimizer step
     calibration_ms = timed(step, 1)
@@ -213,71 +336,21 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     sampler.start()   # nvidia-smi needs a moment to start: begin before the warm-up
     for _ in range(warm):
         step()
-    if world > 1:
-        dist.barrier()
     ms = timed(step, args.steps)
-    if world > 1:
-        t = torch.tensor([ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t)
     # the timed region is a few tens of milliseconds, shorter than the sampling period: keep the same
-    # load running (untimed, the same count on every rank) until the sampler has seen it
+    # load running (untimed) until the sampler has seen it
     for _ in range(int(400.0 / max(ms, 0.05)) + 1):
         step()
     torch.cuda.synchronize()
     clocks = sampler.stop()
-    if world > 1:
-        dist.barrier()
+    opt.check()
 
-    if world > 1:
-        per_tensor = [opt.periods[t] for t in range(len(shapes))]
-    else:
-        per_tensor = [opt.state[p]["automatic_period"] for _, p in named]
-    periods = per_tensor
+    per_tensor = [opt.state[p]["automatic_period"] for _, p in named]
     elem_bytes = params[0].element_size()
     total_elems = sum(workloads.numel(s) for _, s in shapes)
     algo_bytes = workloads.step_bytes(shapes, per_tensor, elem_bytes, elem_bytes)
-    by_period = {}
-    for (_, shape), period in zip(shapes, per_tensor):
-        by_period[period] = by_period.get(period, 0) + workloads.numel(shape)
     result = {"ms": ms, "calibration_ms": calibration_ms, "clocks": clocks, "algo_bytes": algo_bytes,
-              "total_elems": total_elems, "n_tensors": len(shapes), "periods": sorted(set(periods)),
-              "period_elements": {str(k): by_period[k] for k in sorted(by_period)}}
-    if world > 1:
-        result["breakdown"] = opt.last_breakdown_ms()
-        result["breakdown"]["all_gather_mode"] = opt.all_gather_mode
-        result["breakdown"]["reduce_scatter_mode"] = opt.reduce_scatter_mode
-        if opt.fused_errors:
-            result["breakdown"]["fused_errors"] = dict(opt.fused_errors)
-        # end to end at N ranks: every rank's gradients come from its own pinned host buffer and the
-        # full updated parameters go back to it (flat buffers, one copy each way per rank and step)
-        e2e = None
-        if not args.no_e2e:
-            host_g = host_p = None
-            try:
-                host_g = torch.empty(opt.flat_grad.shape, dtype=opt.flat_grad.dtype, pin_memory=True)
-                host_p = torch.empty(opt.flat_param.shape, dtype=opt.flat_param.dtype, pin_memory=True)
-                host_g.copy_(opt.flat_grad)
-            except RuntimeError as exc:   # e.g. the host cannot pin 6 GB per rank
-                host_g = None
-                result["breakdown"]["e2e_skipped"] = str(exc)[:200]
-            everyone = torch.tensor([1.0 if host_g is not None else 0.0], device=device)
-            dist.all_reduce(everyone, op=dist.ReduceOp.MIN)
-            if float(everyone) > 0:
-                def e2e_step():
-                    opt.flat_grad.copy_(host_g, non_blocking=True)
-                    step()
-                    host_p.copy_(opt.flat_param, non_blocking=True)
-
-                e2e_step()
-                dist.barrier()
-                e2e_ms = timed(e2e_step, max(2, min(args.steps, 5)))
-                t = torch.tensor([e2e_ms], device=device)
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                nbytes = opt.flat_grad.numel() * opt.flat_grad.element_size()
-                e2e = {"value": float(t), "unit": "ms", "h2d_bytes_per_step": nbytes * world,
-                       "d2h_bytes_per_step": nbytes * world, "note": "per rank {} bytes each way".format(nbytes)}
-        return result, e2e
+              "total_elems": total_elems, "n_tensors": len(shapes), "periods": per_tensor, "shapes": shapes}
 
     # ---- roofline of the dominant kernel: the staged vector step over all its tensors, one launch
     from gefen_b200 import _lib
@@ -286,16 +359,11 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     table = next(t for t in opt._plan.tables)
     rows = table["rows"]
     cls = [lib.gefen_b200_step_tensor_class(rows[r:r + 1].ctypes.data, table["tag"]) for r in range(len(rows))]
+
     def row_bytes(r):
         return int(r["num_blocks"]) * int(r["period"]) * (3 * elem_bytes + 2) + int(r["num_blocks"]) * 4 * elem_bytes
 
-    # the dominant kernel = the launch (one per kernel class) that moves the most bytes
-    by_class = {}
-    for r, c in enumerate(cls):
-        if c >= 1:
-            by_class[c] = by_class.get(c, 0) + row_bytes(rows[r])
-    top_class = max(by_class, key=by_class.get)
-    vec_rows = rows[[r for r, c in enumerate(cls) if c == top_class]].copy()
+    vec_rows = rows[[r for r, c in enumerate(cls) if c == 1]].copy()
     vec_bytes = int(sum(row_bytes(r) for r in vec_rows))
     dev_table = torch.empty(vec_rows.nbytes, dtype=torch.uint8, device=device)
     ws = _lib.codebook_workspace(opt._gefen_codebook)
@@ -309,12 +377,11 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
     vec_ms = timed(vec_only, max(args.steps, 5))
     peak, peak_kind = measured_peaks()
     achieved = vec_bytes / vec_ms / 1e6
+    ratio = STEP_KERNEL_DRAM_BYTES_PER_ALGORITHMIC_BYTE.get(elem_bytes)
     result["roofline"] = {"bound": "hbm", "kernel": "step_vec_kernel<bf16>" if elem_bytes == 2 else "step_vec_kernel<f32>",
                           "achieved": achieved, "peak": peak, "peak_kind": peak_kind + " copy bandwidth, burst",
                           "unit": "GB/s", "frac": achieved / peak,
-                          # dram read+write of one launch: 0.971 x algorithmic, scaled from the ncu capture of a
-                          # 134 M-element launch of the same kernel (profiles/step_vec_kernel_bf16_period2048.md)
-                          "traffic": 0.971 * vec_bytes if elem_bytes == 2 else None,
+                          "traffic": ratio * vec_bytes if ratio is not None else None,
                           "algorithmic_bytes_per_launch": vec_bytes, "launch_ms": vec_ms}
     result["launches_per_step"] = len(set(cls))
 
@@ -338,7 +405,70 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
         e2e_ms = timed(e2e_step, max(2, min(args.steps, 5)))
         nbytes = sum(g.numel() * g.element_size() for g in grads)
         e2e = {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
+        del streamed, host_g, host_p
+
+    # ---- the reference's own CUDA kernels on the same tensors, in the reference's launch order
+    if not args.no_reference_cuda:
+        result["reference_cuda"] = reference_cuda_step_ms(shapes, params, grads, per_tensor, opt, cfg, max(3, min(args.steps, 5)), ms)
     return result, e2e
+
+
+def reference_cuda_step_ms(shapes, params, grads, periods, opt, cfg, steps, own_ms):
+    """The reference's CUDA kernels (compiled unmodified for sm_100a, the second checker of the tests) stepping
+    the whole parameter set the way the reference optimizer launches them: per tensor the second-moment
+    kernel, the weight-decay multiply and the fused step kernel (reference: gefen.py:1276-1311; period-1
+    tensors through their own kernel, :1299). A measured comparison beside the product's number; it runs
+    after the timed region on fresh state and the product's periods and codebook."""
+    try:
+        from oracle import build_ref
+
+        ext = build_ref.load_module()
+    except Exception as exc:   # the checker is optional
+        return {"unavailable": "{}: {}".format(type(exc).__name__, str(exc)[:120])}
+    if ext is None:
+        return {"unavailable": "the reference kernels have not been built on this machine"}
+    lr, wd, beta1, beta2, eps = cfg["lr"], cfg["wd"], 0.9, 0.999, 1e-8
+    codebook = opt._gefen_codebook
+    state = []
+    for p, period in zip(params, periods):
+        n, dev, dt = p.numel(), p.device, p.dtype
+        st = {"codes": torch.zeros(n // period, period, dtype=torch.uint8, device=dev)}
+        if period == 1:
+            st["divisor"] = opt._period_one_divisor_for_numel(n)
+            st["mag"] = torch.zeros(n // st["divisor"], 1, dtype=dt, device=dev)
+            st["v"] = torch.zeros(n, 1, dtype=dt, device=dev)
+        else:
+            st["mag"] = torch.zeros(n // period, 1, dtype=dt, device=dev)
+            st["v"] = torch.zeros(n // period, 1, dtype=dt, device=dev)
+        state.append(st)
+    counter = [0]
+
+    def step():
+        counter[0] += 1
+        bc1, bc2 = 1 - beta1 ** counter[0], 1 - beta2 ** counter[0]
+        for p, g, st, period in zip(params, grads, state, periods):
+            flat = g.reshape(-1)
+            if period != 1:
+                view = flat.view(-1, period)
+                ext.automatic_vmean_update_cuda(st["v"], view, beta2)
+                if wd > 0.0:
+                    p.mul_(1 - lr * wd)
+                ext.automatic_gefen_fused_update_from_vmean_cuda(p, view, st["codes"], st["mag"], st["v"], codebook, False,
+                                                                 beta1, lr, bc1, bc2, eps)
+            else:
+                if wd > 0.0:
+                    p.mul_(1 - lr * wd)
+                ext.automatic_gefen_period1_update_cuda(p, flat, st["codes"], st["mag"], st["v"], codebook, st["divisor"],
+                                                        beta1, beta2, lr, bc1, bc2, eps)
+
+    with torch.no_grad():
+        for _ in range(2):
+            step()
+        # the reference launches on the legacy default stream: time with events on that stream
+        ms = timed(step, steps)
+    launches = sum(3 if period != 1 else 2 for period in periods) if wd > 0.0 else sum(2 if period != 1 else 1 for period in periods)
+    return {"value": ms, "unit": "ms", "ratio_to_this_library": ms / own_ms, "kernel_launches_per_step": launches,
+            "what": "the reference's own CUDA kernels compiled for sm_100a, its per-tensor launch order, same tensors"}
 
 
 def ns_flops(shape, steps=5):
@@ -392,58 +522,170 @@ def run_muon_sharded_arm(args, cfg, rank, world, local_rank):
     }))
 
 
-def run_muon_arm(args, cfg):
-    """GefenMuon on the Qwen3-1.7B-shaped matrices, one GPU: whole step, then Newton-Schulz alone on
-    this library's tcgen05 GEMM and on torch's (cuBLAS) GEMMs for the same inputs."""
+def torch_newton_schulz(grad, coefficients=(3.4445, -4.7750, 2.0315), steps=5, eps=1e-7):
+    """The reference's Newton-Schulz chain on torch's (cuBLAS) GEMMs (reference: gefen_muon.py:16-51): the
+    library path this library's tcgen05 kernels are compared with. Benchmark-side only."""
+    a, b, c = coefficients
+    x = grad.bfloat16()
+    transposed = x.size(0) > x.size(1)
+    if transposed:
+        x = x.T
+    x = x / x.norm().clamp(min=eps)
+    for _ in range(steps):
+        gram = x @ x.T
+        gram_update = torch.addmm(gram, gram, gram, beta=b, alpha=c)
+        x = torch.addmm(x, gram_update, x, beta=a)
+    return x.T if transposed else x
+
+
+def measure_muon(cfg, steps: int, warmup: int):
+    """GefenMuon on the Qwen3-1.7B-shaped matrices, one GPU: the whole step, then Newton-Schulz alone on this
+    library's tcgen05 GEMMs and on torch's (cuBLAS) GEMMs for the same inputs."""
     from gefen_b200 import GefenMuon
     from gefen_b200 import newton_schulz as ns
 
-    device = torch.device("cuda", 0)
+    device = torch.device("cuda", torch.cuda.current_device())
     shapes, params, grads = build_model(cfg, device)
     named = [(name, torch.nn.Parameter(p)) for (name, _), p in zip(shapes, params)]
     for (_, p), g in zip(named, grads):
         p.grad = g
     opt = GefenMuon(named, lr=cfg["lr"], weight_decay=cfg["wd"], momentum=0.95, ns_steps=5)
     calibration_ms = timed(opt.step, 1)
-    for _ in range(max(args.warmup - 1, 2)):
+    for _ in range(max(warmup - 1, 2)):
         opt.step()
-    sampler = ClockSampler(0)
+    sampler = ClockSampler(device.index)
     sampler.start()
-    ms = timed(opt.step, args.steps)
+    ms = timed(opt.step, steps)
     clocks = sampler.stop()
-    ns.check_status(device)
+    opt.check()
     total_flops = sum(ns_flops(s) for _, s in shapes)
+    coeffs = (3.4445, -4.7750, 2.0315)
 
-    def ns_all():
+    def ns_ours():
         for g in grads:
-            ns.zeropower_via_newtonschulz(g, (3.4445, -4.7750, 2.0315), 5, 1e-7)
+            ns.zeropower_via_newtonschulz(g, coeffs, 5, 1e-7)
+
+    def ns_torch():
+        for g in grads:
+            torch_newton_schulz(g, coeffs, 5, 1e-7)
 
     results = {}
-    for mode in ("tcgen05", "torch"):
-        ns.USE_TCGEN05 = mode == "tcgen05"
-        ns_all()
-        results[mode] = timed(ns_all, max(2, min(args.steps, 5)))
-    ns.USE_TCGEN05 = True
+    for name, fn in (("tcgen05", ns_ours), ("torch", ns_torch)):
+        fn()
+        results[name] = timed(fn, max(2, min(steps, 5)))
+    ns.check_status(device)
     peak_file = ROOT / "MEASURED_PEAKS.json"
     peak = json.loads(peak_file.read_text())["bf16_tflops_sustained"] if peak_file.exists() else 1400.0
     achieved = total_flops / results["tcgen05"] / 1e9
     elems = sum(workloads.numel(s) for _, s in shapes)
+    roofline = {"bound": "tensor", "kernel": "ns_gemm_tn_kernel", "achieved": achieved, "peak": peak,
+                "peak_kind": "measured cuBLAS bf16, sustained", "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": None, "algorithmic_flops_per_step": total_flops,
+                "newton_schulz_ms": results["tcgen05"],
+                "newton_schulz_ms_torch_cublas": results["torch"],
+                "torch_cublas_tflops": total_flops / results["torch"] / 1e9}
+    summary = {"workload": "qwen3_muon", "matrices": len(shapes), "elements": elems, "step_ms": ms,
+               "newton_schulz_ms": results["tcgen05"], "newton_schulz_tflops": achieved,
+               "frac_of_bf16_tflops_sustained": achieved / peak,
+               "torch_cublas_chain_ms": results["torch"], "calibration_first_step_ms": calibration_ms}
+    return {"ms": ms, "calibration_ms": calibration_ms, "clocks": clocks, "roofline": roofline, "summary": summary,
+            "shapes": shapes, "elements": elems}
+
+
+def run_muon_arm(args, cfg):
+    m = measure_muon(cfg, args.steps, args.warmup)
     line = {
-        "metric": "optimizer_step_ms", "value": ms, "unit": "ms", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "metric": "optimizer_step_ms", "value": m["ms"], "unit": "ms", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": m["ms"], "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
         "config": {"workload": args.workload, "optimizer": "GefenMuon(momentum=0.95, ns_steps=5)", "lr": cfg["lr"],
-                   "weight_decay": cfg["wd"], "matrices": len(shapes), "elements": elems},
-        "calibration_first_step_ms": calibration_ms, "clocks": clocks,
-        "roofline": {"bound": "tensor", "kernel": "ns_gemm_tn_kernel", "achieved": achieved, "peak": peak,
-                     "peak_kind": "measured cuBLAS bf16, sustained", "unit": "TFLOP/s", "frac": achieved / peak,
-                     "traffic": None, "algorithmic_flops_per_step": total_flops,
-                     "newton_schulz_ms": results["tcgen05"],
-                     "newton_schulz_ms_torch_cublas": results["torch"],
-                     "torch_cublas_tflops": total_flops / results["torch"] / 1e9},
-        "gpu_launches": args.steps * (len(shapes) * 15 + 8),
+                   "weight_decay": cfg["wd"], "matrices": len(m["shapes"]), "elements": m["elements"]},
+        "calibration_first_step_ms": m["calibration_ms"], "clocks": m["clocks"],
+        "roofline": m["roofline"],
+        "gpu_launches": args.steps * (len(m["shapes"]) * 15 + 8),
     }
     print(json.dumps(line))
+
+
+def run_flat_sweep(args):
+    """Flat-tensor sweep: one fp32 parameter tensor and gradient of 2^20 ... 2^30 elements, gradients N(0,1) times
+    a log-normal scale per 4096-element run. Per size: one fused step (steady state) and every pass of the
+    calibration on its own (period scan of all candidate periods, exact histogram, exact-DP codebook fit, one
+    Lloyd-Max accumulation), each as ms and as GB/s of its algorithmic bytes (step: 14 B per element; a
+    calibration pass: one 4-byte read per element) against the measured copy bandwidth."""
+    from gefen_b200 import Gefen, partitioning, quantization
+    from gefen_b200.kernels.exact_histogram_fused import gefen_exact_histogram_cuda
+    from gefen_b200.kernels.lloyd_max_fused import gefen_lloyd_accumulate_cuda
+
+    device = torch.device("cuda", 0)
+    peak, peak_kind = measured_peaks()
+    rows = []
+    for log2n in (20, 24, 28, 30):
+        if log2n > args.sweep_max_log2:
+            continue
+        n = 1 << log2n
+        gen = torch.Generator(device=device).manual_seed(log2n)
+        g = torch.randn(n // 4096, 4096, generator=gen, device=device)
+        g.mul_(torch.exp(torch.randn(n // 4096, 1, generator=gen, device=device)))
+        g = g.reshape(-1)
+        p = torch.nn.Parameter(torch.randn(n, generator=gen, device=device) * 0.02)
+        p.grad = g
+        opt = Gefen([p], lr=1e-3)
+        first_ms = timed(opt.step, 1)
+        period = opt.state[p]["automatic_period"]
+        for _ in range(3):
+            opt.step()
+        k = max(3, min(args.steps, 20 if log2n <= 24 else 5))
+        step_ms = timed(opt.step, k)
+        opt.check()
+        step_bytes = 14 * n + (n // period) * 16
+
+        def scan():
+            return partitioning.find_period_by_block_variance(g, print_results=False, backend="cuda_kernel",
+                                                              input_is_squared=False)
+
+        scan()
+        scan_ms = timed(scan, 3)
+        counts = torch.zeros(4096, dtype=torch.int64, device=device)
+        gefen_exact_histogram_cuda(g, period, counts)
+        hist_ms = timed(lambda: gefen_exact_histogram_cuda(g, period, counts), 5)
+        counts.zero_()
+        gefen_exact_histogram_cuda(g, period, counts)
+        host = counts.cpu().to(torch.float32)
+        edges = torch.linspace(-1.0, 1.0, steps=4097, dtype=torch.float32)
+        centers = 0.5 * (edges[:-1] + edges[1:])
+        active = host > 0
+        stats = {"active_centers": centers[active], "active_counts": host[active]}
+        quantization.exact_dp(stats, 256, True, device=device)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        quantization.exact_dp(stats, 256, True, device=device)
+        dp_ms = 1e3 * (time.perf_counter() - t0)
+        cb = opt._gefen_codebook
+        sums = torch.zeros(256, device=device)
+        cnts = torch.zeros(256, dtype=torch.int64, device=device)
+        gefen_lloyd_accumulate_cuda(g, cb, period, sums, cnts)
+        lloyd_ms = timed(lambda: gefen_lloyd_accumulate_cuda(g, cb, period, sums, cnts), 5)
+        read_bytes = 4 * n
+
+        def gbs(nbytes, ms):
+            return nbytes / ms / 1e6
+
+        rows.append({"log2_elements": log2n, "period": period, "first_step_ms_with_calibration": first_ms,
+                     "step_ms": step_ms, "step_gbs": gbs(step_bytes, step_ms), "step_frac": gbs(step_bytes, step_ms) / peak,
+                     "period_scan_ms": scan_ms, "period_scan_gbs": gbs(read_bytes, scan_ms),
+                     "histogram_ms": hist_ms, "histogram_gbs": gbs(read_bytes, hist_ms), "histogram_frac": gbs(read_bytes, hist_ms) / peak,
+                     "exact_dp_ms": dp_ms, "active_bins": int(active.sum()),
+                     "lloyd_accumulate_ms": lloyd_ms, "lloyd_accumulate_gbs": gbs(read_bytes, lloyd_ms),
+                     "lloyd_accumulate_frac": gbs(read_bytes, lloyd_ms) / peak})
+        del opt, p, g
+        torch.cuda.empty_cache()
+    print(json.dumps({"metric": "flat_sweep", "unit": "ms and GB/s", "n_gpus": 1, "dtype": "f32", "data": "synthetic",
+                      "peak_gbs": peak, "peak_kind": peak_kind + " copy bandwidth",
+                      "config": {"workload": "flat_sweep", "optimizer": "Gefen(fused=True)", "lr": 1e-3,
+                                 "note": "L2 is flushed by the inputs themselves from 2^24 elements on; the 2^20 point "
+                                         "(14 MB per step) runs out of L2"},
+                      "sweep": rows}))
 
 
 def run_microbench(spec: str, steps: int, warmup: int):
@@ -493,12 +735,11 @@ def run_microbench_other(spec: str, steps: int, warmup: int):
         g = (torch.randn(rows, cols, generator=gen, device=dev) * 1e-3).bfloat16()
         coeffs = (3.4445, -4.7750, 2.0315)
         res = {}
-        for mode in ("tcgen05", "torch"):
-            ns.USE_TCGEN05 = mode == "tcgen05"
+        for mode, fn in (("tcgen05", lambda: ns.zeropower_via_newtonschulz(g, coeffs, 5, 1e-7)),
+                         ("torch", lambda: torch_newton_schulz(g, coeffs, 5, 1e-7))):
             for _ in range(max(warmup, 3)):
-                ns.zeropower_via_newtonschulz(g, coeffs, 5, 1e-7)
-            res[mode] = timed(lambda: ns.zeropower_via_newtonschulz(g, coeffs, 5, 1e-7), steps)
-        ns.USE_TCGEN05 = True
+                fn()
+            res[mode] = timed(fn, steps)
         ns.check_status(dev)
         flops = ns_flops((rows, cols))
         out.update({"ms": res["tcgen05"], "tflops": flops / res["tcgen05"] / 1e9, "torch_ms": res["torch"],
@@ -575,16 +816,22 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="gefen_b200", choices=["gefen_b200", "reference"])
-    ap.add_argument("--workload", default="llama_1_5b", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="llama_1_5b", choices=sorted(WORKLOADS) + ["flat_sweep"])
     ap.add_argument("--cpu-sample-elems", type=int, default=62_000_000,
                     help="size of the CPU baseline's sample of the workload, in elements")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--e2e-buckets", type=int, default=8)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-cuda", action="store_true", help="skip timing the reference's CUDA kernels")
+    ap.add_argument("--no-muon", action="store_true", help="skip the GefenMuon summary of the default line")
+    ap.add_argument("--sweep-max-log2", type=int, default=30, help="flat_sweep: largest tensor, log2 of its elements")
     ap.add_argument("--microbench", default=None, help="dtype:period:blocks, single-tensor step kernel only")
     args = ap.parse_args()
     if args.microbench:
         run_microbench(args.microbench, args.steps, args.warmup)
+        return
+    if args.workload == "flat_sweep":
+        run_flat_sweep(args)
         return
     cfg = WORKLOADS[args.workload]
 
@@ -593,7 +840,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     if args.impl == "reference":
-        run_reference_arm(args, cfg, rank)
+        run_reference_arm(args, cfg, rank, world)
         return
 
     if cfg.get("muon"):
@@ -618,23 +865,22 @@ def main():
 
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    result, e2e = run_gpu_arm(args, cfg, rank, world, local_rank)
+        result, e2e = run_sharded_arm(args, cfg, rank, world, local_rank)
+    else:
+        result, e2e = run_gpu_arm(args, cfg, rank, world, local_rank)
     if rank == 0:
         peak, peak_kind = measured_peaks()
         ms = result["ms"]
         eff_gbs = result["algo_bytes"] / ms / 1e6
+        shapes, periods = result["shapes"], result["periods"]
         line = {
             "metric": "optimizer_step_ms", "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": ms / PUBLISHED_LLAMA_1_5B_MS if args.workload == "llama_1_5b" else None,
             "vs_baseline_note": "reference README: Gefen step 29 ms for Llama 3 1.5B, hardware not stated",
             "dtype": "bf16" if cfg["dtype"] == torch.bfloat16 else "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "optimizer": "Gefen(fused=True)", "lr": cfg["lr"],
-                       "weight_decay": cfg["wd"], "betas": [0.9, 0.999], "eps": 1e-8,
-                       "tensors": result["n_tensors"], "elements": result["total_elems"],
-                       "parallelism": "zero1-dp{}".format(world) if world > 1 else "single-gpu",
-                       "l2": "inputs ({:.1f} GB per step) are larger than L2".format(result["algo_bytes"] / 1e9),
-                       "periods": result["periods"], "elements_by_period": result["period_elements"]},
+            "config": workload_config(args, cfg, world, result["n_tensors"], result["total_elems"], periods,
+                                      period_census(shapes, periods), result["algo_bytes"]),
             "effective_hbm_gbs": eff_gbs, "effective_hbm_frac_of_{}".format(peak_kind): eff_gbs * (1 if world == 1 else 1.0 / world) / peak,
             "algorithmic_bytes_per_step": result["algo_bytes"],
             "calibration_first_step_ms": result["calibration_ms"],
@@ -646,15 +892,29 @@ def main():
         if "breakdown" in result:
             line["breakdown_ms"] = result["breakdown"]
             line["gpu_launches"] = result["breakdown"].get("kernel_launches_per_step", 0) * args.steps
+        if "n_vs_1" in result:
+            line["n_vs_1"] = result["n_vs_1"]
+        if "reference_cuda" in result:
+            line["reference_cuda"] = result["reference_cuda"]
         if e2e is not None:
             line["e2e"] = e2e
+        if world == 1 and not args.no_muon and args.workload == "llama_1_5b":
+            # GefenMuon on the Qwen3-1.7B-shaped matrices, measured after everything above (its own tensors)
+            torch.cuda.empty_cache()
+            try:
+                line["muon"] = measure_muon(WORKLOADS["qwen3_muon"], max(2, min(args.steps, 5)), 3)["summary"]
+            except Exception as exc:   # the summary is an extra: never lose the headline line to it
+                line["muon"] = {"unavailable": "{}: {}".format(type(exc).__name__, str(exc)[:160])}
         if world == 1 and not args.no_cpu_baseline:
             torch.set_num_threads(os.cpu_count() or 1)
-            cms, sample, total, calib_s, cores = cpu_port_step_ms(cfg, 2, 1, args.cpu_sample_elems)
+            run = cpu_port_run(cfg, 2, 1, args.cpu_sample_elems)
+            scaled = run["ms"] * result["total_elems"] / run["elements"]
             line["cpu_baseline"] = {
-                "value": cms, "unit": "ms", "cores": cores, "kind": "port",
-                "sample": "{} of {} elements (one transformer layer's tensors), steady-state step of the C oracle "
-                          "with OpenMP, scaled by element count".format(sample, total)}
+                "value": scaled, "unit": "ms", "cores": run["cores"], "kind": "port",
+                "sample": "{} of {} elements (the tensors of the first transformer layers, whole tensors): the C "
+                          "oracle with OpenMP, its own calibration, {} steady-state steps at {:.0f} ms each, scaled "
+                          "by element count to the whole workload (`--impl reference` runs the whole workload)"
+                          .format(run["elements"], result["total_elems"], run["timed_steps"], run["ms"])}
         print(json.dumps(line))
     if world > 1:
         import torch.distributed as dist

@@ -3,7 +3,7 @@
 // The workspace turns "nearest codebook entry, left on ties" (reference:
 // kernels/automatic_gefen_fused_kernel.cu:59-90) into data the step kernels can stage into
 // shared memory with one bulk copy: the padded codebook, the 255 exact decision thresholds and
-// an 8193-cell table over [-1, 1] that resolves an element with one 8-byte read and one compare.
+// a 4097-cell table over [-1, 1] that resolves an element with one 8-byte read and one compare.
 #include "common.cuh"
 
 #include <mutex>

@@ -64,8 +64,14 @@ struct StepLaunch {
     int n_grad_srcs;
     float grad_scale;
     long long grad_delta[GEFEN_B200_MAX_PEERS + 1];
-    // register-resident path: warps that share one block (see step_reg_kernel)
-    int warps_per_block;
+    // NVLink multicast (NVSwitch) mappings of the ranks' buffers, as byte distances from this GPU's own
+    // buffer; 0 = not used. grad_mc_delta: the staged kernel reads every gradient chunk with one
+    // multimem.ld_reduce (the switch adds the ranks' copies, fp32 accumulation) instead of n_grad_srcs
+    // peer loads. param_mc_delta: every updated parameter chunk leaves with one multimem.st that the
+    // switch delivers to all ranks' copies, this GPU's included, instead of a local store plus n_peers
+    // peer stores.
+    long long grad_mc_delta;
+    long long param_mc_delta;
     // iteration limit of the wait for the staged tables (g_stage_spin_limit on the host)
     unsigned int spin_limit;
 };
@@ -147,9 +153,48 @@ __device__ __forceinline__ int find_tensor(const gefen_b200_step_tensor_t* table
 // --------------------------------------------------------------------------- vector IO
 // A "chunk" is 8 consecutive elements: 8 code bytes, 16 B of bf16/f16 or 32 B of fp32. Everything is
 // read once per step: the loads carry the streaming (evict-first) hint.
+// 16-byte accesses to a multicast address: the store reaches every GPU's copy, the load returns the
+// element-wise sum of all copies (added in the switch, fp32 accumulation for the 2-byte types).
+__device__ __forceinline__ void multimem_store16(void* mc_addr, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z),
+                 "r"(v.w)
+                 : "memory");
+}
+template <typename S> __device__ __forceinline__ uint4 multimem_load_sum16(const void* mc_addr);
+template <> __device__ __forceinline__ uint4 multimem_load_sum16<__nv_bfloat16>(const void* mc_addr) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc_addr)
+                 : "memory");
+    return v;
+}
+template <> __device__ __forceinline__ uint4 multimem_load_sum16<__half>(const void* mc_addr) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc_addr)
+                 : "memory");
+    return v;
+}
+template <> __device__ __forceinline__ uint4 multimem_load_sum16<float>(const void* mc_addr) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc_addr)
+                 : "memory");
+    return v;
+}
+
 template <typename S> struct Chunk;
 template <> struct Chunk<__nv_bfloat16> {
     uint4 raw;
+    __device__ __forceinline__ void load_sum(const void* mc_base, long long chunk) {
+        raw = multimem_load_sum16<__nv_bfloat16>(reinterpret_cast<const uint4*>(mc_base) + chunk);
+    }
+    __device__ __forceinline__ void store_all(void* mc_base, long long chunk) const {
+        multimem_store16(reinterpret_cast<uint4*>(mc_base) + chunk, raw);
+    }
     __device__ __forceinline__ void load(const void* base, long long chunk) {
         raw = __ldcs(reinterpret_cast<const uint4*>(base) + chunk);
     }
@@ -176,6 +221,12 @@ template <> struct Chunk<__nv_bfloat16> {
 };
 template <> struct Chunk<__half> {
     uint4 raw;
+    __device__ __forceinline__ void load_sum(const void* mc_base, long long chunk) {
+        raw = multimem_load_sum16<__half>(reinterpret_cast<const uint4*>(mc_base) + chunk);
+    }
+    __device__ __forceinline__ void store_all(void* mc_base, long long chunk) const {
+        multimem_store16(reinterpret_cast<uint4*>(mc_base) + chunk, raw);
+    }
     __device__ __forceinline__ void load(const void* base, long long chunk) {
         raw = __ldcs(reinterpret_cast<const uint4*>(base) + chunk);
     }
@@ -203,6 +254,18 @@ template <> struct Chunk<__half> {
 };
 template <> struct Chunk<float> {
     float4 lo, hi;
+    __device__ __forceinline__ void load_sum(const void* mc_base, long long chunk) {
+        const uint4 a = multimem_load_sum16<float>(reinterpret_cast<const uint4*>(mc_base) + 2 * chunk);
+        const uint4 b = multimem_load_sum16<float>(reinterpret_cast<const uint4*>(mc_base) + 2 * chunk + 1);
+        lo = make_float4(__uint_as_float(a.x), __uint_as_float(a.y), __uint_as_float(a.z), __uint_as_float(a.w));
+        hi = make_float4(__uint_as_float(b.x), __uint_as_float(b.y), __uint_as_float(b.z), __uint_as_float(b.w));
+    }
+    __device__ __forceinline__ void store_all(void* mc_base, long long chunk) const {
+        multimem_store16(reinterpret_cast<uint4*>(mc_base) + 2 * chunk,
+                         make_uint4(__float_as_uint(lo.x), __float_as_uint(lo.y), __float_as_uint(lo.z), __float_as_uint(lo.w)));
+        multimem_store16(reinterpret_cast<uint4*>(mc_base) + 2 * chunk + 1,
+                         make_uint4(__float_as_uint(hi.x), __float_as_uint(hi.y), __float_as_uint(hi.z), __float_as_uint(hi.w)));
+    }
     __device__ __forceinline__ void load(const void* base, long long chunk) {
         lo = __ldcs(reinterpret_cast<const float4*>(base) + 2 * chunk);
         hi = __ldcs(reinterpret_cast<const float4*>(base) + 2 * chunk + 1);
@@ -272,10 +335,12 @@ __device__ __forceinline__ float group_sum(float v, int lanes) {
 
 // First pass over U chunks of one lane (chunks c0, c0 + LANES, ...): all loads first, then the
 // moment update, the running absmax and sum of squares, and the staging of the updated momenta.
-template <typename S, int U, bool GUARD>
+// SUMMED: g_blk is the multicast address of the block's gradients; a load returns the sum over the ranks,
+// which is scaled by `scale` and rounded to the gradient dtype as a reduce-scatter into it would leave it.
+template <typename S, int U, bool GUARD, bool SUMMED>
 __device__ __forceinline__ void first_pass_group(const S* g_blk, const uint2* codes_in, float4* stage_a, float4* stage_b,
                                                  const float* rep, int c0, int LANES, int nchunks, float old_mag,
-                                                 float beta1, float omb1, float& absmax, float& sumsq) {
+                                                 float beta1, float omb1, float scale, float& absmax, float& sumsq) {
     uint2 craw[U];
     Chunk<S> graw[U];
 #pragma unroll
@@ -283,7 +348,8 @@ __device__ __forceinline__ void first_pass_group(const S* g_blk, const uint2* co
         const int c = c0 + LANES * u;
         if (!GUARD || c < nchunks) {
             craw[u] = __ldcs(codes_in + c);
-            graw[u].load(g_blk, c);
+            if (SUMMED) graw[u].load_sum(g_blk, c);
+            else graw[u].load(g_blk, c);
         }
     }
 #pragma unroll
@@ -292,6 +358,13 @@ __device__ __forceinline__ void first_pass_group(const S* g_blk, const uint2* co
         if (!GUARD || c < nchunks) {
             float g[8], m[8];
             graw[u].unpack(g);
+            if (SUMMED) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) g[i] *= scale;
+                Chunk<S> rounded;
+                rounded.pack(g);
+                rounded.unpack(g);
+            }
             const uint32_t cw[2] = {craw[u].x, craw[u].y};
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -384,11 +457,14 @@ __device__ __forceinline__ void reduce_pass(const StepLaunch& L, const S* g_blk,
 // second halves, so that the 128-bit shared accesses of a full warp are conflict-free.
 // The descriptor lives in global or parameter memory, which the stores below might alias as far as
 // the compiler can tell: everything the loops need from it is copied into locals first.
-template <typename S, bool REDUCE, bool FULL>
+// GSRC: where the gradients come from: 0 = this GPU's buffer, 1 = averaged over the ranks' buffers with peer
+// loads, 2 = summed by the switch through the multicast mapping (StepLaunch::grad_mc_delta).
+template <typename S, int GSRC, bool FULL>
 __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& t, long long unit, const StepLaunch& L,
                                                 const SmemView& s, float* stage, int warp_lane) {
     const float* const stepsize = L.stepsize;
     const int n_peers = L.n_peers;
+    const long long param_mc = L.param_mc_delta;
     const int period = static_cast<int>(t.period);     // at most kFastMaxPeriod
     const int LANES = FULL ? 32 : lanes_per_block(period);
     const int lane = warp_lane & (LANES - 1);          // lane within the block's group
@@ -429,7 +505,13 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
     // ---- pass over codes and gradients (the only read of both)
     float absmax = 0.0f;
     float sumsq = 0.0f;
-    if (REDUCE) {
+    if (GSRC == 2) {
+        constexpr int U = FULL ? 4 : 1;
+        const S* const g_sum = peer_ptr(g_blk, L.grad_mc_delta);
+        for (int c0 = lane; c0 < nchunks; c0 += LANES * U)
+            first_pass_group<S, U, true, true>(g_sum, codes_in, stage_a, stage_b, rep, c0, LANES, nchunks, old_mag, beta1, omb1,
+                                               L.grad_scale, absmax, sumsq);
+    } else if (GSRC == 1) {
         // The gradient of this block is the average over the ranks' buffers (this GPU's and the
         // peers', read over NVLink), summed in fp32 in rank order and rounded to the gradient dtype,
         // as a reduce-scatter into that dtype would leave it.
@@ -442,8 +524,8 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
         // (a separate loop without bounds tests for the complete groups was measured: slower, it
         // costs registers)
         for (int c0 = lane; c0 < nchunks; c0 += LANES * U)
-            first_pass_group<S, U, true>(g_blk, codes_in, stage_a, stage_b, rep, c0, LANES, nchunks, old_mag, beta1, omb1,
-                                         absmax, sumsq);
+            first_pass_group<S, U, true, false>(g_blk, codes_in, stage_a, stage_b, rep, c0, LANES, nchunks, old_mag, beta1, omb1,
+                                                1.0f, absmax, sumsq);
     }
     absmax = group_max_nan(absmax, LANES);
 
@@ -559,8 +641,12 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
 #pragma unroll
             for (int i = 0; i < 8; ++i) pv[i] = fmaf(-(q[i] * step), lr, pv[i]);
             praw.pack(pv);
-            praw.store(p_blk, c);
-            for (int r = 0; r < n_peers; ++r) praw.store(peer_ptr(p_blk, L.peer_delta[r]), c);
+            if (param_mc != 0) {
+                praw.store_all(peer_ptr(p_blk, param_mc), c);   // every rank's copy, this one included
+            } else {
+                praw.store(p_blk, c);
+                for (int r = 0; r < n_peers; ++r) praw.store(peer_ptr(p_blk, L.peer_delta[r]), c);
+            }
         }
     }
     __syncwarp();  // the staging slice is free for this warp's next block
@@ -570,13 +656,13 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
 // fp32, whose wider chunks need the full 128.
 // The variant that averages gradients over NVLink holds more loads in flight per thread and is not
 // bound by occupancy: sixteen warps of 128 registers for every type.
-template <typename S, bool REDUCE> __host__ __device__ constexpr int vec_max_threads() {
-    return (sizeof(S) == 2 && !REDUCE) ? 640 : 512;
+template <typename S, int GSRC> __host__ __device__ constexpr int vec_max_threads() {
+    return (sizeof(S) == 2 && GSRC != 1) ? 640 : 512;
 }
 
-// REDUCE: the gradients are averaged over the ranks' buffers inside the kernel (StepLaunch::grad_delta).
-template <typename S, bool REDUCE>
-__global__ void __launch_bounds__(vec_max_threads<S, REDUCE>(), 1) step_vec_kernel(const __grid_constant__ StepLaunch L,
+// GSRC: see warp_block_step.
+template <typename S, int GSRC>
+__global__ void __launch_bounds__(vec_max_threads<S, GSRC>(), 1) step_vec_kernel(const __grid_constant__ StepLaunch L,
                                                            const __grid_constant__ gefen_b200_step_tensor_t single) {
     extern __shared__ __align__(128) unsigned char smem[];
     SmemView s;
@@ -608,347 +694,15 @@ __global__ void __launch_bounds__(vec_max_threads<S, REDUCE>(), 1) step_vec_kern
         const long long nb_local = gb - t_first;
         const long long next = nb_local + warp_stride;
         // same tensor: hint the next block of this warp (measured: pays for 2-byte dtypes with long blocks only)
-        if (!REDUCE && sizeof(S) == 2 && t.period >= 1024 && next < t_count) {
+        if (GSRC == 0 && sizeof(S) == 2 && t.period >= 1024 && next < t_count) {
             const long long elem0 = next * t.period;
             prefetch_l2_range(t.codes + elem0, t.period, lane);
             prefetch_l2_range(static_cast<const char*>(t.g) + elem0 * sizeof(S), t.period * sizeof(S), lane);
             if (!(t.flags & GEFEN_B200_STEP_MUON))
                 prefetch_l2_range(static_cast<const char*>(t.p) + elem0 * sizeof(S), t.period * sizeof(S), lane);
         }
-        if (t.period >= 256) warp_block_step<S, REDUCE, true>(t, nb_local, L, s, stage, lane);
-        else warp_block_step<S, REDUCE, false>(t, nb_local, L, s, stage, lane);
-    }
-}
-
-// --------------------------------------------------------------------------- register-resident path
-// Blocks of 512 to 8192 elements (a multiple of 8). W = ceil(period / 512) consecutive warps of a
-// CTA own one block; every lane holds two chunks (16 elements) of it, and the updated momenta stay
-// in registers between the absmax reduction and the re-encoding: nothing is staged in shared
-// memory, so the warps per SM are bound by registers only, and the loops are two chunks long. The
-// warps of a block meet once per block at a named barrier after exchanging their partial absmax
-// and sum of squares through shared memory. Codes, gradients and the old magnitude of the group's
-// NEXT block are requested before the current block is worked on (2-byte types), so that a block
-// never starts on a global-load wait.
-// The codebook is replicated per lane in rows of 256 bytes (entry e of lane l at byte 256 e + 4 l):
-// the byte offset of a lookup is one byte permute of the code with the lane's offset.
-constexpr int kRegChunksPerLane = 2;
-constexpr int kRegRowBytes = 256;
-constexpr int kSmemWsPadded = (kSmemWs + 255) / 256 * 256;
-constexpr int kSmemRepWide = kMaxCodebook * kRegRowBytes;
-constexpr int kRegMaxWarpsPerBlock = 16;
-constexpr int kRegMaxGroups = 12;       // groups that exchange through shared memory (W >= 2)
-constexpr int kRegMinPeriod = 512;
-constexpr int kRegMaxPeriod = 512 * kRegMaxWarpsPerBlock;
-
-__host__ __device__ __forceinline__ int reg_warps_per_block(long long period) {
-    return static_cast<int>((period + 511) / 512);
-}
-
-__device__ __forceinline__ void group_barrier(int id, int threads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-
-// cb[code] for this lane: `word` holds the code in byte `BYTE`, lane4 = 4 * lane.
-template <int BYTE>
-__device__ __forceinline__ float rep_lookup(const unsigned char* rep, uint32_t word, uint32_t lane4) {
-    const uint32_t off = __byte_perm(word, lane4, 0x5504u | (static_cast<uint32_t>(BYTE) << 4));
-    return *reinterpret_cast<const float*>(rep + off);
-}
-
-__device__ __forceinline__ float round_state(float value, int dtype) {
-    if (dtype == GEFEN_B200_F32) return value;
-    if (dtype == GEFEN_B200_BF16) return __bfloat162float(__float2bfloat16_rn(value));
-    return __half2float(__float2half_rn(value));
-}
-
-// What a warp holds of a block before it works on it.
-template <typename S>
-struct RegBlockInputs {
-    uint2 codes[kRegChunksPerLane];
-    Chunk<S> grads[kRegChunksPerLane];
-    float old_mag;
-};
-
-template <typename S>
-__device__ __forceinline__ void reg_request(const gefen_b200_step_tensor_t& t, long long b, int wg, int lane,
-                                            RegBlockInputs<S>& in) {
-    const int period = static_cast<int>(t.period);
-    const int nchunks = period >> 3;
-    const long long elem0 = b * static_cast<long long>(period);
-    const uint2* codes = reinterpret_cast<const uint2*>(t.codes + elem0);
-    const S* g_blk = static_cast<const S*>(t.g) + elem0;
-#pragma unroll
-    for (int u = 0; u < kRegChunksPerLane; ++u) {
-        const int c = (wg * kRegChunksPerLane + u) * 32 + lane;
-        if (c < nchunks) {
-            in.codes[u] = __ldcs(codes + c);
-            in.grads[u].load(g_blk, c);
-        }
-    }
-    in.old_mag = load_state(t.mag, b, t.mag_dtype);
-}
-
-template <typename S>
-__device__ __forceinline__ void reg_block_step(const gefen_b200_step_tensor_t& t, long long b, const StepLaunch& L,
-                                               const unsigned char* smem, const SmemView& s,
-                                               const RegBlockInputs<S>& in, int W, int wg, int grp, int lane,
-                                               float2 (*xchg)[kRegMaxWarpsPerBlock], float (*xchg_exact)[kRegMaxWarpsPerBlock]) {
-    constexpr int CPL = kRegChunksPerLane;
-    const unsigned char* const rep = smem + kSmemWsPadded;
-    const unsigned char* const lut = smem + kWsLutOff;
-    const uint32_t lane4 = static_cast<uint32_t>(lane) << 2;
-    const int period = static_cast<int>(t.period);
-    const int nchunks = period >> 3;
-    const long long elem0 = b * static_cast<long long>(period);
-    uint2* const codes_out = reinterpret_cast<uint2*>(t.codes + elem0);
-    const S* const g_blk = static_cast<const S*>(t.g) + elem0;
-    S* const p_blk = static_cast<S*>(t.p) + elem0;
-    const uint32_t flags = t.flags;
-    const bool muon = (flags & GEFEN_B200_STEP_MUON) != 0;
-    const float beta1 = t.beta1;
-    const float omb1 = 1.0f - beta1;
-    const float lr = t.lr;
-    const bool do_update = muon || lr != 0.0f;
-    const bool load_p = !muon && do_update;
-    const float old_mag = in.old_mag;
-
-    int chunk[CPL];
-    bool ok[CPL];
-    Chunk<S> praw[CPL];
-#pragma unroll
-    for (int u = 0; u < CPL; ++u) {
-        chunk[u] = (wg * CPL + u) * 32 + lane;
-        ok[u] = chunk[u] < nchunks;
-        if (load_p && ok[u]) praw[u].load(p_blk, chunk[u]);
-    }
-    float v_in = 1.0f;
-    if (!muon) v_in = L.stepsize != nullptr ? L.stepsize[b] : load_state(t.v, b, t.v_dtype);
-
-    // ---- moment update; the momenta stay in registers
-    float m[CPL * 8];
-    float absmax = 0.0f, sumsq = 0.0f;
-#pragma unroll
-    for (int u = 0; u < CPL; ++u) {
-        if (ok[u]) {
-            float g[8];
-            in.grads[u].unpack(g);
-            const uint32_t c0 = in.codes[u].x, c1 = in.codes[u].y;
-            const float cbv[8] = {rep_lookup<0>(rep, c0, lane4), rep_lookup<1>(rep, c0, lane4), rep_lookup<2>(rep, c0, lane4),
-                                  rep_lookup<3>(rep, c0, lane4), rep_lookup<0>(rep, c1, lane4), rep_lookup<1>(rep, c1, lane4),
-                                  rep_lookup<2>(rep, c1, lane4), rep_lookup<3>(rep, c1, lane4)};
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float cur = old_mag * cbv[i];
-                const float mi = ema_update(beta1, cur, omb1, g[i]);
-                m[u * 8 + i] = mi;
-                absmax = max_abs_nan(absmax, mi);
-                sumsq = fmaf(g[i], g[i], sumsq);
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) m[u * 8 + i] = 0.0f;
-        }
-    }
-    absmax = warp_max_nan(absmax);
-    sumsq = warp_sum(sumsq);
-    if (W > 1) {
-        // partial results of the block's warps, combined in warp order by everyone. Two slots in turn:
-        // a warp can be at most one barrier ahead of the slowest warp of its group.
-        float2* slot = xchg[grp];
-        if (lane == 0) slot[wg] = make_float2(absmax, sumsq);
-        group_barrier(grp + 1, W * 32);
-        absmax = 0.0f;
-        sumsq = 0.0f;
-        for (int w = 0; w < W; ++w) {
-            const float2 part = slot[w];
-            asm("max.NaN.f32 %0, %1, %2;" : "=f"(absmax) : "f"(absmax), "f"(part.x));
-            sumsq += part.y;
-        }
-    }
-
-    // ---- second moment (optionally fused) and the step size
-    float step = 0.0f;
-    if (!muon) {
-        if (L.stepsize != nullptr) {
-            step = v_in;
-        } else {
-            float v = v_in;
-            if (flags & GEFEN_B200_STEP_FUSE_VMEAN) {
-                const float mean_sq = sumsq / static_cast<float>(period);
-                const float nv = fmaf(t.beta2, v_in, (1.0f - t.beta2) * mean_sq);
-                v = round_state(nv, t.v_dtype);
-                if (wg == 0 && lane == 0) store_state(t.v, b, t.v_dtype, nv);
-            }
-            step = adam_step_size(v, t.bc1, t.bc2, t.eps);
-        }
-    }
-
-    // ---- rare: a NaN or Inf in the block. The reference's max ignores NaN; redo it that way and
-    // let the exact (threshold) quantiser handle non-finite quotients. The test is uniform over the
-    // block's warps: they all hold the same absmax.
-    bool exact_path = false;
-    if (!(absmax <= 3.0e38f)) {
-        float mx = 0.0f;
-#pragma unroll
-        for (int i = 0; i < CPL * 8; ++i) mx = fmaxf(mx, fabsf(m[i]));
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        if (W > 1) {
-            float* slot = xchg_exact[grp];
-            if (lane == 0) slot[wg] = mx;
-            group_barrier(grp + 1, W * 32);
-            mx = 0.0f;
-            for (int w = 0; w < W; ++w) mx = fmaxf(mx, slot[w]);
-        }
-        absmax = mx;
-        exact_path = true;
-    }
-    if (wg == 0 && lane == 0) store_state(t.mag, b, t.mag_dtype, absmax);
-
-    const bool nonzero = absmax > 0.0f;
-    const bool fastdiv = !exact_path && div_range_ok(absmax);
-    const float rinv = fastdiv ? 1.0f / absmax : 0.0f;
-    const bool wd = (flags & GEFEN_B200_STEP_WEIGHT_DECAY) != 0;
-    const bool nesterov = (flags & GEFEN_B200_STEP_NESTEROV) != 0;
-    const float wd_mul = t.wd_mul;
-    const float nesterov_alpha = t.beta2;
-    const int n_peers = L.n_peers;
-
-    // ---- re-encode and update
-#pragma unroll
-    for (int u = 0; u < CPL; ++u) {
-        if (!ok[u]) continue;
-        uint32_t code[8];
-        if (fastdiv) {
-            uint32_t any = 0u;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float x = div_by_block_constant(m[u * 8 + i], absmax, rinv);
-                code[i] = lut_query_fast(x, lut);
-                any |= code[i];
-            }
-            if (any & kLutSlowBit) {   // rare: a cell with two thresholds, or values above the last entry
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    if (code[i] & kLutSlowBit) {
-                        const float x = div_by_block_constant(m[u * 8 + i], absmax, rinv);
-                        code[i] = static_cast<uint32_t>(entry_exact(x, s.thr, s.cb, s.k));
-                    }
-                }
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                float x = 0.0f;
-                if (nonzero) x = m[u * 8 + i] / absmax;
-                code[i] = static_cast<uint32_t>(entry_exact(x, s.thr, s.cb, s.k));
-            }
-        }
-        float q[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) q[i] = rep_lookup<0>(rep, code[i], lane4) * absmax;
-        uint2 cw;
-        cw.x = __byte_perm(__byte_perm(code[0], code[1], 0x0040), __byte_perm(code[2], code[3], 0x0040), 0x5410);
-        cw.y = __byte_perm(__byte_perm(code[4], code[5], 0x0040), __byte_perm(code[6], code[7], 0x0040), 0x5410);
-        codes_out[chunk[u]] = cw;
-        if (muon) {
-            if (nesterov) {
-                // torch: m.mul_(momentum).add_(g, alpha=1-momentum) on the rounded momentum
-                // (reference: gefen_muon.py:312-314); alpha travels in t.beta2.
-                Chunk<S> g2;
-                g2.load(g_blk, chunk[u]);
-                float g[8];
-                g2.unpack(g);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float m1 = ScalarIO<S>::round(ScalarIO<S>::round(q[i]) * beta1);
-                    q[i] = fmaf(nesterov_alpha, g[i], m1);
-                }
-            }
-            Chunk<S> out;
-            out.pack(q);
-            out.store(p_blk, chunk[u]);
-        } else if (do_update) {
-            float pv[8];
-            praw[u].unpack(pv);
-            if (wd) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) pv[i] *= wd_mul;
-                Chunk<S> rounded;       // the separate multiply of the reference rounds to the parameter dtype
-                rounded.pack(pv);
-                rounded.unpack(pv);
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) pv[i] = fmaf(-(q[i] * step), lr, pv[i]);
-            Chunk<S> out;
-            out.pack(pv);
-            out.store(p_blk, chunk[u]);
-            for (int r = 0; r < n_peers; ++r) out.store(peer_ptr(p_blk, L.peer_delta[r]), chunk[u]);
-        }
-    }
-}
-
-template <typename S, int MAXW>
-__global__ void __launch_bounds__(MAXW * 32, 1) step_reg_kernel(const __grid_constant__ StepLaunch L,
-                                                                const __grid_constant__ gefen_b200_step_tensor_t single) {
-    extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ float2 xchg[2][kRegMaxGroups][kRegMaxWarpsPerBlock];
-    __shared__ float xchg_exact[kRegMaxGroups][kRegMaxWarpsPerBlock];
-    SmemView s;
-    if (!stage_tables(L.ws, smem, s, L.spin_limit)) return;
-    const gefen_b200_step_tensor_t* table = L.table != nullptr ? L.table : &single;
-    {
-        float* rep = reinterpret_cast<float*>(smem + kSmemWsPadded);
-        for (int i = threadIdx.x; i < kMaxCodebook * 32; i += blockDim.x) rep[(i >> 5) * (kRegRowBytes / 4) + (i & 31)] = s.cb[i >> 5];
-        __syncthreads();
-    }
-    const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-    const int W = L.warps_per_block;
-    const int grp = warp / W;
-    const int wg = warp - grp * W;
-    const int groups = static_cast<int>(blockDim.x >> 5) / W;
-    const long long stride = static_cast<long long>(gridDim.x) * groups;
-    long long gb = static_cast<long long>(blockIdx.x) * groups + grp;
-    if (gb >= L.total_blocks) return;   // the whole group leaves together
-
-    // the tensor that owns a global block index; consecutive blocks of a group mostly share it
-    const gefen_b200_step_tensor_t* tp = table;
-    long long t_first = tp->first_block, t_count = tp->num_blocks;
-    auto locate = [&](long long block) {
-        if (block < t_first || block >= t_first + t_count) {
-            tp = table + find_tensor(table, L.n_tensors, block);
-            t_first = tp->first_block;
-            t_count = tp->num_blocks;
-        }
-    };
-    constexpr bool kAhead = sizeof(S) == 2;   // request the next block's inputs one block ahead
-    locate(gb);
-    const gefen_b200_step_tensor_t* cur = tp;
-    long long b = gb - t_first;
-    RegBlockInputs<S> in;
-    reg_request<S>(*cur, b, wg, lane, in);
-    int turn = 0;
-    for (;;) {
-        const long long gb_next = gb + stride;
-        const bool has_next = gb_next < L.total_blocks;
-        const gefen_b200_step_tensor_t* nxt = cur;
-        long long b_next = 0;
-        RegBlockInputs<S> ahead;
-        if (has_next) {
-            locate(gb_next);
-            nxt = tp;
-            b_next = gb_next - t_first;
-            if (kAhead) reg_request<S>(*nxt, b_next, wg, lane, ahead);
-        }
-        reg_block_step<S>(*cur, b, L, smem, s, in, W, wg, grp, lane, xchg[turn], xchg_exact);
-        if (!has_next) break;
-        if (kAhead) in = ahead;
-        else reg_request<S>(*nxt, b_next, wg, lane, in);
-        cur = nxt;
-        b = b_next;
-        gb = gb_next;
-        turn ^= 1;
+        if (t.period >= 256) warp_block_step<S, GSRC, true>(t, nb_local, L, s, stage, lane);
+        else warp_block_step<S, GSRC, false>(t, nb_local, L, s, stage, lane);
     }
 }
 
@@ -1147,6 +901,25 @@ __global__ void __launch_bounds__(kThreads) vmean_kernel(void* __restrict__ vmea
     }
 }
 
+// --------------------------------------------------------------------------- multicast sum
+// dst[i] = round(scale * sum over the ranks of src[i]), the sum formed by the switch: the gradient the
+// staged kernel sees when it reads through the multicast mapping, written out for checks.
+template <typename S>
+__global__ void __launch_bounds__(kThreads) multicast_sum_kernel(void* __restrict__ dst, const void* __restrict__ src_mc,
+                                                                 long long chunks, float scale) {
+    const long long stride = static_cast<long long>(gridDim.x) * kThreads;
+    for (long long c = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x; c < chunks; c += stride) {
+        Chunk<S> v;
+        v.load_sum(src_mc, c);
+        float f[8];
+        v.unpack(f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] *= scale;
+        v.pack(f);
+        v.store(dst, c);
+    }
+}
+
 // --------------------------------------------------------------------------- host dispatch
 static int grid_for(long long groups_needed, int groups_per_cta, int ctas_per_sm) {
     long long ctas = (groups_needed + groups_per_cta - 1) / groups_per_cta;
@@ -1175,22 +948,9 @@ static int env_int(const char* name) {
     const int v = e != nullptr ? atoi(e) : 0;
     return v < 0 ? 0 : v;
 }
-// GEFEN_B200_STEP_WARPS=n caps the warps per CTA of the staged kernel, GEFEN_B200_STEP_REG_WARPS=n
-// picks the warps per CTA of the register-resident kernel (16, 20 or 24), GEFEN_B200_STEP_PATH=staged
-// keeps every block on the staged kernel (all three for measurements; read once).
+// GEFEN_B200_STEP_WARPS=n caps the warps per CTA of the staged kernel (for measurements; read once).
 static int warps_override() {
     static const int cached = env_int("GEFEN_B200_STEP_WARPS");
-    return cached;
-}
-static int reg_warps_override() {
-    static const int cached = env_int("GEFEN_B200_STEP_REG_WARPS");
-    return cached;
-}
-static bool reg_path_enabled() {
-    static const bool cached = [] {
-        const char* e = getenv("GEFEN_B200_STEP_PATH");
-        return !(e != nullptr && e[0] == 's');
-    }();
     return cached;
 }
 
@@ -1199,11 +959,11 @@ static bool reg_path_enabled() {
 constexpr unsigned int kDefaultStageSpinLimit = 4000000u;
 static unsigned int g_stage_spin_limit = kDefaultStageSpinLimit;
 
-template <typename S, bool REDUCE>
+template <typename S, int GSRC>
 static int launch_vec_variant(StepLaunch L, const gefen_b200_step_tensor_t& single, long long max_period,
                               cudaStream_t stream) {
     static bool configured[kMaxDevices];
-    auto kernel = step_vec_kernel<S, REDUCE>;
+    auto kernel = step_vec_kernel<S, GSRC>;
     {
         int dev = 0;
         const int rc = current_device(&dev);
@@ -1216,7 +976,7 @@ static int launch_vec_variant(StepLaunch L, const gefen_b200_step_tensor_t& sing
     }
     // a warp stages one long block, or the 32 / lanes short blocks (at most 256 elements together) of a unit
     const long long stage_bytes = (max_period > 256 ? max_period : 256) * 4;
-    int max_warps = vec_max_threads<S, REDUCE>() / 32;
+    int max_warps = vec_max_threads<S, GSRC>() / 32;
     if (warps_override() > 0 && warps_override() < max_warps) max_warps = warps_override();
     int warps = static_cast<int>((kMaxSmem - kStaticSmemSlack - kSmemWs - kSmemRep) / stage_bytes);
     if (warps > max_warps) warps = max_warps;
@@ -1235,45 +995,9 @@ static int launch_vec_variant(StepLaunch L, const gefen_b200_step_tensor_t& sing
 
 template <typename S>
 static int launch_vec(StepLaunch L, const gefen_b200_step_tensor_t& single, long long max_period, cudaStream_t stream) {
-    if (L.n_grad_srcs > 0) return launch_vec_variant<S, true>(L, single, max_period, stream);
-    return launch_vec_variant<S, false>(L, single, max_period, stream);
-}
-
-template <typename S, int MAXW>
-static int launch_reg_variant(StepLaunch L, const gefen_b200_step_tensor_t& single, cudaStream_t stream) {
-    constexpr int smem = kSmemWsPadded + kSmemRepWide;
-    static bool configured[kMaxDevices];
-    auto kernel = step_reg_kernel<S, MAXW>;
-    {
-        int dev = 0;
-        const int rc = current_device(&dev);
-        if (rc != GEFEN_B200_OK) return rc;
-        std::lock_guard<std::mutex> lock(g_config_mutex);
-        if (!configured[dev]) {
-            GEFEN_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            configured[dev] = true;
-        }
-    }
-    const int W = L.warps_per_block;
-    int groups = MAXW / W;
-    if (groups < 1) groups = 1;
-    // few blocks: fewer groups per CTA, so that the blocks spread over the SMs
-    const long long per_sm = (L.total_blocks + sm_count() - 1) / sm_count();
-    if (per_sm < groups) groups = per_sm < 1 ? 1 : static_cast<int>(per_sm);
-    const int grid = grid_for(L.total_blocks, groups, 1);
-    kernel<<<grid, groups * W * 32, smem, stream>>>(L, single);
-    GEFEN_CHECK_CUDA(cudaGetLastError());
-    return GEFEN_B200_OK;
-}
-
-// Warps per CTA of the register-resident kernel (the register budget per thread follows from it).
-template <typename S>
-static int launch_reg(const StepLaunch& L, const gefen_b200_step_tensor_t& single, cudaStream_t stream) {
-    int warps = reg_warps_override();
-    if (warps == 0) warps = sizeof(S) == 2 ? 20 : 16;
-    if (L.warps_per_block > 12 || warps <= 16) return launch_reg_variant<S, 16>(L, single, stream);
-    if (warps >= 24) return launch_reg_variant<S, 24>(L, single, stream);
-    return launch_reg_variant<S, 20>(L, single, stream);
+    if (L.grad_mc_delta != 0) return launch_vec_variant<S, 2>(L, single, max_period, stream);
+    if (L.n_grad_srcs > 0) return launch_vec_variant<S, 1>(L, single, max_period, stream);
+    return launch_vec_variant<S, 0>(L, single, max_period, stream);
 }
 
 template <typename S>
@@ -1303,17 +1027,13 @@ static int launch_generic(bool cta_per_block, const StepLaunch& L, const gefen_b
     return GEFEN_B200_OK;
 }
 
-// Class of a tensor: kRegClassBase + W = register-resident path with W warps per block, 1 = vectorised
-// staged path, 0 = generic warp per block, -1 = generic CTA per block.
-constexpr int kRegClassBase = 100;
+// Class of a tensor: 1 = vectorised staged path, 0 = generic warp per block, -1 = generic CTA per block.
 static int tensor_class(const gefen_b200_step_tensor_t& t, int dtype) {
     const bool vec_dtype = dtype == GEFEN_B200_F32 || dtype == GEFEN_B200_BF16 || dtype == GEFEN_B200_F16;
     const bool period1 = (t.flags & GEFEN_B200_STEP_PERIOD1) != 0;
     const bool packed = (t.flags & GEFEN_B200_STEP_PACKED) != 0;
     if (vec_dtype && !period1 && !packed && t.period % 8 == 0 && t.period <= kFastMaxPeriod && aligned16(t.g) && aligned16(t.p) &&
         (reinterpret_cast<uintptr_t>(t.codes) & 7u) == 0) {
-        if (t.period >= kRegMinPeriod && t.period <= kRegMaxPeriod && reg_path_enabled())
-            return kRegClassBase + reg_warps_per_block(t.period);
         return 1;
     }
     return t.period > 2048 ? -1 : 0;
@@ -1325,13 +1045,6 @@ static long long class_units(const gefen_b200_step_tensor_t& t, int cls) {
 
 static int launch_class(int cls, int dtype, const StepLaunch& L, const gefen_b200_step_tensor_t& single,
                         long long max_period, cudaStream_t stream) {
-    if (cls > kRegClassBase) {
-        StepLaunch R = L;
-        R.warps_per_block = cls - kRegClassBase;
-        if (dtype == GEFEN_B200_BF16) return launch_reg<__nv_bfloat16>(R, single, stream);
-        if (dtype == GEFEN_B200_F16) return launch_reg<__half>(R, single, stream);
-        return launch_reg<float>(R, single, stream);
-    }
     if (cls >= 1) {
         if (dtype == GEFEN_B200_BF16) return launch_vec<__nv_bfloat16>(L, single, max_period, stream);
         if (dtype == GEFEN_B200_F16) return launch_vec<__half>(L, single, max_period, stream);
@@ -1380,7 +1093,8 @@ static int run_single(gefen_b200_step_tensor_t& t, int param_dtype, const float*
     L.n_peers = 0;
     L.n_grad_srcs = 0;
     L.grad_scale = 1.0f;
-    L.warps_per_block = 1;
+    L.grad_mc_delta = 0;
+    L.param_mc_delta = 0;
     L.spin_limit = g_stage_spin_limit;
     return launch_class(cls, param_dtype, L, t, t.period, stream);
 }
@@ -1571,6 +1285,24 @@ int gefen_b200_step_tensor_class(const gefen_b200_step_tensor_t* host_entry, int
     return tensor_class(*host_entry, param_dtype);
 }
 
+int gefen_b200_multicast_sum(void* dst, const void* src_multicast, int dtype, int64_t numel, double scale, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    GEFEN_CHECK_ARG(dst != nullptr && src_multicast != nullptr, "Expected non-null buffers.");
+    GEFEN_CHECK_ARG(dtype == GEFEN_B200_F32 || dtype == GEFEN_B200_F16 || dtype == GEFEN_B200_BF16,
+                    "The multicast sum supports fp32, fp16 and bf16.");
+    GEFEN_CHECK_ARG(numel >= 0 && numel % 8 == 0 && aligned16(dst) && aligned16(src_multicast),
+                    "Expected 16-byte aligned buffers and a multiple of 8 elements.");
+    if (numel == 0) return GEFEN_B200_OK;
+    const long long chunks = numel / 8;
+    const int grid = grid_for(chunks, kThreads, 4);
+    const float sc = static_cast<float>(scale);
+    if (dtype == GEFEN_B200_BF16) multicast_sum_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(dst, src_multicast, chunks, sc);
+    else if (dtype == GEFEN_B200_F16) multicast_sum_kernel<__half><<<grid, kThreads, 0, stream>>>(dst, src_multicast, chunks, sc);
+    else multicast_sum_kernel<float><<<grid, kThreads, 0, stream>>>(dst, src_multicast, chunks, sc);
+    GEFEN_CHECK_CUDA(cudaGetLastError());
+    return GEFEN_B200_OK;
+}
+
 int gefen_b200_step_status(int* host_status, int clear) {
     GEFEN_CHECK_ARG(host_status != nullptr, "Expected a host pointer for the status.");
     int value = 0;
@@ -1598,7 +1330,24 @@ int gefen_b200_multi_tensor_step_peers(gefen_b200_step_tensor_t* host_table, voi
                                        int param_dtype, const void* codebook_ws, const int64_t* peer_deltas,
                                        int n_peers, const int64_t* grad_deltas, int n_grad_srcs, double grad_scale,
                                        void* stream_) {
+    return gefen_b200_multi_tensor_step_multicast(host_table, device_table, n_tensors, param_dtype, codebook_ws, peer_deltas,
+                                                  n_peers, grad_deltas, n_grad_srcs, grad_scale, 0, 0, stream_);
+}
+
+int gefen_b200_multi_tensor_step_multicast(gefen_b200_step_tensor_t* host_table, void* device_table, int n_tensors,
+                                           int param_dtype, const void* codebook_ws, const int64_t* peer_deltas,
+                                           int n_peers, const int64_t* grad_deltas, int n_grad_srcs, double grad_scale,
+                                           int64_t param_multicast_delta, int64_t grad_multicast_delta, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    GEFEN_CHECK_ARG(param_multicast_delta % 16 == 0 && grad_multicast_delta % 16 == 0,
+                    "Multicast offsets must be multiples of 16 bytes.");
+    GEFEN_CHECK_ARG(grad_multicast_delta == 0 || n_grad_srcs > 0,
+                    "Summing gradients through the multicast mapping also needs the per-rank gradient offsets "
+                    "(the kernels for short or odd blocks read the ranks' buffers directly).");
+    GEFEN_CHECK_ARG(param_multicast_delta == 0 || n_peers > 0,
+                    "Storing parameters through the multicast mapping also needs the per-rank parameter offsets.");
+    GEFEN_CHECK_ARG((param_multicast_delta == 0 && grad_multicast_delta == 0) || param_dtype != GEFEN_B200_F64,
+                    "The multicast paths support fp32, fp16 and bf16.");
     GEFEN_CHECK_ARG(n_grad_srcs >= 0 && n_grad_srcs <= GEFEN_B200_MAX_PEERS + 1,
                     "Expected between 0 and %d gradient buffers, got %d.", GEFEN_B200_MAX_PEERS + 1, n_grad_srcs);
     GEFEN_CHECK_ARG(n_grad_srcs == 0 || grad_deltas != nullptr, "Expected offsets for %d gradient buffers.", n_grad_srcs);
@@ -1632,9 +1381,7 @@ int gefen_b200_multi_tensor_step_peers(gefen_b200_step_tensor_t* host_table, voi
                         "Tensor %d: 4-bit codes need an even period and are not defined for period-1 tensors.", i);
         GEFEN_CHECK_ARG(n_grad_srcs == 0 || !(t.flags & GEFEN_B200_STEP_MUON),
                         "Tensor %d: the momentum-only step does not average gradients over ranks.", i);
-        int cls = tensor_class(t, param_dtype);
-        if (cls > kRegClassBase && n_grad_srcs > 0) cls = 1;   // gradient averaging lives on the staged kernel
-        t.reserved_[0] = cls;
+        t.reserved_[0] = tensor_class(t, param_dtype);
     }
     for (int begin = 0; begin < n_tensors;) {
         int end = begin;
@@ -1668,7 +1415,8 @@ int gefen_b200_multi_tensor_step_peers(gefen_b200_step_tensor_t* host_table, voi
             L.n_grad_srcs = n_grad_srcs;
             L.grad_scale = static_cast<float>(grad_scale);
             for (int r = 0; r < n_grad_srcs; ++r) L.grad_delta[r] = grad_deltas[r];
-            L.warps_per_block = 1;
+            L.grad_mc_delta = grad_multicast_delta;
+            L.param_mc_delta = param_multicast_delta;
             L.spin_limit = g_stage_spin_limit;
             const int rc = launch_class(host_table[begin].reserved_[0], param_dtype, L, host_table[begin], max_period, stream);
             if (rc != GEFEN_B200_OK) return rc;

@@ -550,11 +550,14 @@ class Gefen(torch.optim.Optimizer):
                 if (peers is not None and len(peers)) or (grad_srcs is not None and len(grad_srcs)):
                     n_peers = 0 if peers is None else len(peers)
                     n_srcs = 0 if grad_srcs is None else len(grad_srcs)
-                    _lib.check(lib.gefen_b200_multi_tensor_step_peers(
+                    # multicast (NVSwitch) addresses of the same buffers, where the wrapper found them
+                    param_mc = int(getattr(self, "_param_multicast_delta", 0) or 0) if n_peers else 0
+                    grad_mc = int(getattr(self, "_grad_multicast_delta", 0) or 0) if n_srcs else 0
+                    _lib.check(lib.gefen_b200_multi_tensor_step_multicast(
                         rows.ctypes.data, _lib.ptr(table["device_table"]), n, table["tag"], _lib.ptr(ws),
                         peers.ctypes.data if n_peers else None, n_peers,
                         grad_srcs.ctypes.data if n_srcs else None, n_srcs, float(getattr(self, "_grad_src_scale", 1.0)),
-                        _lib.current_stream(device)))
+                        param_mc, grad_mc, _lib.current_stream(device)))
                 else:
                     _lib.check(lib.gefen_b200_multi_tensor_step(
                         rows.ctypes.data, _lib.ptr(table["device_table"]), n, table["tag"], _lib.ptr(ws),

@@ -88,6 +88,21 @@ class GefenMuon(Gefen):
             self._scratch = torch.empty(numel, dtype=dtype, device=device)
         return self._scratch
 
+    def _device_table(self, nbytes: int, device) -> torch.Tensor:
+        """Device copy of the launch table, kept between steps (work on one stream is ordered)."""
+        t = getattr(self, "_table", None)
+        if t is None or t.numel() < nbytes or t.device != device:
+            t = self._table = torch.empty(max(nbytes, 4096), dtype=torch.uint8, device=device)
+        return t
+
+    def check(self) -> None:
+        """As `Gefen.check`, and also raises if a Newton-Schulz GEMM gave up one of its bounded waits."""
+        super().check()
+        from . import newton_schulz
+
+        for device in {p.device for g in self.param_groups for p in g["params"] if p.device.type == "cuda"}:
+            newton_schulz.check_status(device)
+
     def _quantized_momentum(self, chunk, scratch: torch.Tensor):
         """One multi-tensor launch: new 8-bit momentum for every matrix of `chunk`, its dequantised
         value (Nesterov-blended when asked) written into consecutive slices of `scratch`."""
@@ -119,7 +134,7 @@ class GefenMuon(Gefen):
         order = sorted(range(len(chunk)), key=lambda r: classes[r])
         rows = np.ascontiguousarray(rows[order])
         device = chunk[0][4].device
-        table = torch.empty(rows.nbytes, dtype=torch.uint8, device=device)
+        table = self._device_table(rows.nbytes, device)
         ws = _lib.codebook_workspace(self._gefen_codebook)
         with _lib.device_guard(device):
             _lib.check(lib.gefen_b200_multi_tensor_step(rows.ctypes.data, _lib.ptr(table), len(chunk), tag, _lib.ptr(ws),

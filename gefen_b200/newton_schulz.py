@@ -4,14 +4,14 @@ X <- X / max(||X||_F, eps); then `steps` times: A = X X^T, B = b*A + c*A*A, X <-
 bf16 with fp32 accumulation, on the wide orientation (rows <= cols; taller inputs are transposed).
 Each product rounds its result to bf16 once, as the reference's torch.addmm / `@` calls do.
 
-The products run on the library's tcgen05 GEMM (`gefen_b200_ns_gemm_tn`, K-major operands). Keeping
-X and X^T side by side makes every product of the iteration K-major: the third GEMM writes its
-result in both orientations. Shapes the kernel does not take (a dimension that is not a multiple
-of 8) use torch's GEMMs.
+The products run on the library's tcgen05 GEMMs (`gefen_b200_newton_schulz`: K-major and MN-major
+operands, so no transposed copy is ever made). The kernels take dimensions that are multiples of 8
+(16-byte rows); any other matrix is padded with zero rows and columns, which the iteration maps to
+zero rows and columns (they add nothing to X X^T), and the result is cut back. There is no library
+GEMM behind this module.
 """
 from __future__ import annotations
 
-import os
 from typing import Optional, Tuple
 
 import torch
@@ -19,7 +19,6 @@ import torch
 from . import _lib
 
 _STATUS = {}
-USE_TCGEN05 = os.environ.get("GEFEN_B200_NS", "tcgen05") != "torch"
 
 
 _SCRATCH = {}
@@ -101,10 +100,6 @@ def gemm_tt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
     return out
 
 
-def _supported(m: int, n: int) -> bool:
-    return USE_TCGEN05 and m % 8 == 0 and n % 8 == 0
-
-
 def zeropower_via_newtonschulz(grad: torch.Tensor, ns_coefficients: Tuple[float, float, float], ns_steps: int,
                                eps: float) -> torch.Tensor:
     if ns_steps >= 100:
@@ -118,29 +113,27 @@ def zeropower_via_newtonschulz(grad: torch.Tensor, ns_coefficients: Tuple[float,
     a, b, c = ns_coefficients
     x = grad.bfloat16()
     rows, cols = x.shape
-    if not _supported(rows, cols) or ns_steps == 0:
-        transposed = rows > cols
-        if transposed:
-            x = x.T
-        x = x / x.norm().clamp(min=eps)
-        for _ in range(ns_steps):
-            gram = x @ x.T
-            gram_update = torch.addmm(gram, gram, gram, beta=b, alpha=c)
-            x = torch.addmm(x, gram_update, x, beta=a)
-        return x.T if transposed else x
-
+    if rows == 0 or cols == 0:
+        return x
     # bf16 norm and quotient, as the reference's div_ (the Frobenius norm does not care about orientation).
     # Both iterates live in the per-device scratch: the same addresses for every matrix of a shape, which
     # lets the native driver replay the chain of products as one graph.
-    m = min(rows, cols)
-    scratch = _scratch(x.device, 2 * m * m + 2 * rows * cols)
+    prow, pcol = (rows + 7) // 8 * 8, (cols + 7) // 8 * 8
+    m = min(prow, pcol)
+    scratch = _scratch(x.device, 2 * m * m + 2 * prow * pcol)
     gram = scratch[: m * m]
     poly = scratch[m * m: 2 * m * m]
-    nxt = scratch[2 * m * m: 2 * m * m + rows * cols].view(rows, cols)
-    first = scratch[2 * m * m + rows * cols: 2 * m * m + 2 * rows * cols].view(rows, cols)
-    x = torch.div(x, x.norm().clamp(min=eps), out=first)
-    with _lib.device_guard(x.device):
-        _lib.check(_lib.load().gefen_b200_newton_schulz(
-            _lib.ptr(x), _lib.ptr(nxt), _lib.ptr(gram), _lib.ptr(poly), rows, cols, int(ns_steps), float(a), float(b),
-            float(c), _lib.ptr(_status(x.device)), _lib.current_stream(x.device)))
-    return (x if ns_steps % 2 == 0 else nxt).clone()
+    nxt = scratch[2 * m * m: 2 * m * m + prow * pcol].view(prow, pcol)
+    first = scratch[2 * m * m + prow * pcol: 2 * m * m + 2 * prow * pcol].view(prow, pcol)
+    padded = (prow, pcol) != (rows, cols)
+    if padded:
+        first.zero_()
+        nxt.zero_()
+    torch.div(x, x.norm().clamp(min=eps), out=first[:rows, :cols])
+    if ns_steps > 0:
+        with _lib.device_guard(x.device):
+            _lib.check(_lib.load().gefen_b200_newton_schulz(
+                _lib.ptr(first), _lib.ptr(nxt), _lib.ptr(gram), _lib.ptr(poly), prow, pcol, int(ns_steps), float(a), float(b),
+                float(c), _lib.ptr(_status(x.device)), _lib.current_stream(x.device)))
+    result = first if ns_steps % 2 == 0 else nxt
+    return result[:rows, :cols].clone()

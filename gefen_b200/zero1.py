@@ -3,10 +3,15 @@ the optimizer state of one contiguous segment of a flat layout, and a step is
 
     reduce-scatter(gradients)  ->  Gefen step on the owned segment  ->  all-gather(parameters).
 
-On NCCL the parameter buffers of all ranks are mapped into every process (symmetric memory) and the
-step kernels store each updated parameter into all copies themselves, over NVLink, while they
-compute: the all-gather costs no launch and no second pass over the parameters, only a one-element
-all-reduce as the closing barrier. The gradient reduce-scatter is NCCL's.
+On NCCL the parameter and gradient buffers of all ranks are symmetric memory: mapped into every
+process and, where the machine has NVSwitch multicast, bound to a multicast address as well. The step
+kernels then carry both collectives on their own accesses while they compute. With multicast, a
+gradient chunk arrives with one `multimem.ld_reduce` (the switch adds the ranks' copies) and an
+updated parameter chunk leaves with one `multimem.st` (the switch delivers it to every copy): each
+rank pulls 1/N of the gradient bytes and pushes 1/N of the parameter bytes that the unicast
+collectives move, and the two directions of the links are busy at the same time inside one kernel.
+Without multicast the kernels store to every peer copy (plain peer stores) and NCCL reduce-scatters
+the gradients first. Two one-element all-reduces order the ranks around the step.
 
 The reference has no communication code at all (its only distributed awareness is unwrapping
 DTensor shards, gefen.py:692-706); this module is the exchange step the data-parallel use of the
@@ -19,6 +24,7 @@ optimizer needs. Two properties are kept so that N ranks reproduce one rank bit 
 """
 from __future__ import annotations
 
+import ctypes
 import math
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
@@ -210,7 +216,8 @@ class Zero1Gefen:
 
     def __init__(self, named_params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, *, group=None,
                  ops=None, average_gradients: bool = True, fused_all_gather: Optional[bool] = None,
-                 fused_reduce_scatter: Optional[bool] = None):
+                 fused_reduce_scatter: Optional[bool] = None, multicast: Optional[bool] = None, device=None,
+                 dtype=None):
         self.group = group
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -219,35 +226,64 @@ class Zero1Gefen:
         self.named = [(n, p) for n, p in named_params]
         if not self.named:
             raise ValueError("Zero1Gefen needs at least one parameter")
-        p0 = self.named[0][1]
-        self.dtype, self.device = p0.dtype, p0.device
-        for n, p in self.named:
-            if p.dtype != self.dtype or p.device != self.device:
-                raise ValueError("Zero1Gefen expects one dtype and device per instance, got {} for {}".format(p.dtype, n))
-        self.layout = self._make_layout([tuple(p.shape) for _, p in self.named])
+        # (name, shape) entries instead of (name, Parameter): a model too large to exist twice. The flat
+        # buffers are created on `device` with `dtype`, the parameters are made as views of them (see
+        # `self.named` afterwards) and the caller fills them.
+        self._from_shapes = not torch.is_tensor(self.named[0][1])
+        if self._from_shapes:
+            if device is None or dtype is None:
+                raise ValueError("Zero1Gefen built from shapes needs `device` and `dtype`")
+            self.dtype, self.device = dtype, torch.device(device)
+            self.named = [(n, tuple(int(x) for x in shape)) for n, shape in self.named]
+        else:
+            p0 = self.named[0][1]
+            self.dtype, self.device = p0.dtype, p0.device
+            for n, p in self.named:
+                if p.dtype != self.dtype or p.device != self.device:
+                    raise ValueError("Zero1Gefen expects one dtype and device per instance, got {} for {}".format(p.dtype, n))
+        self.layout = self._make_layout([tuple(p) if self._from_shapes else tuple(p.shape) for _, p in self.named])
         self._token = None
-        self.flat_param, param_ptrs = self._allocate_flat(fused_all_gather, "GEFEN_B200_ZERO1_FUSED_AG", "all_gather")
-        # Off unless asked for. With it a rank's step kernel reads its gradients from every peer with
-        # plain loads; NVLink's load latency then bounds the kernel (two B200s, 1.5 G parameters: one
-        # 5.0 ms kernel, against 3.2 ms of NCCL reduce-scatter plus a 2.5 ms kernel), and it gets
-        # worse with more sources per element. Kept for its exactness: fp32 sum in rank order.
-        self.flat_grad, grad_ptrs = self._allocate_flat(fused_reduce_scatter, "GEFEN_B200_ZERO1_FUSED_RS",
-                                                        "reduce_scatter", default="0")
+        import os
+
+        want_mc = multicast if multicast is not None else os.environ.get("GEFEN_B200_ZERO1_MULTICAST", "1") != "0"
+        self.flat_param, param_ptrs, param_mc = self._allocate_flat(fused_all_gather, "GEFEN_B200_ZERO1_FUSED_AG",
+                                                                    "all_gather")
+        # The gradient buffer is symmetric as well unless fused_reduce_scatter=False. Averaging inside the step
+        # kernels is the default when the buffer has a multicast address (one switch-reduced load per chunk).
+        # Over plain peer loads it must be asked for (fused_reduce_scatter=True or GEFEN_B200_ZERO1_FUSED_RS=1):
+        # NVLink's load latency then bounds the kernel, more so with more sources per element; that form is
+        # kept for its exactness (fp32 sum in rank order).
+        self.flat_grad, grad_ptrs, grad_mc = self._allocate_flat(False if fused_reduce_scatter is False else None,
+                                                                 "GEFEN_B200_ZERO1_SYMMETRIC_GRADS", "reduce_scatter")
+        if not want_mc:
+            param_mc = grad_mc = 0
+        peer_rs = fused_reduce_scatter if fused_reduce_scatter is not None else \
+            os.environ.get("GEFEN_B200_ZERO1_FUSED_RS", "0") != "0"
+        mc_rs = os.environ.get("GEFEN_B200_ZERO1_MULTICAST_RS", "1") != "0"
         # peers in ring order starting after this rank, so that concurrent ranks write to different GPUs
         self._peer_deltas = None if param_ptrs is None else np.array(
             [param_ptrs[(self.rank + k) % self.world] - param_ptrs[self.rank] for k in range(1, self.world)], dtype=np.int64)
+        self._param_mc_delta = int(param_mc - param_ptrs[self.rank]) if (param_ptrs is not None and param_mc) else 0
         # gradient buffers in rank order: the same summation order on every rank
-        self._grad_deltas = None if grad_ptrs is None else np.array(
-            [grad_ptrs[r] - grad_ptrs[self.rank] for r in range(self.world)], dtype=np.int64)
+        self._grad_mc_delta = int(grad_mc - grad_ptrs[self.rank]) if (grad_ptrs is not None and grad_mc and mc_rs) else 0
+        use_grad_srcs = grad_ptrs is not None and (self._grad_mc_delta != 0 or peer_rs)
+        self._grad_deltas = np.array([grad_ptrs[r] - grad_ptrs[self.rank] for r in range(self.world)], dtype=np.int64) \
+            if use_grad_srcs else None
         with torch.no_grad():
             for t, (n, p) in enumerate(self.named):
                 off = self.layout.tensor_offset[t]
-                view = self.flat_param[off:off + p.numel()].view(p.shape)
-                view.copy_(p.data)
-                gview = self.flat_grad[off:off + p.numel()].view(p.shape)
-                if p.grad is not None:
-                    gview.copy_(p.grad)
-                p.data = view
+                shape = self.layout.shapes[t]
+                numel = int(math.prod(shape)) if len(shape) else 1
+                view = self.flat_param[off:off + numel].view(shape)
+                gview = self.flat_grad[off:off + numel].view(shape)
+                if self._from_shapes:
+                    p = torch.nn.Parameter(view)
+                    self.named[t] = (n, p)
+                else:
+                    view.copy_(p.data)
+                    if p.grad is not None:
+                        gview.copy_(p.grad)
+                    p.data = view
                 p.grad = gview
         seg = self.layout.segment
         self.my_param = self.flat_param[self.rank * seg:(self.rank + 1) * seg]
@@ -267,6 +303,7 @@ class Zero1Gefen:
             if named_pieces else None
         if self.local is not None and self._peer_deltas is not None:
             self.local._peer_param_deltas = self._peer_deltas
+            self.local._param_multicast_delta = self._param_mc_delta
         self.period_mismatches: List[Tuple[str, Dict[int, int]]] = []
         self._events = None
         self._calibrated = False
@@ -296,8 +333,8 @@ class Zero1Gefen:
         usable = (want and self.world > 1 and self.world - 1 <= 7 and self.device.type == "cuda"
                   and self._backend() == "nccl" and self.dtype != torch.float64)
         if not usable:
-            return torch.zeros(self.layout.total, dtype=self.dtype, device=self.device), None
-        buf, ptrs = None, None
+            return torch.zeros(self.layout.total, dtype=self.dtype, device=self.device), None, 0
+        buf, ptrs, mc = None, None, 0
         try:
             import torch.distributed._symmetric_memory as symm_mem
 
@@ -309,19 +346,24 @@ class Zero1Gefen:
                 raise RuntimeError("symmetric buffer is not at the address the mapping reports")
             if any((x - ptrs[self.rank]) % 16 for x in ptrs):
                 raise RuntimeError("peer buffers are not 16-byte congruent")
+            mc = int(getattr(handle, "multicast_ptr", 0) or 0)   # 0: no NVSwitch multicast on this machine
+            if mc and (mc - ptrs[self.rank]) % 16:
+                mc = 0
             setattr(self, "_symm_handle_" + what, handle)   # keeps the mapping alive
             buf.zero_()
         except Exception as exc:  # mapping is a property of the machine: fall back to the collective
             self.fused_errors[what] = "{}: {}".format(type(exc).__name__, exc)
-            buf, ptrs = None, None
+            buf, ptrs, mc = None, None, 0
         ok = [None] * self.world
-        dist.all_gather_object(ok, ptrs is not None, group=self.group)
-        if not all(ok):
+        dist.all_gather_object(ok, (ptrs is not None, bool(mc)), group=self.group)
+        if not all(o[0] for o in ok):
             self.fused_errors.setdefault(what, "another rank could not map its buffer")
-            return torch.zeros(self.layout.total, dtype=self.dtype, device=self.device), None
+            return torch.zeros(self.layout.total, dtype=self.dtype, device=self.device), None, 0
+        if not all(o[1] for o in ok):
+            mc = 0
         if self._token is None:
             self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
-        return buf, ptrs
+        return buf, ptrs, mc
 
     @property
     def fused_all_gather_error(self):
@@ -331,13 +373,17 @@ class Zero1Gefen:
     def reduce_scatter_mode(self) -> str:
         if self.world == 1:
             return "none"
-        return "peer loads in the step kernels" if self._grad_deltas is not None else "nccl reduce_scatter"
+        if self._grad_deltas is None:
+            return "nccl reduce_scatter"
+        return "multimem.ld_reduce in the step kernels" if self._grad_mc_delta else "peer loads in the step kernels"
 
     @property
     def all_gather_mode(self) -> str:
         if self.world == 1:
             return "none"
-        return "peer stores from the step kernels" if self._peer_deltas is not None else "nccl all_gather"
+        if self._peer_deltas is None:
+            return "nccl all_gather"
+        return "multimem.st from the step kernels" if self._param_mc_delta else "peer stores from the step kernels"
 
     # ------------------------------------------------------------------ collectives
     def _backend(self) -> str:
@@ -351,11 +397,12 @@ class Zero1Gefen:
     def _reduce_scatter(self) -> None:
         if self.world == 1:
             return
-        fused = self._grad_deltas is not None and self._calibrated
+        fused = self._grad_deltas is not None and self._calibrated and not getattr(self, "_materialize_gradients", False)
         if self.local is not None:
             # the calibration step needs the averaged gradients in memory (periods, histogram), so it
             # uses the collective; afterwards the step kernels average while they read
             self.local._grad_src_deltas = self._grad_deltas if fused else None
+            self.local._grad_multicast_delta = self._grad_mc_delta if fused else 0
             self.local._grad_src_scale = (1.0 / self.world) if self.average else 1.0
         if fused:
             self._rank_barrier()   # every rank's gradients are final, nobody still reads old parameters
@@ -473,6 +520,137 @@ class Zero1Gefen:
 
     def zero_grad(self):
         self.flat_grad.zero_()
+
+    # ------------------------------------------------------------------ N ranks against one process
+    def verify_against_single_process(self, steps: int = 2, max_elements: int = 48 << 20) -> Dict[str, object]:
+        """Collective; call it between steps of a calibrated optimizer. Checks the invariant of the sharding:
+        given the same reduced gradients, the state and parameters of the pieces a rank owns are bit for bit
+        what a plain single-process `Gefen` computes. Every rank takes a few of its pieces (up to
+        `max_elements` elements), clones their state and parameters into a single-process optimizer, and for
+        `steps` steps both sides consume the gradients that NCCL's reduce-scatter left in memory: the sharded
+        side through its production step kernels (parameters leaving through multimem.st or peer stores), the
+        single-process side through `Gefen.step`. Codes, magnitudes, second moments and parameters must be
+        identical. Where the gradients are normally summed by the switch inside the kernel, one more step
+        compares that path with a single-process step fed the same switch-summed values written to memory
+        (`gefen_b200_multicast_sum`). Finally all ranks must hold the same parameter buffer. Advances the
+        optimizer by steps (+1) real steps. Returns the verdict (identical on every rank)."""
+        from . import _lib
+        from .gefen import Gefen
+
+        if not self._calibrated:
+            raise RuntimeError("verify_against_single_process needs a calibrated optimizer: run one step first")
+        chosen, total = [], 0
+        if self.local is not None:
+            for pc, prm in zip(self.pieces, self.piece_params):
+                if chosen and total + pc.numel > max_elements:
+                    continue
+                chosen.append((pc, prm))
+                total += pc.numel
+                if total >= max_elements:
+                    break
+        single, mine = None, []
+        if chosen:
+            named = []
+            for pc, prm in chosen:
+                clone = torch.nn.Parameter(prm.detach().clone())
+                clone.grad = torch.zeros_like(clone)
+                mine.append(clone)
+                named.append(("{}#{}".format(self.named[pc.tensor][0], pc.row0), clone))
+            g0 = self.local.param_groups[0]
+            single = Gefen(named, lr=g0["lr"], betas=(g0["beta1"], g0["beta2"]), eps=g0["eps"],
+                           weight_decay=g0["weight_decay"])
+            for (pc, prm), clone in zip(chosen, mine):
+                single.state[clone].update({k: (v.detach().clone() if torch.is_tensor(v) else v)
+                                            for k, v in self.local.state[prm].items()})
+            single._gefen_codebook = self.local._gefen_codebook.clone()
+            single._gefen_global_step = self.local._gefen_global_step
+
+        def identical() -> bool:
+            ok = True
+            for (pc, prm), clone in zip(chosen, mine):
+                a, b = self.local.state[prm], single.state[clone]
+                ok = ok and torch.equal(prm.detach(), clone.detach())
+                for key in ("m_codebook", "m_magnitude", "vmean"):
+                    ok = ok and torch.equal(a[key], b[key])
+            return ok
+
+        verdict = {"tensors": len(chosen), "elements": total, "steps": steps, "bit_identical": True}
+        self._materialize_gradients = True
+        try:
+            for _ in range(steps):
+                self._reduce_scatter()                        # NCCL: the averaged gradients are in memory
+                for (pc, prm), clone in zip(chosen, mine):
+                    clone.grad.copy_(prm.grad)
+                if self.local is not None:
+                    self.local.step()                         # production kernels, production all-gather
+                self._all_gather()
+                if single is not None:
+                    single.step()
+                    verdict["bit_identical"] = verdict["bit_identical"] and identical()
+        finally:
+            self._materialize_gradients = False
+        if self._grad_mc_delta and self._grad_deltas is not None:
+            # the production gradient path: summed by the switch inside the kernel
+            lib = _lib.load()
+            classes_ok = []
+            if single is not None:
+                scale = (1.0 / self.world) if self.average else 1.0
+                for (pc, prm), clone in zip(chosen, mine):
+                    src = prm.grad.data_ptr() + self._grad_mc_delta
+                    usable = pc.numel % 8 == 0 and prm.grad.data_ptr() % 16 == 0
+                    classes_ok.append(usable)
+                    if usable:
+                        with _lib.device_guard(self.device):
+                            _lib.check(lib.gefen_b200_multicast_sum(_lib.ptr(clone.grad), ctypes.c_void_p(src),
+                                                                    _lib.dtype_tag(self.dtype), pc.numel, scale,
+                                                                    _lib.current_stream(self.device)))
+            self.step()
+            if single is not None:
+                # pieces that the generic kernels handle take the rank-order sum of the peers' copies: leave
+                # them out of this comparison (they were covered above)
+                keep = [i for i, ok in enumerate(classes_ok) if ok and self._piece_is_staged(chosen[i][1])]
+                single.step()
+                same = True
+                for i in keep:
+                    (pc, prm), clone = chosen[i], mine[i]
+                    a, b = self.local.state[prm], single.state[clone]
+                    same = same and torch.equal(prm.detach(), clone.detach()) and torch.equal(a["m_codebook"], b["m_codebook"]) \
+                        and torch.equal(a["m_magnitude"], b["m_magnitude"]) and torch.equal(a["vmean"], b["vmean"])
+                verdict["in_kernel_reduce_bit_identical"] = same
+                verdict["in_kernel_reduce_tensors"] = len(keep)
+        # every rank ends with the same parameters
+        check = self.flat_param.view(torch.int16).to(torch.int64).sum().reshape(1) if self.flat_param.element_size() == 2 \
+            else self.flat_param.view(torch.int32).to(torch.int64).sum().reshape(1)
+        lo, hi = check.clone(), check.clone()
+        if self.world > 1:
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=self.group)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=self.group)
+        verdict["params_identical_across_ranks"] = bool(int(lo) == int(hi))
+        flags = torch.tensor([1.0 if verdict["bit_identical"] else 0.0,
+                              1.0 if verdict.get("in_kernel_reduce_bit_identical", True) else 0.0,
+                              float(verdict["tensors"]), float(verdict["elements"])], device=self.device, dtype=torch.float64)
+        worst = flags[:2].clone()
+        sums = flags[2:].clone()
+        if self.world > 1:
+            dist.all_reduce(worst, op=dist.ReduceOp.MIN, group=self.group)
+            dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=self.group)
+        verdict["bit_identical"] = bool(worst[0] > 0)
+        if self._grad_mc_delta:
+            verdict["in_kernel_reduce_bit_identical"] = bool(worst[1] > 0)
+        verdict["tensors"], verdict["elements"] = int(sums[0]), int(sums[1])
+        return verdict
+
+    def _piece_is_staged(self, prm) -> bool:
+        """True if the local optimizer steps this piece with the staged (vectorised) kernel."""
+        plan = getattr(self.local, "_plan", None)
+        if plan is None:
+            return False
+        params = [p for g in self.local.param_groups for p in g["params"] if p.grad is not None]
+        for table in plan.tables or []:
+            for entry, cls in zip(table["entries"], table["classes"]):
+                if entry < len(params) and params[entry] is prm:
+                    return cls == 1
+        return False
 
     def state_dict(self):
         """This rank's shard of the optimizer state plus the (identical everywhere) codebook."""

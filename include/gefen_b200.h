@@ -164,10 +164,34 @@ int gefen_b200_multi_tensor_step_peers(gefen_b200_step_tensor_t* host_table, voi
                                        const int64_t* peer_deltas, int n_peers,
                                        const int64_t* grad_deltas, int n_grad_srcs, double grad_scale,
                                        void* stream);
+/* The same launch when the ranks' buffers are also bound to an NVLink multicast object (NVSwitch), as
+ * symmetric-memory allocators provide it. *_multicast_delta = (multicast address of the buffer) -
+ * (this GPU's address of it) in bytes, multiples of 16, 0 = not used:
+ *  - param_multicast_delta: the staged kernel writes every updated parameter chunk with ONE multimem.st,
+ *    which the switch delivers to every rank's copy (this GPU's included), instead of a local store plus
+ *    n_peers peer stores: 1/N of the egress of the unicast all-gather;
+ *  - grad_multicast_delta: the staged kernel reads every gradient chunk with ONE multimem.ld_reduce (the
+ *    switch adds the ranks' copies, fp32 accumulation, one rounding to the gradient dtype), scales by
+ *    grad_scale and rounds, instead of n_grad_srcs peer loads: 1/N of the ingress of the unicast
+ *    reduce-scatter. The order of the switch's additions is not the rank order of the peer-load path.
+ * The kernels for short, odd or unaligned blocks keep using the per-rank offsets, which must therefore be
+ * given as well. Ordering between ranks is the caller's, as for gefen_b200_multi_tensor_step_peers. No
+ * counterpart in the reference. */
+int gefen_b200_multi_tensor_step_multicast(gefen_b200_step_tensor_t* host_table, void* device_table,
+                                           int n_tensors, int param_dtype, const void* codebook_ws,
+                                           const int64_t* peer_deltas, int n_peers,
+                                           const int64_t* grad_deltas, int n_grad_srcs, double grad_scale,
+                                           int64_t param_multicast_delta, int64_t grad_multicast_delta,
+                                           void* stream);
+/* dst[i] = round(scale * sum over ranks of src[i]) with the sum formed by the switch (one
+ * multimem.ld_reduce per 16 bytes): what the staged kernel sees of a gradient range when it reads through
+ * grad_multicast_delta, written to local memory. numel a multiple of 8, both pointers 16-byte aligned;
+ * fp32, fp16 or bf16. For checks of the fused path; no counterpart in the reference. */
+int gefen_b200_multicast_sum(void* dst, const void* src_multicast, int dtype, int64_t numel, double scale,
+                             void* stream);
 /* sizeof(gefen_b200_step_tensor_t) as compiled, for binding-side layout checks. */
 int gefen_b200_step_tensor_size(void);
-/* Kernel class the library would use for one table entry: 100 + W = register-resident path with W
- * warps per block (periods of 512 to 8192 elements), 1 = vectorised staged path,
+/* Kernel class the library would use for one table entry: 1 = vectorised staged path,
  * 0 = generic warp-per-block, -1 = generic CTA-per-block. Rows of equal
  * class that are adjacent in the table share one launch. */
 int gefen_b200_step_tensor_class(const gefen_b200_step_tensor_t* host_entry, int param_dtype);

@@ -17,7 +17,9 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
 NAME = "gefen_cuda_ext_ref"
-REFERENCE_KERNELS = Path(os.environ.get("GEFEN_REFERENCE_ROOT", "/root/reference")) / "kernels"
+# where the reference checkout lies: the environment variable GEFEN_REFERENCE_ROOT (no default path)
+_ROOT = os.environ.get("GEFEN_REFERENCE_ROOT")
+REFERENCE_KERNELS = Path(_ROOT) / "kernels" if _ROOT else None
 SOURCES = [
     "gefen_cuda_binding.cpp",
     "automatic_gefen_fused_kernel.cu",
@@ -32,19 +34,22 @@ def built_module_path() -> Path:
     return OUT / (NAME + ".so")
 
 
-def build(force: bool = False) -> Path:
+def build(force: bool = False, reference_root=None) -> Path:
+    """reference_root: the reference checkout (default: the environment variable GEFEN_REFERENCE_ROOT)."""
     target = built_module_path()
     if target.exists() and not force:
         return target
-    if not REFERENCE_KERNELS.is_dir():
-        raise FileNotFoundError("reference sources not found at {}".format(REFERENCE_KERNELS))
+    kernels = Path(reference_root) / "kernels" if reference_root is not None else REFERENCE_KERNELS
+    if kernels is None or not kernels.is_dir():
+        raise FileNotFoundError("reference sources not found: pass reference_root or set GEFEN_REFERENCE_ROOT to the "
+                                "reference checkout (got {})".format(kernels))
     from torch.utils.cpp_extension import load
 
     OUT.mkdir(exist_ok=True)
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
     load(
         name=NAME,
-        sources=[str(REFERENCE_KERNELS / s) for s in SOURCES],
+        sources=[str(kernels / s) for s in SOURCES],
         extra_cflags=["-O3"],
         extra_cuda_cflags=["-O3"],
         build_directory=str(OUT),
@@ -69,4 +74,5 @@ def load_module():
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv))
+    roots = [a for a in sys.argv[1:] if not a.startswith("--")]
+    print(build(force="--force" in sys.argv, reference_root=roots[0] if roots else None))

@@ -307,6 +307,45 @@ double oracle_adjacent_log_score(const void* values, int dt, int64_t numel, int6
     return total / (double)(nb - 1);
 }
 
+/* The same score for several candidate periods of one tensor, as the reference's period search asks
+ * for them one after the other (partitioning.py:259-268). The logarithm of an element does not depend
+ * on the period, so it is taken once into a scratch array; every block sum then adds the same values
+ * in the same left-to-right order as oracle_adjacent_log_score, which makes the scores bit-identical
+ * to calling that function per period (a CPU test holds the two against each other). Returns 0, or
+ * -1 when the scratch array cannot be allocated. */
+int oracle_adjacent_log_scores_many(const void* values, int dt, int64_t numel, const int64_t* periods, int n_periods,
+                                    int squared, double eps, double* scores, double* invalid) {
+    double* logs = (double*)malloc(sizeof(double) * (size_t)(numel > 0 ? numel : 1));
+    if (logs == NULL) return -1;
+    double bad = 0.0;
+#pragma omp parallel for schedule(static) reduction(+ : bad)
+    for (int64_t i = 0; i < numel; ++i) {
+        const double raw = (double)load_as_float(values, i, dt);
+        const double x = (squared ? raw : raw * raw) + eps;
+        if (x <= 0.0) { bad += 1.0; logs[i] = 0.0; } else logs[i] = log(x);
+    }
+    for (int k = 0; k < n_periods; ++k) {
+        const int64_t period = periods[k];
+        const int64_t nb = numel / period;
+        double* means = (double*)malloc(sizeof(double) * (size_t)(nb > 0 ? nb : 1));
+        if (means == NULL) { free(logs); return -1; }
+#pragma omp parallel for schedule(static)
+        for (int64_t b = 0; b < nb; ++b) {
+            double s = 0.0;
+            const double* src = logs + b * period;
+            for (int64_t i = 0; i < period; ++i) s += src[i];
+            means[b] = s / (double)period;
+        }
+        double total = 0.0;
+        for (int64_t b = 0; b + 1 < nb; ++b) total += fabs(means[b + 1] - means[b]);
+        free(means);
+        scores[k] = total / (double)(nb - 1);
+    }
+    free(logs);
+    *invalid = bad;
+    return 0;
+}
+
 /* reference: average_within_block_variance_kernel / ..._coefficient_of_variation_kernel,
  * period_variance_kernel.cu:13-106 (fp32 sums per block). stats: [sum_var] or [sum_cov, n_pos, n_neg]. */
 void oracle_block_moments(const void* values, int dt, int64_t numel, int64_t period, int squared, int cov,

@@ -38,6 +38,7 @@ def lib():
         _lib = ctypes.CDLL(str(_LIB_PATH))
         _lib.oracle_adjacent_log_score.restype = ctypes.c_double
         _lib.oracle_exact_dp.restype = ctypes.c_int
+        _lib.oracle_adjacent_log_scores_many.restype = ctypes.c_int
         _lib.oracle_nearest_index.restype = ctypes.c_int
         _lib.oracle_get_contraction.restype = ctypes.c_int
     return _lib
@@ -163,6 +164,22 @@ def average_adjacent_log_block_mean_difference(values, period, input_is_squared,
     return score
 
 
+def adjacent_log_scores(values, periods, input_is_squared, epsilon):
+    """Scores of several candidate periods of one tensor: the logarithms are taken once, the sums are
+    added in the order of `average_adjacent_log_block_mean_difference` (bit-identical scores)."""
+    arr = (ctypes.c_int64 * len(periods))(*[int(p) for p in periods])
+    out = (ctypes.c_double * len(periods))()
+    invalid = ctypes.c_double(0.0)
+    rc = lib().oracle_adjacent_log_scores_many(_ptr(values), _DT[values.dtype], _i64(values.numel()), arr,
+                                               ctypes.c_int(len(periods)), ctypes.c_int(1 if input_is_squared else 0),
+                                               _d(epsilon), out, ctypes.byref(invalid))
+    if rc != 0:
+        raise MemoryError("oracle: no memory for the logarithm scratch of {} elements".format(values.numel()))
+    if invalid.value > 0:
+        raise RuntimeError("Expected values plus epsilon to be positive before log transform.")
+    return [float(x) for x in out]
+
+
 def block_moments(values, period, input_is_squared, cov):
     stats = torch.zeros(3, dtype=torch.float64)
     lib().oracle_block_moments(_ptr(values), _DT[values.dtype], _i64(values.numel()), _i64(period),
@@ -247,7 +264,7 @@ def find_period(grad: torch.Tensor, *, cuda_kernel_semantics: bool = True, max_p
         values, squared = flat.contiguous(), False
     else:
         values, squared = flat.float().square().contiguous(), True
-    scores = [(p, average_adjacent_log_block_mean_difference(values, p, squared, epsilon)) for p in cands]
+    scores = list(zip(cands, adjacent_log_scores(values, cands, squared, epsilon)))
     return choose_period(scores, n)
 
 

@@ -79,3 +79,19 @@ def test_contraction_modes_differ_only_in_rounding(oracle):
     oracle.set_contraction(1)
     assert float((outs[0][1] == outs[1][1]).float().mean()) > 0.999
     assert rel_l2(outs[0][0], outs[1][0]) < 1e-6
+
+
+def test_one_pass_period_scores_equal_the_per_period_function(oracle):
+    """The oracle scores all candidate periods of a tensor from one array of logarithms; the sums are
+    added in the same order as by the per-period restatement of the reference kernel, so the scores
+    must be bit-identical (and the decisions with them)."""
+    import torch
+
+    from tests.util import make_grad
+
+    for shape, dtype in [((96, 768), torch.float32), ((64, 2304), torch.bfloat16), ((1000,), torch.float32), ((37, 12), torch.bfloat16)]:
+        g = make_grad(shape, 4, 2, 0, dtype).reshape(-1).contiguous()
+        cands = oracle.candidate_periods(g.numel())
+        many = oracle.adjacent_log_scores(g, cands, False, 1e-12)
+        single = [oracle.average_adjacent_log_block_mean_difference(g, p, False, 1e-12) for p in cands]
+        assert many == single

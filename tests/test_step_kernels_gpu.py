@@ -14,8 +14,7 @@ DTYPES = [torch.float32, torch.bfloat16, torch.float16]
 # warp path (odd / tiny periods) and the generic CTA path (period > 2048)
 SHAPES = [(64, 512), (33, 768), (20, 1152), (16, 2048), (9, 1120), (7, 1664), (5, 8), (40, 24), (11, 12),
           (301, 1), (13, 37), (6, 4096), (3, 3000), (2, 10007),
-          # register-resident path: 1 to 16 warps per block, full and ragged last warps, more blocks than
-          # one wave of groups (the prefetch of the next block crosses the end of the tensor)
+          # long blocks and more blocks than one wave of warps
           (700, 512), (333, 2048), (5, 5000), (4, 6144), (3, 8192), (2, 7688), (50, 520), (9, 1536),
           # blocks shorter than 256 elements share a warp (32, 16, 8, 4, 2 blocks per pass), ragged last pass
           (37, 128), (101, 64), (1001, 16), (67, 8), (3, 256), (50, 40), (21, 104), (1, 8)]
@@ -172,7 +171,7 @@ def test_vmean_update(oracle, cuda_device, dtype, nb, period):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("period", [128, 512, 2048, 3000])   # staged path; one, four and six warps per block
+@pytest.mark.parametrize("period", [128, 512, 2048, 3000])   # several blocks per warp, one block per warp, ragged
 def test_nonfinite_gradients_follow_the_reference(oracle, cuda_device, dtype, period):
     from gefen_b200.kernels.automatic_gefen_fused import automatic_gefen_fused_update_from_vmean_cuda
 

@@ -20,7 +20,7 @@ def zero_polls():
     _lib.check(lib.gefen_b200_debug_set_stage_spin_limit(-1))
 
 
-@pytest.mark.parametrize("nb,period", [(64, 2048), (40, 128), (30, 24)])   # register-resident, staged, generic kernel
+@pytest.mark.parametrize("nb,period", [(64, 2048), (40, 128), (30, 24)])   # staged kernel (long and short blocks), generic kernel
 def test_timed_out_staging_is_reported_and_nothing_is_half_done(cuda_device, zero_polls, nb, period):
     from gefen_b200 import _lib
     from gefen_b200.kernels.automatic_gefen_fused import automatic_gefen_fused_update_from_vmean_cuda

@@ -1,7 +1,9 @@
 """ZeRO-1 on two GPUs of one machine. The step with the all-gather fused into the kernels (peer
 stores into the other rank's parameter buffer) must leave every rank with exactly the parameters
 that the NCCL all-gather leaves; with the reduce-scatter fused in as well (peer loads of the other
-rank's gradients) it must equal a run that is fed the rank-order fp32 mean of the gradients.
+rank's gradients) it must equal a run that is fed the rank-order fp32 mean of the gradients; and the
+default mode, both collectives on the NVSwitch multicast mapping of the buffers (multimem.ld_reduce /
+multimem.st), must equal that run too (two ranks: a sum of two has one order).
 Skipped with fewer than two GPUs."""
 import os
 import socket
@@ -44,13 +46,17 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
     results = {}
     # own gradients + NCCL / own gradients + fused all-gather / pre-averaged gradients + fused all-gather /
     # own gradients + both collectives fused
-    for name, fused_ag, fused_rs, pre_averaged in (("nccl", False, False, False), ("fused_ag", True, False, False),
-                                                   ("averaged_inputs", True, False, True), ("fused_both", True, True, False)):
+    # ... / both collectives on the switch's multicast (where the machine has it; otherwise the defaults)
+    for name, fused_ag, fused_rs, pre_averaged, mc in (("nccl", False, False, False, False), ("fused_ag", True, False, False, False),
+                                                       ("averaged_inputs", True, False, True, False),
+                                                       ("fused_both", True, True, False, False),
+                                                       ("multicast", None, None, False, True)):
         params = [torch.nn.Parameter(make_param(s, 5, i, torch.bfloat16).to(dev)) for i, s in enumerate(shapes)]
         named = [("p{}".format(i), p) for i, p in enumerate(params)]
         for i, (p, s) in enumerate(zip(params, shapes)):
             p.grad = torch.zeros(s, dtype=torch.bfloat16, device=dev)
-        opt = Zero1Gefen(named, lr=1e-3, weight_decay=0.1, fused_all_gather=fused_ag, fused_reduce_scatter=fused_rs)
+        opt = Zero1Gefen(named, lr=1e-3, weight_decay=0.1, fused_all_gather=fused_ag, fused_reduce_scatter=fused_rs,
+                         multicast=mc)
         for step in range(4):
             for i, (p, s) in enumerate(zip(params, shapes)):
                 g = averaged(i, s, step) if pre_averaged else grad_of(rank, i, s, step)
@@ -83,7 +89,14 @@ def test_fused_collectives_equal_nccl_collectives(tmp_path):
         assert torch.equal(res["fused_both"][3], res["averaged_inputs"][3])
         # and it is close to NCCL's own bf16 average
         assert (res["fused_both"][3].float() - res["nccl"][3].float()).abs().max() < 1e-2
-    for name in ("nccl", "fused_ag", "fused_both"):
+        # the defaults: multimem.st / multimem.ld_reduce where the switch offers multicast. With two ranks the
+        # switch's sum of two values has no order to differ in: identical to the rank-order mean
+        if res["multicast"][1].startswith("multimem"):
+            assert res["multicast"][0] == "multimem.st from the step kernels"
+            assert torch.equal(res["multicast"][3], res["averaged_inputs"][3])
+        assert (res["multicast"][3].float() - res["nccl"][3].float()).abs().max() < 1e-2
+    print("collectives with the defaults:", ranks[0]["multicast"][:3])
+    for name in ("nccl", "fused_ag", "fused_both", "multicast"):
         assert torch.equal(ranks[0][name][3], ranks[1][name][3]), name
     assert float(ranks[0]["fused_both"][3].float().abs().sum()) > 0
 
