@@ -506,6 +506,7 @@ def run_muon_sharded_arm(args, cfg, rank, world, local_rank):
     torch.cuda.synchronize()
     clocks = sampler.stop()
     ns.check_status(device)
+    n_vs_1 = opt.verify_against_single_process(steps=2, max_elements=40 << 20)
     if rank != 0:
         return
     elems = sum(workloads.numel(s) for _, s in shapes)
@@ -517,7 +518,7 @@ def run_muon_sharded_arm(args, cfg, rank, world, local_rank):
         "config": {"workload": args.workload, "optimizer": "GefenMuon(momentum=0.95, ns_steps=5)", "lr": cfg["lr"],
                    "weight_decay": cfg["wd"], "matrices": len(shapes), "elements": elems,
                    "parallelism": "zero1-dp{} (whole matrices per rank)".format(world)},
-        "calibration_first_step_ms": calibration_ms, "clocks": clocks, "breakdown_ms": breakdown,
+        "calibration_first_step_ms": calibration_ms, "clocks": clocks, "breakdown_ms": breakdown, "n_vs_1": n_vs_1,
         "gpu_launches": args.steps * (owned * 15 + 8),
     }))
 
@@ -561,9 +562,8 @@ def measure_muon(cfg, steps: int, warmup: int):
     total_flops = sum(ns_flops(s) for _, s in shapes)
     coeffs = (3.4445, -4.7750, 2.0315)
 
-    def ns_ours():
-        for g in grads:
-            ns.zeropower_via_newtonschulz(g, coeffs, 5, 1e-7)
+    def ns_ours():   # the optimizer's own path: the chains of two matrices side by side
+        ns.orthogonalize_all([(g, coeffs, 5, 1e-7) for g in grads], lambda i, ortho: None)
 
     def ns_torch():
         for g in grads:

@@ -45,11 +45,60 @@ __device__ __forceinline__ float block_absmax(const S* g, long long period, int 
     return m;
 }
 
+// ------------------------------------------------------------------------------- vector access
+// Eight consecutive elements (16 bytes of a 2-byte type, 32 bytes of fp32) as floats; the pointer is
+// 16-byte aligned. Calibration reads every block twice: the second look hits L1.
+template <typename S> __device__ __forceinline__ void load8(const S* p, float (&f)[8]);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float (&f)[8]) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&f)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+}
+template <> __device__ __forceinline__ void load8<__half>(const __half* p, float (&f)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        f[2 * i] = v.x;
+        f[2 * i + 1] = v.y;
+    }
+}
+template <> __device__ __forceinline__ void load8<double>(const double* p, float (&f)[8]) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = static_cast<float>(p[i]);
+}
+
+// x = v / absmax as the reference divides (IEEE), through the block's reciprocal where that is exact.
+struct BlockDivider {
+    float absmax, rinv;
+    bool fast, nonzero;
+    __device__ __forceinline__ explicit BlockDivider(float a) : absmax(a) {
+        nonzero = a > 0.0f;
+        fast = div_range_ok(a);
+        rinv = fast ? 1.0f / a : 0.0f;
+    }
+    __device__ __forceinline__ float operator()(float v) const {
+        if (fast) return div_by_block_constant(v, absmax, rinv);
+        return nonzero ? v / absmax : 0.0f;
+    }
+};
+
 // ------------------------------------------------------------------------------- histogram
 // bin = clamp(floor((g/absmax + 1) * bins/2), 0, bins-1); counts are integers and therefore
-// independent of the order of accumulation. Increments into the CTA's shared histogram are
-// aggregated across the lanes of a warp that hit the same bin (one atomic per distinct bin).
-template <typename S, int GROUP>
+// independent of the order of accumulation. One warp per block (VEC: 128-bit loads, eight elements
+// per lane and access) or one CTA per very long block. Every element is one shared-memory atomic
+// on the CTA's histogram: the values of a block are bell-shaped over a few hundred bins, so the
+// lanes of a warp rarely meet in one bin, and the hardware serialises those that do.
+template <typename S, int GROUP, bool VEC>
 __global__ void __launch_bounds__(kThreads) histogram_kernel(const S* __restrict__ g, long long period,
                                                              long long num_blocks, int bins,
                                                              unsigned long long* __restrict__ counts) {
@@ -64,27 +113,45 @@ __global__ void __launch_bounds__(kThreads) histogram_kernel(const S* __restrict
                                          : static_cast<long long>(blockIdx.x);
     const long long stride = GROUP == 32 ? static_cast<long long>(gridDim.x) * kWarps : static_cast<long long>(gridDim.x);
     const float scale = 0.5f * static_cast<float>(bins);
+    const int last_bin = bins - 1;
     unsigned long long since_flush = 0;
 
     for (long long b = group0; b < num_blocks; b += stride) {
         const S* gb = g + b * period;
-        const float absmax = block_absmax<S, GROUP>(gb, period, tig, red);
-        const long long rounds = (period + GROUP - 1) / GROUP;
-        for (long long r = 0; r < rounds; ++r) {
-            const long long i = r * GROUP + tig;
-            const bool active = i < period;
-            int bin = -1;
-            if (active) {
+        if (VEC) {   // GROUP == 32, period a multiple of 8, 16-byte aligned blocks
+            const int nchunks = static_cast<int>(period >> 3);
+            float m = 0.0f;
+            for (int c = lane; c < nchunks; c += 32) {
+                float f[8];
+                load8<S>(gb + 8 * c, f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(f[i]));
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            const BlockDivider divide(m);
+            const unsigned int top = static_cast<unsigned int>(last_bin);
+            for (int c = lane; c < nchunks; c += 32) {
+                float f[8];
+                load8<S>(gb + 8 * c, f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    // |x| <= 1 (or x is NaN), so (x + 1) * scale >= 0: the floor is a truncation, NaN maps to
+                    // bin 0 and only the upper clamp can act
+                    const float x = divide(f[i]);
+                    const unsigned int bin = min(__float2uint_rz((x + 1.0f) * scale), top);
+                    atomicAdd(&hist[bin], 1u);
+                }
+            }
+        } else {
+            const float absmax = block_absmax<S, GROUP>(gb, period, tig, red);
+            for (long long i = tig; i < period; i += GROUP) {
                 const float v = ScalarIO<S>::load(gb + i);
                 float x = 0.0f;
                 if (absmax > 0.0f) x = v / absmax;
-                bin = static_cast<int>(floorf((x + 1.0f) * scale));
-                bin = bin < 0 ? 0 : (bin >= bins ? bins - 1 : bin);
-            }
-            const unsigned int amask = __ballot_sync(0xffffffffu, active);
-            if (active) {
-                const unsigned int peers = __match_any_sync(amask, bin);
-                if (lane == (__ffs(peers) - 1)) atomicAdd(&hist[bin], static_cast<unsigned int>(__popc(peers)));
+                int bin = static_cast<int>(floorf((x + 1.0f) * scale));
+                bin = bin < 0 ? 0 : (bin > last_bin ? last_bin : bin);
+                atomicAdd(&hist[bin], 1u);
             }
         }
         since_flush += static_cast<unsigned long long>(period);
@@ -246,24 +313,52 @@ __global__ void __launch_bounds__(kThreads) block_moment_kernel(const S* __restr
 }
 
 // ------------------------------------------------------------------------------- Lloyd-Max
+// Both kernels assign every normalised value to its codebook entry with the rule of the step kernels
+// (nearest entry, left on ties; reference: lloyd_max_fused_kernel.cu:16-48), through the codebook
+// workspace staged in shared memory: one table read and one compare per value, the binary search
+// over the thresholds only for the few undecidable cells.
+struct LloydTables {
+    const float* cb;
+    const float* thr;
+    const unsigned char* lut;
+    int k;
+    __device__ __forceinline__ int entry(float x) const {
+        // the table covers [-1, 1]; values outside it (non-finite gradients) take the exact rule
+        if (!(fabsf(x) <= 1.0f)) return entry_exact(x, thr, cb, k);
+        bool slow;
+        const int e = lut_query(x, lut, &slow);
+        return slow ? entry_exact(x, thr, cb, k) : e;
+    }
+};
+
+__device__ __forceinline__ LloydTables stage_lloyd_tables(const unsigned char* ws, unsigned char* smem) {
+    const uint4* src = reinterpret_cast<const uint4*>(ws);
+    uint4* dst = reinterpret_cast<uint4*>(smem);
+    for (int i = threadIdx.x; i < GEFEN_B200_CODEBOOK_WS_BYTES / 16; i += blockDim.x) dst[i] = src[i];
+    __syncthreads();
+    LloydTables t;
+    t.cb = reinterpret_cast<const float*>(smem + kWsCodebookOff);
+    t.thr = reinterpret_cast<const float*>(smem + kWsThresholdOff);
+    t.lut = smem + kWsLutOff;
+    t.k = reinterpret_cast<const int*>(smem + kWsMetaOff)[0];
+    return t;
+}
+
 // E-step: per codebook entry, the sum of the normalised values assigned to it and their count
 // (reference: lloyd_max_fused_kernel.cu:50-118). Sums are fp32 atomics (order-dependent in the
 // reference too); counts are exact.
-template <typename S, int GROUP>
+template <typename S, int GROUP, bool VEC>
 __global__ void __launch_bounds__(kThreads) lloyd_accumulate_kernel(const S* __restrict__ g, long long period,
                                                                     long long num_blocks, const unsigned char* ws,
                                                                     int k, float* __restrict__ sums,
                                                                     unsigned long long* __restrict__ counts) {
-    __shared__ float thr[kMaxCodebook];
-    __shared__ float ocb[kMaxCodebook];
+    __shared__ __align__(16) unsigned char tables[GEFEN_B200_CODEBOOK_WS_BYTES];
     __shared__ float ssum[kMaxCodebook];
     __shared__ unsigned int scnt[kMaxCodebook];
     __shared__ float red[kWarps];
-    thr[threadIdx.x] = reinterpret_cast<const float*>(ws + kWsThresholdOff)[threadIdx.x];
-    ocb[threadIdx.x] = reinterpret_cast<const float*>(ws + kWsCodebookOff)[threadIdx.x];
     ssum[threadIdx.x] = 0.0f;
     scnt[threadIdx.x] = 0u;
-    __syncthreads();
+    const LloydTables t = stage_lloyd_tables(ws, tables);
     const int lane = threadIdx.x & 31;
     const int tig = GROUP == 32 ? lane : static_cast<int>(threadIdx.x);
     const long long group0 = GROUP == 32 ? static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5)
@@ -272,14 +367,39 @@ __global__ void __launch_bounds__(kThreads) lloyd_accumulate_kernel(const S* __r
     unsigned long long since_flush = 0;
     for (long long b = group0; b < num_blocks; b += stride) {
         const S* gb = g + b * period;
-        const float absmax = block_absmax<S, GROUP>(gb, period, tig, red);
-        for (long long i = tig; i < period; i += GROUP) {
-            const float v = ScalarIO<S>::load(gb + i);
-            float x = 0.0f;
-            if (absmax > 0.0f) x = v / absmax;
-            const int e = entry_exact(x, thr, ocb, k);
-            atomicAdd(&ssum[e], x);
-            atomicAdd(&scnt[e], 1u);
+        if (VEC) {
+            const int nchunks = static_cast<int>(period >> 3);
+            float m = 0.0f;
+            for (int c = lane; c < nchunks; c += 32) {
+                float f[8];
+                load8<S>(gb + 8 * c, f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(f[i]));
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            const BlockDivider divide(m);
+            for (int c = lane; c < nchunks; c += 32) {
+                float f[8];
+                load8<S>(gb + 8 * c, f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float x = divide(f[i]);
+                    const int e = t.entry(x);
+                    atomicAdd(&ssum[e], x);
+                    atomicAdd(&scnt[e], 1u);
+                }
+            }
+        } else {
+            const float absmax = block_absmax<S, GROUP>(gb, period, tig, red);
+            for (long long i = tig; i < period; i += GROUP) {
+                const float v = ScalarIO<S>::load(gb + i);
+                float x = 0.0f;
+                if (absmax > 0.0f) x = v / absmax;
+                const int e = t.entry(x);
+                atomicAdd(&ssum[e], x);
+                atomicAdd(&scnt[e], 1u);
+            }
         }
         since_flush += static_cast<unsigned long long>(period);
         if (GROUP > 32 && since_flush > 0x7fffffffull) {
@@ -301,20 +421,17 @@ __global__ void __launch_bounds__(kThreads) lloyd_accumulate_kernel(const S* __r
 
 // Logging MSE of assigning with the old codebook and reconstructing with the new one
 // (reference: lloyd_max_fused_kernel.cu:120-195).
-template <typename S, int GROUP>
+template <typename S, int GROUP, bool VEC>
 __global__ void __launch_bounds__(kThreads) lloyd_mse_kernel(const S* __restrict__ g, long long period,
                                                              long long num_blocks, const unsigned char* old_ws,
                                                              const float* __restrict__ new_codebook, int k,
                                                              float* __restrict__ mse_norm, float* __restrict__ mse_orig) {
-    __shared__ float thr[kMaxCodebook];
+    __shared__ __align__(16) unsigned char tables[GEFEN_B200_CODEBOOK_WS_BYTES];
     __shared__ float ncb[kMaxCodebook];
     __shared__ float red[kWarps];
     __shared__ float red2[2][kWarps];
-    __shared__ float ocb[kMaxCodebook];
-    thr[threadIdx.x] = reinterpret_cast<const float*>(old_ws + kWsThresholdOff)[threadIdx.x];
-    ocb[threadIdx.x] = reinterpret_cast<const float*>(old_ws + kWsCodebookOff)[threadIdx.x];
     ncb[threadIdx.x] = new_codebook[threadIdx.x < k ? threadIdx.x : k - 1];
-    __syncthreads();
+    const LloydTables t = stage_lloyd_tables(old_ws, tables);
     const int lane = threadIdx.x & 31;
     const int tig = GROUP == 32 ? lane : static_cast<int>(threadIdx.x);
     const long long group0 = GROUP == 32 ? static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5)
@@ -323,15 +440,41 @@ __global__ void __launch_bounds__(kThreads) lloyd_mse_kernel(const S* __restrict
     float en = 0.0f, eo = 0.0f;
     for (long long b = group0; b < num_blocks; b += stride) {
         const S* gb = g + b * period;
-        const float absmax = block_absmax<S, GROUP>(gb, period, tig, red);
-        for (long long i = tig; i < period; i += GROUP) {
-            const float v = ScalarIO<S>::load(gb + i);
-            float x = 0.0f;
-            if (absmax > 0.0f) x = v / absmax;
-            const float err = x - ncb[entry_exact(x, thr, ocb, k)];
-            en = fmaf(err, err, en);
-            const float oe = err * absmax;
-            eo = fmaf(oe, oe, eo);
+        if (VEC) {
+            const int nchunks = static_cast<int>(period >> 3);
+            float m = 0.0f;
+            for (int c = lane; c < nchunks; c += 32) {
+                float f[8];
+                load8<S>(gb + 8 * c, f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(f[i]));
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            const BlockDivider divide(m);
+            for (int c = lane; c < nchunks; c += 32) {
+                float f[8];
+                load8<S>(gb + 8 * c, f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float x = divide(f[i]);
+                    const float err = x - ncb[t.entry(x)];
+                    en = fmaf(err, err, en);
+                    const float oe = err * m;
+                    eo = fmaf(oe, oe, eo);
+                }
+            }
+        } else {
+            const float absmax = block_absmax<S, GROUP>(gb, period, tig, red);
+            for (long long i = tig; i < period; i += GROUP) {
+                const float v = ScalarIO<S>::load(gb + i);
+                float x = 0.0f;
+                if (absmax > 0.0f) x = v / absmax;
+                const float err = x - ncb[t.entry(x)];
+                en = fmaf(err, err, en);
+                const float oe = err * absmax;
+                eo = fmaf(oe, oe, eo);
+            }
         }
     }
     en = warp_sum(en);
@@ -461,12 +604,19 @@ int gefen_b200_exact_histogram(const void* grad_flat, int grad_dtype, int64_t nu
     const int64_t nb = numel / period;
     if (nb == 0) return GEFEN_B200_OK;
     unsigned long long* counts = reinterpret_cast<unsigned long long*>(bin_counts);
+    // a warp's 32-bit counters cannot wrap: a CTA of the warp-per-block form sees at most 2^31 elements
     if (period <= 8192) {
-        const int grid = persistent_grid(nb, kWarps, 4);
-        GEFEN_DISPATCH_S(grad_dtype, histogram_kernel<S, 32><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, histogram_bins, counts));
+        const int grid = persistent_grid(nb, kWarps, 6);
+        const bool vec = period % 8 == 0 && aligned16(grad_flat) && grad_dtype != GEFEN_B200_F64 &&
+                         numel / grid < 0x7fffffffll;
+        if (vec) {
+            GEFEN_DISPATCH_S(grad_dtype, histogram_kernel<S, 32, true><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, histogram_bins, counts));
+        } else {
+            GEFEN_DISPATCH_S(grad_dtype, histogram_kernel<S, 32, false><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, histogram_bins, counts));
+        }
     } else {
-        const int grid = persistent_grid(nb, 1, 4);
-        GEFEN_DISPATCH_S(grad_dtype, histogram_kernel<S, 256><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, histogram_bins, counts));
+        const int grid = persistent_grid(nb, 1, 6);
+        GEFEN_DISPATCH_S(grad_dtype, histogram_kernel<S, 256, false><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, histogram_bins, counts));
     }
     GEFEN_CHECK_CUDA(cudaGetLastError());
     return GEFEN_B200_OK;
@@ -589,12 +739,17 @@ int gefen_b200_lloyd_accumulate(const void* grad_flat, int grad_dtype, int64_t n
     if (nb == 0) return GEFEN_B200_OK;
     unsigned long long* cnt = reinterpret_cast<unsigned long long*>(counts);
     const unsigned char* wsb = static_cast<const unsigned char*>(ws);
+    GEFEN_CHECK_ARG(aligned16(ws), "Expected a 16-byte aligned codebook workspace.");
     if (period <= 8192) {
         const int grid = persistent_grid(nb, kWarps, 4);
-        GEFEN_DISPATCH_S(grad_dtype, lloyd_accumulate_kernel<S, 32><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, wsb, codebook_size, sums, cnt));
+        if (period % 8 == 0 && aligned16(grad_flat) && grad_dtype != GEFEN_B200_F64) {
+            GEFEN_DISPATCH_S(grad_dtype, lloyd_accumulate_kernel<S, 32, true><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, wsb, codebook_size, sums, cnt));
+        } else {
+            GEFEN_DISPATCH_S(grad_dtype, lloyd_accumulate_kernel<S, 32, false><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, wsb, codebook_size, sums, cnt));
+        }
     } else {
         const int grid = persistent_grid(nb, 1, 4);
-        GEFEN_DISPATCH_S(grad_dtype, lloyd_accumulate_kernel<S, 256><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, wsb, codebook_size, sums, cnt));
+        GEFEN_DISPATCH_S(grad_dtype, lloyd_accumulate_kernel<S, 256, false><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, wsb, codebook_size, sums, cnt));
     }
     GEFEN_CHECK_CUDA(cudaGetLastError());
     return GEFEN_B200_OK;
@@ -615,12 +770,17 @@ int gefen_b200_lloyd_mse(const void* grad_flat, int grad_dtype, int64_t numel, i
     const int64_t nb = numel / period;
     if (nb == 0) return GEFEN_B200_OK;
     const unsigned char* wsb = static_cast<const unsigned char*>(ws);
+    GEFEN_CHECK_ARG(aligned16(ws), "Expected a 16-byte aligned codebook workspace.");
     if (period <= 8192) {
         const int grid = persistent_grid(nb, kWarps, 4);
-        GEFEN_DISPATCH_S(grad_dtype, lloyd_mse_kernel<S, 32><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, wsb, new_codebook, codebook_size, mse_normalized_sum, mse_original_sum));
+        if (period % 8 == 0 && aligned16(grad_flat) && grad_dtype != GEFEN_B200_F64) {
+            GEFEN_DISPATCH_S(grad_dtype, lloyd_mse_kernel<S, 32, true><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, wsb, new_codebook, codebook_size, mse_normalized_sum, mse_original_sum));
+        } else {
+            GEFEN_DISPATCH_S(grad_dtype, lloyd_mse_kernel<S, 32, false><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, wsb, new_codebook, codebook_size, mse_normalized_sum, mse_original_sum));
+        }
     } else {
         const int grid = persistent_grid(nb, 1, 4);
-        GEFEN_DISPATCH_S(grad_dtype, lloyd_mse_kernel<S, 256><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, wsb, new_codebook, codebook_size, mse_normalized_sum, mse_original_sum));
+        GEFEN_DISPATCH_S(grad_dtype, lloyd_mse_kernel<S, 256, false><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, wsb, new_codebook, codebook_size, mse_normalized_sum, mse_original_sum));
     }
     GEFEN_CHECK_CUDA(cudaGetLastError());
     return GEFEN_B200_OK;

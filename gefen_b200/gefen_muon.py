@@ -17,7 +17,7 @@ import torch.nn as nn
 
 from . import _lib
 from .gefen import Gefen, _local, automatic_partition_view
-from .newton_schulz import zeropower_via_newtonschulz
+from .newton_schulz import orthogonalize_all
 
 EPS = 1e-7
 DEFAULT_A = 3.4445
@@ -174,13 +174,17 @@ class GefenMuon(Gefen):
             total = sum((it[4].numel() + 7) // 8 * 8 for it in chunk)
             scratch = self._momentum_scratch(total, chunk[0][4].dtype, chunk[0][4].device)
             outs = self._quantized_momentum(chunk, scratch)
-            for (group, name, p, local_p, grad), update in zip(chunk, outs):
-                ortho = zeropower_via_newtonschulz(update, group["ns_coefficients"], group["ns_steps"], group["eps"])
+
+            def apply(i, ortho):
+                group, name, p, local_p, grad = chunk[i]
                 lr = group["lr"]
                 adjusted_lr = _adjust_lr(lr, group["adjust_lr_fn"], p.shape)
                 if group["weight_decay"] > 0.0:
                     local_p.mul_(1 - float(lr) * group["weight_decay"])
                 local_p.add_(ortho, alpha=-adjusted_lr)
+
+            orthogonalize_all([(update, group["ns_coefficients"], group["ns_steps"], group["eps"])
+                               for (group, name, p, local_p, grad), update in zip(chunk, outs)], apply)
 
     @torch.no_grad()
     def step(self, closure=None):

@@ -22,15 +22,17 @@ _STATUS = {}
 
 
 _SCRATCH = {}
+LANES = 2   # matrices orthogonalised side by side (see `orthogonalize_all`)
 
 
-def _scratch(device, numel: int) -> torch.Tensor:
-    """Per-device bf16 scratch for the iteration (Gram matrix, polynomial, second iterate), grown on demand.
-    Work on one stream is ordered, so successive matrices can share it."""
-    t = _SCRATCH.get(device.index)
+def _scratch(device, numel: int, lane: int = 0) -> torch.Tensor:
+    """Per-device, per-lane bf16 scratch for the iteration (Gram matrix, polynomial, both iterates), grown on
+    demand. Work on one stream is ordered, so successive matrices of a lane can share it."""
+    key = (device.index, lane)
+    t = _SCRATCH.get(key)
     if t is None or t.numel() < numel:
         t = torch.empty(numel, dtype=torch.bfloat16, device=device)
-        _SCRATCH[device.index] = t
+        _SCRATCH[key] = t
     return t[:numel]
 
 
@@ -100,8 +102,9 @@ def gemm_tt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
     return out
 
 
-def zeropower_via_newtonschulz(grad: torch.Tensor, ns_coefficients: Tuple[float, float, float], ns_steps: int,
-                               eps: float) -> torch.Tensor:
+def _newton_schulz_into_scratch(grad: torch.Tensor, ns_coefficients, ns_steps: int, eps: float, lane: int) -> torch.Tensor:
+    """The iteration on the current stream; returns a VIEW of the lane's scratch that holds the result (valid
+    until the lane's next matrix is enqueued)."""
     if ns_steps >= 100:
         raise ValueError("Number of steps must be less than 100 for computational efficiency")
     if len(grad.shape) != 2:
@@ -116,17 +119,16 @@ def zeropower_via_newtonschulz(grad: torch.Tensor, ns_coefficients: Tuple[float,
     if rows == 0 or cols == 0:
         return x
     # bf16 norm and quotient, as the reference's div_ (the Frobenius norm does not care about orientation).
-    # Both iterates live in the per-device scratch: the same addresses for every matrix of a shape, which
-    # lets the native driver replay the chain of products as one graph.
+    # Both iterates live in the lane's scratch: the same addresses for every matrix of a shape, which lets
+    # the native driver replay the chain of products as one graph.
     prow, pcol = (rows + 7) // 8 * 8, (cols + 7) // 8 * 8
     m = min(prow, pcol)
-    scratch = _scratch(x.device, 2 * m * m + 2 * prow * pcol)
+    scratch = _scratch(x.device, 2 * m * m + 2 * prow * pcol, lane)
     gram = scratch[: m * m]
     poly = scratch[m * m: 2 * m * m]
     nxt = scratch[2 * m * m: 2 * m * m + prow * pcol].view(prow, pcol)
     first = scratch[2 * m * m + prow * pcol: 2 * m * m + 2 * prow * pcol].view(prow, pcol)
-    padded = (prow, pcol) != (rows, cols)
-    if padded:
+    if (prow, pcol) != (rows, cols):
         first.zero_()
         nxt.zero_()
     torch.div(x, x.norm().clamp(min=eps), out=first[:rows, :cols])
@@ -136,4 +138,48 @@ def zeropower_via_newtonschulz(grad: torch.Tensor, ns_coefficients: Tuple[float,
                 _lib.ptr(first), _lib.ptr(nxt), _lib.ptr(gram), _lib.ptr(poly), prow, pcol, int(ns_steps), float(a), float(b),
                 float(c), _lib.ptr(_status(x.device)), _lib.current_stream(x.device)))
     result = first if ns_steps % 2 == 0 else nxt
-    return result[:rows, :cols].clone()
+    return result[:rows, :cols]
+
+
+def zeropower_via_newtonschulz(grad: torch.Tensor, ns_coefficients: Tuple[float, float, float], ns_steps: int,
+                               eps: float) -> torch.Tensor:
+    """reference: gefen_muon.py:16-51. Returns a new tensor."""
+    return _newton_schulz_into_scratch(grad, ns_coefficients, ns_steps, eps, 0).clone()
+
+
+_LANE_STREAMS = {}
+
+
+def _lane_streams(device):
+    streams = _LANE_STREAMS.get(device.index)
+    if streams is None:
+        streams = _LANE_STREAMS[device.index] = [torch.cuda.Stream(device) for _ in range(LANES)]
+    return streams
+
+
+def orthogonalize_all(items, consume) -> None:
+    """Newton-Schulz for many matrices, LANES of them side by side.
+
+    items: list of (matrix, ns_coefficients, ns_steps, eps); consume(i, ortho) is called with the
+    orthogonalised matrix i (a view of scratch memory: use it at once, on the current stream). The two
+    symmetric products of an iteration have fewer output tiles than the GPU has SMs (72 tiles of 128 x 256
+    for a 2048-row Gram matrix); running the chains of two matrices on two streams lets those launches
+    share the SMs. Every lane stream starts after the work already on the caller's stream and the caller's
+    stream waits for all lanes at the end, so to the caller this is one ordered piece of work."""
+    if not items:
+        return
+    device = items[0][0].device
+    cur = torch.cuda.current_stream(device)
+    streams = _lane_streams(device)
+    start = torch.cuda.Event()
+    start.record(cur)
+    for lane, stream in enumerate(streams):
+        stream.wait_event(start)
+    for i, (matrix, coefficients, steps, eps) in enumerate(items):
+        lane = i % LANES
+        with torch.cuda.stream(streams[lane]):
+            consume(i, _newton_schulz_into_scratch(matrix, coefficients, steps, eps, lane))
+    for stream in streams:
+        done = torch.cuda.Event()
+        done.record(stream)
+        cur.wait_event(done)
