@@ -623,8 +623,12 @@ class Zero1Gefen:
                 verdict["in_kernel_reduce_bit_identical"] = same
                 verdict["in_kernel_reduce_tensors"] = len(keep)
         # every rank ends with the same parameters
-        check = self.flat_param.view(torch.int16).to(torch.int64).sum().reshape(1) if self.flat_param.element_size() == 2 \
-            else self.flat_param.view(torch.int32).to(torch.int64).sum().reshape(1)
+        # (summed in slices: the int64 copy torch makes of a slice stays small beside a buffer that may fill the GPU)
+        bits = torch.int16 if self.flat_param.element_size() == 2 else torch.int32
+        as_int = self.flat_param.view(bits)
+        check = torch.zeros(1, dtype=torch.int64, device=self.device)
+        for begin in range(0, as_int.numel(), 1 << 27):
+            check += as_int[begin:begin + (1 << 27)].sum(dtype=torch.int64)
         lo, hi = check.clone(), check.clone()
         if self.world > 1:
             dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=self.group)
