@@ -12,7 +12,7 @@
 //
 // Two kernels:
 //  * step_vec_kernel  - the fast path. One warp owns one block (several blocks when they are
-//    shorter than 256 elements). Codes and gradients are read once
+//    not longer than 1024 elements: see lanes_per_block). Codes and gradients are read once
 //    (128-bit loads), the updated momenta wait in the warp's slice of shared memory while the
 //    block's absmax is reduced with shuffles, then they are re-encoded and the parameters updated:
 //    codes, gradients and params cross HBM exactly once (8 B/element in bf16, 14 B/element in
@@ -302,13 +302,21 @@ __device__ __forceinline__ void staged_momenta(const float4* stage_a, const floa
 }
 
 // --------------------------------------------------------------------------- fast path
-// Lanes that share one block: all 32 for blocks of 256 elements or more, otherwise the smallest
-// power of two that covers the block's chunks, so that a warp works on 32 / lanes blocks at once.
+// Lanes that share one block, a power of two, so that a warp works on 32 / lanes blocks at once. Blocks of
+// up to 256 elements: the smallest power of two that covers the block's chunks (one chunk per lane). Longer
+// blocks: about eight chunks per lane, as in a 2048-element block, so that the per-block work (reductions,
+// step size, reciprocal, descriptor reads) is shared by as many elements: 8 lanes for 512 elements, 16 for
+// 1024, all 32 from 1032 elements on (measured on 512-element blocks: 0.43 ms -> 0.32 ms per 134 M elements).
 __host__ __device__ __forceinline__ int lanes_per_block(long long period) {
     const long long nchunks = period >> 3;
+    const long long want = nchunks > 32 ? (nchunks + 7) >> 3 : nchunks;
     int lanes = 1;
-    while (lanes < 32 && lanes < nchunks) lanes <<= 1;
+    while (lanes < 32 && lanes < want) lanes <<= 1;
     return lanes;
+}
+// Elements of one work unit of a tensor (what a warp stages at a time).
+__host__ __device__ __forceinline__ long long unit_elements(long long period) {
+    return period * (32 / lanes_per_block(period));
 }
 // Work units (one warp pass each) of a tensor on the fast path.
 __host__ __device__ __forceinline__ long long vec_units(long long num_blocks, long long period) {
@@ -368,7 +376,7 @@ __device__ __forceinline__ void first_pass_group(const S* g_blk, const uint2* co
             const uint32_t cw[2] = {craw[u].x, craw[u].y};
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const uint32_t code = (cw[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+                const uint32_t code = __byte_perm(cw[i >> 2], 0u, 0x4440u + (i & 3));   // byte i & 3, zero-extended
                 const float cur = old_mag * rep[code * kRepCopies];
                 m[i] = ema_update(beta1, cur, omb1, g[i]);
                 absmax = max_abs_nan(absmax, m[i]);
@@ -453,7 +461,7 @@ __device__ __forceinline__ void reduce_pass(const StepLaunch& L, const S* g_blk,
 
 // One warp, one unit: 32 / LANES consecutive blocks of t.period = 8 * nchunks elements, LANES lanes
 // each (LANES = lanes_per_block(t.period), uniform over the warp; FULL fixes it to 32 at compile
-// time). A block's slice of `stage` holds period floats: the first halves of all chunks, then the
+// time, for blocks of more than 1024 elements). A block's slice of `stage` holds period floats: the first halves of all chunks, then the
 // second halves, so that the 128-bit shared accesses of a full warp are conflict-free.
 // The descriptor lives in global or parameter memory, which the stores below might alias as far as
 // the compiler can tell: everything the loops need from it is copied into locals first.
@@ -694,14 +702,15 @@ __global__ void __launch_bounds__(vec_max_threads<S, GSRC>(), 1) step_vec_kernel
         const long long nb_local = gb - t_first;
         const long long next = nb_local + warp_stride;
         // same tensor: hint the next block of this warp (measured: pays for 2-byte dtypes with long blocks only)
-        if (GSRC == 0 && sizeof(S) == 2 && t.period >= 1024 && next < t_count) {
-            const long long elem0 = next * t.period;
-            prefetch_l2_range(t.codes + elem0, t.period, lane);
-            prefetch_l2_range(static_cast<const char*>(t.g) + elem0 * sizeof(S), t.period * sizeof(S), lane);
+        const long long unit_elems = unit_elements(t.period);
+        if (GSRC == 0 && sizeof(S) == 2 && unit_elems >= 1024 && next + 1 < t_count) {   // (not a ragged last unit)
+            const long long elem0 = next * unit_elems;
+            prefetch_l2_range(t.codes + elem0, unit_elems, lane);
+            prefetch_l2_range(static_cast<const char*>(t.g) + elem0 * sizeof(S), unit_elems * sizeof(S), lane);
             if (!(t.flags & GEFEN_B200_STEP_MUON))
-                prefetch_l2_range(static_cast<const char*>(t.p) + elem0 * sizeof(S), t.period * sizeof(S), lane);
+                prefetch_l2_range(static_cast<const char*>(t.p) + elem0 * sizeof(S), unit_elems * sizeof(S), lane);
         }
-        if (t.period >= 256) warp_block_step<S, GSRC, true>(t, nb_local, L, s, stage, lane);
+        if (lanes_per_block(t.period) == 32) warp_block_step<S, GSRC, true>(t, nb_local, L, s, stage, lane);
         else warp_block_step<S, GSRC, false>(t, nb_local, L, s, stage, lane);
     }
 }
@@ -974,7 +983,8 @@ static int launch_vec_variant(StepLaunch L, const gefen_b200_step_tensor_t& sing
             configured[dev] = true;
         }
     }
-    // a warp stages one long block, or the 32 / lanes short blocks (at most 256 elements together) of a unit
+    // a warp stages one unit: one long block, or the 32 / lanes shorter blocks that share the warp
+    // (max_period: the largest unit of the launch, see unit_elements)
     const long long stage_bytes = (max_period > 256 ? max_period : 256) * 4;
     int max_warps = vec_max_threads<S, GSRC>() / 32;
     if (warps_override() > 0 && warps_override() < max_warps) max_warps = warps_override();
@@ -1096,7 +1106,7 @@ static int run_single(gefen_b200_step_tensor_t& t, int param_dtype, const float*
     L.grad_mc_delta = 0;
     L.param_mc_delta = 0;
     L.spin_limit = g_stage_spin_limit;
-    return launch_class(cls, param_dtype, L, t, t.period, stream);
+    return launch_class(cls, param_dtype, L, t, cls == 1 ? unit_elements(t.period) : t.period, stream);
 }
 
 }  // namespace gefen
@@ -1400,8 +1410,11 @@ int gefen_b200_multi_tensor_step_multicast(gefen_b200_step_tensor_t* host_table,
         const int run = host_table[begin].reserved_[1];
         const gefen_b200_step_tensor_t& last = host_table[begin + run - 1];
         const long long total = last.first_block + class_units(last, last.reserved_[0]);
-        long long max_period = 0;
-        for (int i = begin; i < begin + run; ++i) max_period = host_table[i].period > max_period ? host_table[i].period : max_period;
+        long long max_period = 0;   // largest staging need of a warp: the elements of one unit on the staged path
+        for (int i = begin; i < begin + run; ++i) {
+            const long long need = host_table[begin].reserved_[0] == 1 ? unit_elements(host_table[i].period) : host_table[i].period;
+            max_period = need > max_period ? need : max_period;
+        }
         if (total > 0) {
             StepLaunch L;
             L.table = static_cast<const gefen_b200_step_tensor_t*>(device_table) + begin;
