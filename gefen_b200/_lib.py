@@ -75,6 +75,7 @@ def _declare(lib):
         "gefen_b200_multi_tensor_step_peers": (i32, [vp, vp, i32, i32, vp, vp, i32, vp, i32, dbl, vp]),
         "gefen_b200_multi_tensor_step_multicast": (i32, [vp, vp, i32, i32, vp, vp, i32, vp, i32, dbl, i64, i64, vp]),
         "gefen_b200_multicast_sum": (i32, [vp, vp, i32, i64, dbl, vp]),
+        "gefen_b200_muon_apply": (i32, [vp, vp, i32, i64, dbl, dbl, vp, i32, vp]),
         "gefen_b200_step_tensor_size": (i32, []),
         "gefen_b200_step_tensor_class": (i32, [vp, i32]),
         "gefen_b200_step_status": (i32, [vp, i32]),

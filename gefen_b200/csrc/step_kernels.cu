@@ -929,6 +929,46 @@ __global__ void __launch_bounds__(kThreads) multicast_sum_kernel(void* __restric
     }
 }
 
+// --------------------------------------------------------------------------- GefenMuon apply
+// p <- round(p * wd_mul) ; p <- round(p + alpha * u)   (reference: gefen_muon.py:326-329, torch's mul_ and
+// add_(update, alpha=-adjusted_lr): each rounds to the parameter dtype), one pass over p and u instead of
+// two kernels, and - for ZeRO-1 ranks whose parameter buffers are mapped into each other - the updated
+// parameters also stored to the peers' copies (the all-gather).
+template <typename S>
+__global__ void __launch_bounds__(kThreads) muon_apply_kernel(S* __restrict__ p, const S* __restrict__ u, long long numel,
+                                                              float wd_mul, bool decay, float alpha, bool vec,
+                                                              const __grid_constant__ StepLaunch L) {
+    const long long stride = static_cast<long long>(gridDim.x) * kThreads;
+    const long long tid = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+    const long long chunks = vec ? numel >> 3 : 0;
+    for (long long c = tid; c < chunks; c += stride) {
+        Chunk<S> pr, ur;
+        pr.load(p, c);
+        ur.load(u, c);
+        float pv[8], uv[8];
+        pr.unpack(pv);
+        ur.unpack(uv);
+        if (decay) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) pv[i] *= wd_mul;
+            pr.pack(pv);
+            pr.unpack(pv);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) pv[i] = fmaf(alpha, uv[i], pv[i]);
+        pr.pack(pv);
+        pr.store(p, c);
+        for (int r = 0; r < L.n_peers; ++r) pr.store(peer_ptr(p, L.peer_delta[r]), c);
+    }
+    for (long long i = chunks * 8 + tid; i < numel; i += stride) {
+        float pv = ScalarIO<S>::load(p + i);
+        if (decay) pv = ScalarIO<S>::round(pv * wd_mul);
+        pv = fmaf(alpha, ScalarIO<S>::load(u + i), pv);
+        ScalarIO<S>::store(p + i, pv);
+        for (int r = 0; r < L.n_peers; ++r) ScalarIO<S>::store(peer_ptr(p + i, L.peer_delta[r]), pv);
+    }
+}
+
 // --------------------------------------------------------------------------- host dispatch
 static int grid_for(long long groups_needed, int groups_per_cta, int ctas_per_sm) {
     long long ctas = (groups_needed + groups_per_cta - 1) / groups_per_cta;
@@ -1309,6 +1349,36 @@ int gefen_b200_multicast_sum(void* dst, const void* src_multicast, int dtype, in
     if (dtype == GEFEN_B200_BF16) multicast_sum_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(dst, src_multicast, chunks, sc);
     else if (dtype == GEFEN_B200_F16) multicast_sum_kernel<__half><<<grid, kThreads, 0, stream>>>(dst, src_multicast, chunks, sc);
     else multicast_sum_kernel<float><<<grid, kThreads, 0, stream>>>(dst, src_multicast, chunks, sc);
+    GEFEN_CHECK_CUDA(cudaGetLastError());
+    return GEFEN_B200_OK;
+}
+
+int gefen_b200_muon_apply(void* p, const void* update, int dtype, int64_t numel, double wd_mul, double alpha,
+                          const int64_t* peer_deltas, int n_peers, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    GEFEN_CHECK_ARG(p != nullptr && update != nullptr, "Expected non-null p and update.");
+    GEFEN_CHECK_ARG(dtype == GEFEN_B200_F32 || dtype == GEFEN_B200_F16 || dtype == GEFEN_B200_BF16,
+                    "The GefenMuon apply supports fp32, fp16 and bf16 parameters.");
+    GEFEN_CHECK_ARG(numel >= 0, "Expected a non-negative element count.");
+    GEFEN_CHECK_ARG(n_peers >= 0 && n_peers <= GEFEN_B200_MAX_PEERS, "Expected between 0 and %d peers, got %d.",
+                    GEFEN_B200_MAX_PEERS, n_peers);
+    GEFEN_CHECK_ARG(n_peers == 0 || peer_deltas != nullptr, "Expected peer offsets for %d peers.", n_peers);
+    for (int r = 0; r < n_peers; ++r)
+        GEFEN_CHECK_ARG(peer_deltas[r] % 16 == 0, "Peer offset %d is not a multiple of 16 bytes.", r);
+    if (numel == 0) return GEFEN_B200_OK;
+    StepLaunch L = {};
+    L.n_peers = n_peers;
+    for (int r = 0; r < n_peers; ++r) L.peer_delta[r] = peer_deltas[r];
+    const bool vec = aligned16(p) && aligned16(update);
+    const bool decay = wd_mul != 1.0;
+    const int grid = grid_for((numel + 7) / 8, kThreads, 8);
+    const float wm = static_cast<float>(wd_mul), a = static_cast<float>(alpha);
+    if (dtype == GEFEN_B200_BF16)
+        muon_apply_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(static_cast<__nv_bfloat16*>(p), static_cast<const __nv_bfloat16*>(update), numel, wm, decay, a, vec, L);
+    else if (dtype == GEFEN_B200_F16)
+        muon_apply_kernel<__half><<<grid, kThreads, 0, stream>>>(static_cast<__half*>(p), static_cast<const __half*>(update), numel, wm, decay, a, vec, L);
+    else
+        muon_apply_kernel<float><<<grid, kThreads, 0, stream>>>(static_cast<float*>(p), static_cast<const float*>(update), numel, wm, decay, a, vec, L);
     GEFEN_CHECK_CUDA(cudaGetLastError());
     return GEFEN_B200_OK;
 }

@@ -170,18 +170,33 @@ class GefenMuon(Gefen):
             cur_elems += n
         if cur:
             chunks.append(cur)
+        lib = _lib.load()
         for chunk in chunks:
             total = sum((it[4].numel() + 7) // 8 * 8 for it in chunk)
             scratch = self._momentum_scratch(total, chunk[0][4].dtype, chunk[0][4].device)
             outs = self._quantized_momentum(chunk, scratch)
 
+            peers = getattr(self, "_peer_param_deltas", None)
+            n_peers = 0 if peers is None else len(peers)
+
             def apply(i, ortho):
+                # decoupled weight decay and the update (reference: gefen_muon.py:325-329), one kernel; for a
+                # ZeRO-1 rank it also stores the updated matrix into the other ranks' parameter buffers
                 group, name, p, local_p, grad = chunk[i]
                 lr = group["lr"]
                 adjusted_lr = _adjust_lr(lr, group["adjust_lr_fn"], p.shape)
-                if group["weight_decay"] > 0.0:
-                    local_p.mul_(1 - float(lr) * group["weight_decay"])
-                local_p.add_(ortho, alpha=-adjusted_lr)
+                wd_mul = 1 - float(lr) * group["weight_decay"] if group["weight_decay"] > 0.0 else 1.0
+                if ortho.dtype != local_p.dtype or not local_p.is_contiguous():
+                    if wd_mul != 1.0:
+                        local_p.mul_(wd_mul)
+                    local_p.add_(ortho, alpha=-adjusted_lr)
+                    return
+                if not ortho.is_contiguous():
+                    ortho = ortho.contiguous()
+                with _lib.device_guard(local_p.device):
+                    _lib.check(lib.gefen_b200_muon_apply(
+                        _lib.ptr(local_p), _lib.ptr(ortho), _lib.dtype_tag(local_p.dtype), local_p.numel(), wd_mul,
+                        -adjusted_lr, peers.ctypes.data if n_peers else None, n_peers, _lib.current_stream(local_p.device)))
 
             orthogonalize_all([(update, group["ns_coefficients"], group["ns_steps"], group["eps"])
                                for (group, name, p, local_p, grad), update in zip(chunk, outs)], apply)

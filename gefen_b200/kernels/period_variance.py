@@ -91,3 +91,22 @@ def scores_from_stats(stats_host: torch.Tensor):
 def period_scan(flat: torch.Tensor, periods, *, input_is_squared: bool, epsilon: float):
     return scores_from_stats(period_scan_async(flat, periods, input_is_squared=input_is_squared,
                                                epsilon=epsilon).cpu())
+
+
+# The reference registers its variance score as an opaque custom operator so that graph capture treats it
+# as one node (kernels/period_variance.py:49-72); the same registration under this package's namespace.
+if hasattr(torch.library, "custom_op"):
+
+    @torch.library.custom_op("gefen_b200::average_within_block_variance_cuda", mutates_args=())
+    def _average_within_block_variance_cuda_opaque(values: torch.Tensor, period: int, input_is_squared: bool) -> torch.Tensor:
+        score = average_within_block_variance_cuda_kernel(values, period, input_is_squared=input_is_squared)
+        return torch.tensor(score, dtype=torch.float64, device=values.device)
+
+    @_average_within_block_variance_cuda_opaque.register_fake
+    def _average_within_block_variance_cuda_opaque_fake(values: torch.Tensor, period: int, input_is_squared: bool) -> torch.Tensor:
+        del period, input_is_squared
+        return values.new_empty((), dtype=torch.float64)
+
+    _OPAQUE_OP_AVAILABLE = True
+else:
+    _OPAQUE_OP_AVAILABLE = False

@@ -772,19 +772,22 @@ class Zero1Gefen:
 
 class Zero1GefenMuon(Zero1Gefen):
     """GefenMuon over ZeRO-1 sharded state. Newton-Schulz needs whole matrices, so whole tensors are
-    assigned to ranks (`WholeTensorLayout`); the step is reduce-scatter of the gradients, GefenMuon on
-    the owned matrices, all-gather of the parameters (NCCL: the final update is not one of this
-    library's kernels, so there is nothing to ride the all-gather on). N ranks reproduce one rank bit
-    for bit: every matrix is processed whole by the same kernels, and the codebook is fitted from the
-    gathered histogram."""
+    assigned to ranks (`WholeTensorLayout`); the step is NCCL's reduce-scatter of the gradients, then
+    GefenMuon on the owned matrices, whose last kernel per matrix (decay + update,
+    `gefen_b200_muon_apply`) also stores the new matrix into every peer's parameter buffer: the
+    all-gather rides on those stores, under the other matrices' Newton-Schulz products (plain peer
+    stores; the multicast form would only add the loop back through the switch here, since nothing flows
+    the other way at the same time). N ranks reproduce one rank bit for bit: every matrix is processed
+    whole by the same kernels, and the codebook is fitted from the gathered histogram."""
 
     def __init__(self, named_params, lr=1e-3, weight_decay=0.1, momentum=0.95, nesterov=True,
                  ns_coefficients=(3.4445, -4.7750, 2.0315), eps=1e-7, ns_steps=5, adjust_lr_fn=None, *, group=None,
-                 ops=None, average_gradients: bool = True):
+                 ops=None, average_gradients: bool = True, fused_all_gather: Optional[bool] = None):
         self._muon_kwargs = dict(lr=lr, weight_decay=weight_decay, momentum=momentum, nesterov=nesterov,
                                  ns_coefficients=ns_coefficients, eps=eps, ns_steps=ns_steps, adjust_lr_fn=adjust_lr_fn)
         super().__init__(named_params, lr=lr, eps=eps, weight_decay=weight_decay, group=group, ops=ops,
-                         average_gradients=average_gradients, fused_all_gather=False, fused_reduce_scatter=False)
+                         average_gradients=average_gradients, fused_all_gather=fused_all_gather,
+                         fused_reduce_scatter=False, multicast=False)
 
     def _make_layout(self, shapes):
         for s in shapes:

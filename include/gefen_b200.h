@@ -274,6 +274,15 @@ int gefen_b200_exact_dp(const double* prefix_w, const double* prefix_wx, const d
                         int num_points, int num_codebooks, int force_endpoints, void* dp_scratch,
                         float* codebook_out, void* stream);
 
+/* The end of a GefenMuon step for one matrix (replaces the two torch kernels of gefen_muon.py:326-329):
+ *   p <- round(p * wd_mul)          (skipped when wd_mul == 1; wd_mul = 1 - lr * weight_decay)
+ *   p <- round(p + alpha * update)  (alpha = -adjusted_lr; update = the orthogonalised momentum)
+ * in one pass, p and update of the same dtype (fp32, fp16 or bf16). With n_peers > 0 every updated
+ * parameter is also stored to the same position of the peers' parameter buffers (peer_deltas as for
+ * gefen_b200_multi_tensor_step_peers): the all-gather of a ZeRO-1 group rides on the kernel. */
+int gefen_b200_muon_apply(void* p, const void* update, int dtype, int64_t numel, double wd_mul, double alpha,
+                          const int64_t* peer_deltas, int n_peers, void* stream);
+
 /* bf16 GEMM on the tcgen05 tensor cores for GefenMuon's Newton-Schulz iteration (replaces the
  * torch.addmm / `@` calls, i.e. cuBLAS, of gefen_muon.py:39-47):
  *   D[M,N] = alpha * A[M,K] * B[N,K]^T + beta * C[M,N], and Dt[N,M] = D^T when dt != NULL.

@@ -84,6 +84,9 @@ def test_unused_scores_match(oracle, cuda_device):
         want = float(stats[0] / stats[1])
         got = average_within_block_coefficient_of_variation_cuda_kernel(g.to(cuda_device), period, input_is_squared=False)
         assert got == pytest.approx(want, rel=1e-4)
+    # the opaque custom operator of the variance score (reference: kernels/period_variance.py:49-72)
+    opaque = torch.ops.gefen_b200.average_within_block_variance_cuda(g.to(cuda_device), 512, False)
+    assert float(opaque) == average_within_block_variance_cuda_kernel(g.to(cuda_device), 512, input_is_squared=False)
 
 
 @pytest.mark.parametrize("k,force,active", [(256, True, 4096), (256, True, 700), (16, True, 300), (32, False, 1000),

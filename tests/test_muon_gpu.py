@@ -150,3 +150,28 @@ def test_tcgen05_gemm_symmetric_output(cuda_device, m, k):
     gemm_tn(full, full, c=full, alpha=2.0315, beta=-4.775, out=poly_sym, symmetric=True)
     check_status(cuda_device)
     assert torch.equal(poly_sym, poly_full)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("shape", [(256, 512), (1000, 3), (8,), (5,)])
+def test_fused_apply_matches_the_two_torch_kernels(cuda_device, dtype, shape):
+    """gefen_b200_muon_apply against the reference's tail (gefen_muon.py:326-329): `p.mul_(1 - lr*wd)` then
+    `p.add_(update, alpha=-adjusted_lr)`, each rounding to the parameter dtype. The only freedom is whether
+    the second step is one fused multiply-add: within one rounding of the parameter dtype."""
+    from gefen_b200 import _lib
+
+    lib = _lib.load()
+    gen = torch.Generator(device=cuda_device).manual_seed(sum(shape))
+    p = (torch.randn(shape, generator=gen, device=cuda_device) * 0.02).to(dtype)
+    u = torch.randn(shape, generator=gen, device=cuda_device).to(dtype)
+    for wd_mul, alpha in ((1 - 0.02 * 0.1, -0.02 * 1.4142), (1.0, -0.5)):
+        want = p.clone()
+        if wd_mul != 1.0:
+            want.mul_(wd_mul)
+        want.add_(u, alpha=alpha)
+        got = p.clone()
+        _lib.check(lib.gefen_b200_muon_apply(_lib.ptr(got), _lib.ptr(u), _lib.dtype_tag(dtype), got.numel(), wd_mul, alpha,
+                                             None, 0, _lib.current_stream(cuda_device)))
+        ulp = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11, torch.float32: 2.0 ** -24}[dtype]
+        err = (got.float() - want.float()).abs()
+        assert bool((err <= ulp * want.float().abs() * 1.01 + 1e-30).all())
