@@ -77,6 +77,25 @@ template <> __device__ __forceinline__ void load8<double>(const double* p, float
     for (int i = 0; i < 8; ++i) f[i] = static_cast<float>(p[i]);
 }
 
+// NaN-ignoring max |v| over the eight elements at p, folded into m (fmaxf semantics, as block_absmax).
+template <typename S> __device__ __forceinline__ float absmax8(const S* p, float m) {
+    float f[8];
+    load8<S>(p, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(f[i]));
+    return m;
+}
+// bf16: two elements per instruction on the packed pipe (max of two bf16 values is exact; NaN loses).
+template <> __device__ __forceinline__ float absmax8<__nv_bfloat16>(const __nv_bfloat16* p, float m) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162 a = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const __nv_bfloat162 b = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    const __nv_bfloat162 c = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&raw.z));
+    const __nv_bfloat162 d = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&raw.w));
+    const __nv_bfloat162 top = __hmax2(__hmax2(a, b), __hmax2(c, d));
+    return fmaxf(m, fmaxf(__low2float(top), __high2float(top)));
+}
+
 // x = v / absmax as the reference divides (IEEE), through the block's reciprocal where that is exact.
 struct BlockDivider {
     float absmax, rinv;
@@ -98,13 +117,13 @@ struct BlockDivider {
 // per lane and access) or one CTA per very long block. Every element is one shared-memory atomic
 // on the CTA's histogram: the values of a block are bell-shaped over a few hundred bins, so the
 // lanes of a warp rarely meet in one bin, and the hardware serialises those that do.
-template <typename S, int GROUP, bool VEC>
+template <typename S, int GROUP, bool VEC, bool POW2>
 __global__ void __launch_bounds__(kThreads) histogram_kernel(const S* __restrict__ g, long long period,
                                                              long long num_blocks, int bins,
                                                              unsigned long long* __restrict__ counts) {
-    __shared__ unsigned int hist[4096];
+    __shared__ unsigned int hist[4096 + 1];   // one spare counter for x == 1 (see below)
     __shared__ float red[kWarps];
-    for (int i = threadIdx.x; i < bins; i += kThreads) hist[i] = 0u;
+    for (int i = threadIdx.x; i <= bins; i += kThreads) hist[i] = 0u;
     __syncthreads();
 
     const int lane = threadIdx.x & 31;
@@ -121,26 +140,22 @@ __global__ void __launch_bounds__(kThreads) histogram_kernel(const S* __restrict
         if (VEC) {   // GROUP == 32, period a multiple of 8, 16-byte aligned blocks
             const int nchunks = static_cast<int>(period >> 3);
             float m = 0.0f;
-            for (int c = lane; c < nchunks; c += 32) {
-                float f[8];
-                load8<S>(gb + 8 * c, f);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(f[i]));
-            }
+            for (int c = lane; c < nchunks; c += 32) m = absmax8<S>(gb + 8 * c, m);
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
             const BlockDivider divide(m);
-            const unsigned int top = static_cast<unsigned int>(last_bin);
             for (int c = lane; c < nchunks; c += 32) {
                 float f[8];
                 load8<S>(gb + 8 * c, f);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    // |x| <= 1 (or x is NaN), so (x + 1) * scale >= 0: the floor is a truncation, NaN maps to
-                    // bin 0 and only the upper clamp can act
+                    // |x| <= 1 (or x is NaN), so (x + 1) * scale lies in [0, bins]: the floor is a truncation,
+                    // NaN maps to bin 0, and x == 1 lands in the spare counter hist[bins], folded into the last
+                    // bin at the end (the reference's upper clamp). With a power-of-two scale the sum and the
+                    // product round as one fused multiply-add does (scaling by 2^k commutes with rounding).
                     const float x = divide(f[i]);
-                    const unsigned int bin = min(__float2uint_rz((x + 1.0f) * scale), top);
-                    atomicAdd(&hist[bin], 1u);
+                    const float y = POW2 ? fmaf(x, scale, scale) : (x + 1.0f) * scale;
+                    atomicAdd(&hist[__float2uint_rz(y)], 1u);
                 }
             }
         } else {
@@ -164,6 +179,8 @@ __global__ void __launch_bounds__(kThreads) histogram_kernel(const S* __restrict
             since_flush = 0;
         }
     }
+    __syncthreads();
+    if (threadIdx.x == 0) { hist[last_bin] += hist[bins]; hist[bins] = 0u; }
     __syncthreads();
     for (int i = threadIdx.x; i < bins; i += kThreads) {
         if (hist[i]) atomicAdd(&counts[i], static_cast<unsigned long long>(hist[i]));
@@ -344,6 +361,14 @@ __device__ __forceinline__ LloydTables stage_lloyd_tables(const unsigned char* w
     return t;
 }
 
+// x * 2^24 as a two's-complement 64-bit integer (non-finite values, which only non-finite gradients produce,
+// count as 0 in the sum; their count is still taken).
+__device__ __forceinline__ unsigned long long lloyd_fixed(float x) {
+    const float scaled = x * 16777216.0f;
+    const long long q = (fabsf(scaled) <= 16777216.0f) ? static_cast<long long>(__float2int_rn(scaled)) : 0ll;
+    return static_cast<unsigned long long>(q);
+}
+
 // E-step: per codebook entry, the sum of the normalised values assigned to it and their count
 // (reference: lloyd_max_fused_kernel.cu:50-118). Sums are fp32 atomics (order-dependent in the
 // reference too); counts are exact.
@@ -353,10 +378,13 @@ __global__ void __launch_bounds__(kThreads) lloyd_accumulate_kernel(const S* __r
                                                                     int k, float* __restrict__ sums,
                                                                     unsigned long long* __restrict__ counts) {
     __shared__ __align__(16) unsigned char tables[GEFEN_B200_CODEBOOK_WS_BYTES];
-    __shared__ float ssum[kMaxCodebook];
+    // Per-entry sums are kept in shared memory as 64-bit fixed point (x * 2^24, |x| <= 1): integer atomics
+    // instead of a compare-and-swap loop per float addition, no dependence on the order of the additions, and
+    // every value of magnitude 2^-1 or more is represented exactly (smaller ones to 2^-25 absolute).
+    __shared__ unsigned long long ssum[kMaxCodebook];
     __shared__ unsigned int scnt[kMaxCodebook];
     __shared__ float red[kWarps];
-    ssum[threadIdx.x] = 0.0f;
+    ssum[threadIdx.x] = 0ull;
     scnt[threadIdx.x] = 0u;
     const LloydTables t = stage_lloyd_tables(ws, tables);
     const int lane = threadIdx.x & 31;
@@ -386,7 +414,7 @@ __global__ void __launch_bounds__(kThreads) lloyd_accumulate_kernel(const S* __r
                 for (int i = 0; i < 8; ++i) {
                     const float x = divide(f[i]);
                     const int e = t.entry(x);
-                    atomicAdd(&ssum[e], x);
+                    atomicAdd(&ssum[e], lloyd_fixed(x));
                     atomicAdd(&scnt[e], 1u);
                 }
             }
@@ -397,7 +425,7 @@ __global__ void __launch_bounds__(kThreads) lloyd_accumulate_kernel(const S* __r
                 float x = 0.0f;
                 if (absmax > 0.0f) x = v / absmax;
                 const int e = t.entry(x);
-                atomicAdd(&ssum[e], x);
+                atomicAdd(&ssum[e], lloyd_fixed(x));
                 atomicAdd(&scnt[e], 1u);
             }
         }
@@ -414,7 +442,8 @@ __global__ void __launch_bounds__(kThreads) lloyd_accumulate_kernel(const S* __r
     }
     __syncthreads();
     if (threadIdx.x < k) {
-        atomicAdd(&sums[threadIdx.x], ssum[threadIdx.x]);
+        const double total = static_cast<double>(static_cast<long long>(ssum[threadIdx.x])) * (1.0 / 16777216.0);
+        atomicAdd(&sums[threadIdx.x], static_cast<float>(total));
         atomicAdd(&counts[threadIdx.x], static_cast<unsigned long long>(scnt[threadIdx.x]));
     }
 }
@@ -609,14 +638,17 @@ int gefen_b200_exact_histogram(const void* grad_flat, int grad_dtype, int64_t nu
         const int grid = persistent_grid(nb, kWarps, 6);
         const bool vec = period % 8 == 0 && aligned16(grad_flat) && grad_dtype != GEFEN_B200_F64 &&
                          numel / grid < 0x7fffffffll;
-        if (vec) {
-            GEFEN_DISPATCH_S(grad_dtype, histogram_kernel<S, 32, true><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, histogram_bins, counts));
+        const bool pow2 = (histogram_bins & (histogram_bins - 1)) == 0 && histogram_bins >= 2;
+        if (vec && pow2) {
+            GEFEN_DISPATCH_S(grad_dtype, histogram_kernel<S, 32, true, true><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, histogram_bins, counts));
+        } else if (vec) {
+            GEFEN_DISPATCH_S(grad_dtype, histogram_kernel<S, 32, true, false><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, histogram_bins, counts));
         } else {
-            GEFEN_DISPATCH_S(grad_dtype, histogram_kernel<S, 32, false><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, histogram_bins, counts));
+            GEFEN_DISPATCH_S(grad_dtype, histogram_kernel<S, 32, false, false><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, histogram_bins, counts));
         }
     } else {
         const int grid = persistent_grid(nb, 1, 6);
-        GEFEN_DISPATCH_S(grad_dtype, histogram_kernel<S, 256, false><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, histogram_bins, counts));
+        GEFEN_DISPATCH_S(grad_dtype, histogram_kernel<S, 256, false, false><<<grid, kThreads, 0, stream>>>(static_cast<const S*>(grad_flat), period, nb, histogram_bins, counts));
     }
     GEFEN_CHECK_CUDA(cudaGetLastError());
     return GEFEN_B200_OK;
