@@ -361,12 +361,12 @@ __device__ __forceinline__ LloydTables stage_lloyd_tables(const unsigned char* w
     return t;
 }
 
-// x * 2^24 as a two's-complement 64-bit integer (non-finite values, which only non-finite gradients produce,
-// count as 0 in the sum; their count is still taken).
-__device__ __forceinline__ unsigned long long lloyd_fixed(float x) {
+// (x + 1) * 2^24 rounded to an integer in [0, 2^25] for |x| <= 1 (non-finite values, which only non-finite
+// gradients produce, count as x = 0 in the sum; their count is still taken).
+__device__ __forceinline__ unsigned int lloyd_fixed(float x) {
     const float scaled = x * 16777216.0f;
-    const long long q = (fabsf(scaled) <= 16777216.0f) ? static_cast<long long>(__float2int_rn(scaled)) : 0ll;
-    return static_cast<unsigned long long>(q);
+    const int q = (fabsf(scaled) <= 16777216.0f) ? __float2int_rn(scaled) : 0;
+    return static_cast<unsigned int>(q + 16777216);
 }
 
 // E-step: per codebook entry, the sum of the normalised values assigned to it and their count
@@ -378,14 +378,34 @@ __global__ void __launch_bounds__(kThreads) lloyd_accumulate_kernel(const S* __r
                                                                     int k, float* __restrict__ sums,
                                                                     unsigned long long* __restrict__ counts) {
     __shared__ __align__(16) unsigned char tables[GEFEN_B200_CODEBOOK_WS_BYTES];
-    // Per-entry sums are kept in shared memory as 64-bit fixed point (x * 2^24, |x| <= 1): integer atomics
-    // instead of a compare-and-swap loop per float addition, no dependence on the order of the additions, and
-    // every value of magnitude 2^-1 or more is represented exactly (smaller ones to 2^-25 absolute).
-    __shared__ unsigned long long ssum[kMaxCodebook];
+    // Per-entry sums are kept in shared memory in fixed point, as the 64-bit sum of (x + 1) * 2^24 in two 32-bit
+    // words: float and 64-bit additions to shared memory are compare-and-swap loops, 32-bit integer ones are
+    // native. An element costs one add to the low word (whose returned old value tells a carry, which then
+    // goes to the high word: once per ~128 elements of an entry) and one to the count; the offset count * 2^24
+    // comes off at the flush. The sum does not depend on the order of the additions, values of magnitude 2^-1
+    // or more are exact and smaller ones are within 2^-25.
+    __shared__ unsigned int slo[kMaxCodebook];
+    __shared__ unsigned int shi[kMaxCodebook];
     __shared__ unsigned int scnt[kMaxCodebook];
     __shared__ float red[kWarps];
-    ssum[threadIdx.x] = 0ull;
+    slo[threadIdx.x] = 0u;
+    shi[threadIdx.x] = 0u;
     scnt[threadIdx.x] = 0u;
+    auto add = [&](int e, float x) {
+        const unsigned int v = lloyd_fixed(x);
+        const unsigned int old = atomicAdd(&slo[e], v);
+        if (old + v < old) atomicAdd(&shi[e], 1u);
+        atomicAdd(&scnt[e], 1u);
+    };
+    auto flush = [&]() {   // every thread of the CTA, between two __syncthreads
+        if (threadIdx.x < k && scnt[threadIdx.x]) {
+            const unsigned long long raw = (static_cast<unsigned long long>(shi[threadIdx.x]) << 32) | slo[threadIdx.x];
+            const long long fixed = static_cast<long long>(raw) - (static_cast<long long>(scnt[threadIdx.x]) << 24);
+            atomicAdd(&sums[threadIdx.x], static_cast<float>(static_cast<double>(fixed) * (1.0 / 16777216.0)));
+            atomicAdd(&counts[threadIdx.x], static_cast<unsigned long long>(scnt[threadIdx.x]));
+            slo[threadIdx.x] = shi[threadIdx.x] = scnt[threadIdx.x] = 0u;
+        }
+    };
     const LloydTables t = stage_lloyd_tables(ws, tables);
     const int lane = threadIdx.x & 31;
     const int tig = GROUP == 32 ? lane : static_cast<int>(threadIdx.x);
@@ -413,9 +433,7 @@ __global__ void __launch_bounds__(kThreads) lloyd_accumulate_kernel(const S* __r
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const float x = divide(f[i]);
-                    const int e = t.entry(x);
-                    atomicAdd(&ssum[e], lloyd_fixed(x));
-                    atomicAdd(&scnt[e], 1u);
+                    add(t.entry(x), x);
                 }
             }
         } else {
@@ -424,28 +442,19 @@ __global__ void __launch_bounds__(kThreads) lloyd_accumulate_kernel(const S* __r
                 const float v = ScalarIO<S>::load(gb + i);
                 float x = 0.0f;
                 if (absmax > 0.0f) x = v / absmax;
-                const int e = t.entry(x);
-                atomicAdd(&ssum[e], lloyd_fixed(x));
-                atomicAdd(&scnt[e], 1u);
+                add(t.entry(x), x);
             }
         }
         since_flush += static_cast<unsigned long long>(period);
-        if (GROUP > 32 && since_flush > 0x7fffffffull) {
+        if (GROUP > 32 && since_flush > 0x7fffffffull) {   // keep the 32-bit counts from wrapping
             __syncthreads();
-            if (threadIdx.x < k && scnt[threadIdx.x]) {
-                atomicAdd(&counts[threadIdx.x], static_cast<unsigned long long>(scnt[threadIdx.x]));
-                scnt[threadIdx.x] = 0u;
-            }
+            flush();
             __syncthreads();
             since_flush = 0;
         }
     }
     __syncthreads();
-    if (threadIdx.x < k) {
-        const double total = static_cast<double>(static_cast<long long>(ssum[threadIdx.x])) * (1.0 / 16777216.0);
-        atomicAdd(&sums[threadIdx.x], static_cast<float>(total));
-        atomicAdd(&counts[threadIdx.x], static_cast<unsigned long long>(scnt[threadIdx.x]));
-    }
+    flush();
 }
 
 // Logging MSE of assigning with the old codebook and reconstructing with the new one
