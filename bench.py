@@ -112,14 +112,21 @@ def build_model(cfg, device, limit_elems=None):
 
 
 # --------------------------------------------------------------------------- CPU arm (oracle port)
-def workload_config(args, cfg, world, n_tensors, total_elems, periods, by_period, algo_bytes):
-    """The `config` object of the JSON line: the same for the GPU arm and the reference arm."""
+def workload_config(args, cfg, world, n_tensors, total_elems):
+    """The `config` object of the JSON line: static facts of the workload only, so that the GPU arm and the
+    reference arm print the same object (what calibration finds goes into `periods`, beside it)."""
+    elem_bytes = 2 if cfg["dtype"] == torch.bfloat16 else 4
     return {"workload": args.workload, "optimizer": "Gefen(fused=True)", "lr": cfg["lr"],
             "weight_decay": cfg["wd"], "betas": [0.9, 0.999], "eps": 1e-8,
             "tensors": n_tensors, "elements": total_elems,
             "parallelism": "zero1-dp{}".format(world) if world > 1 else "single-gpu",
-            "l2": "inputs ({:.1f} GB per step) are larger than L2".format(algo_bytes / 1e9),
-            "periods": sorted(set(periods)), "elements_by_period": {str(k): by_period[k] for k in sorted(by_period)}}
+            "l2": "inputs ({:.1f} GB per step) are larger than L2".format(total_elems * (3 * elem_bytes + 2) / 1e9)}
+
+
+def periods_found(shapes, periods):
+    """What the calibration chose: the distinct periods and the elements under each."""
+    by_period = period_census(shapes, periods)
+    return {"distinct": sorted(set(periods)), "elements_by_period": {str(k): by_period[k] for k in sorted(by_period)}}
 
 
 def period_census(shapes, per_tensor):
@@ -129,7 +136,7 @@ def period_census(shapes, per_tensor):
     return by_period
 
 
-def cpu_port_run(cfg, steps: int, warmup: int, sample_elems):
+def cpu_port_run(cfg, steps: int, warmup: int, sample_elems, budget_s=None):
     """The CPU oracle's restatement of the reference step on the host cores (C with OpenMP, all
     threads): the oracle's own calibration (period search, histogram, exact-DP codebook), then
     `warmup` untimed and `steps` timed steady-state steps. sample_elems=None: the whole workload;
@@ -149,35 +156,39 @@ def cpu_port_run(cfg, steps: int, warmup: int, sample_elems):
         dt = time.perf_counter() - t0
         if i >= warmup:
             times.append(dt)
+            if budget_s is not None and sum(times) + dt > budget_s:   # the next step would overrun the budget
+                break
     periods = [st["automatic_period"] for st in opt.state]
     return {"ms": 1e3 * sum(times) / len(times), "shapes": shapes, "periods": periods, "calibration_s": calib_s,
             "elements": sum(workloads.numel(s) for _, s in shapes), "cores": os.cpu_count(), "timed_steps": len(times)}
 
 
-REFERENCE_ARM_MAX_STEPS = 3   # a CPU step of the 1.5 B set takes seconds: the arm times at most this many
+REFERENCE_ARM_BUDGET_S = 100.0   # a CPU step of the 1.5 B set takes seconds: the arm stops timing after this long
 
 
 def run_reference_arm(args, cfg, rank, world):
-    """`--impl reference`: the whole workload through the CPU port, nothing sampled or scaled."""
+    """`--impl reference`: the whole workload through the CPU port, nothing sampled or scaled. It times the
+    K steps it is asked for unless they would take longer than REFERENCE_ARM_BUDGET_S; `steps` of the line
+    is the number actually timed (`requested_steps` the number asked for)."""
     if rank != 0:
         return
     torch.set_num_threads(os.cpu_count() or 1)
-    timed_steps = max(1, min(args.steps, REFERENCE_ARM_MAX_STEPS))
-    run = cpu_port_run(cfg, timed_steps, 1, None)
+    run = cpu_port_run(cfg, max(1, args.steps), 1, None, budget_s=REFERENCE_ARM_BUDGET_S)
     shapes, periods = run["shapes"], run["periods"]
     elem_bytes = 2 if cfg["dtype"] == torch.bfloat16 else 4
     algo_bytes = workloads.step_bytes(shapes, periods, elem_bytes, elem_bytes)
     ms = run["ms"]
     line = {
         "impl": "reference", "metric": "optimizer_step_ms", "value": ms, "unit": "ms", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False,
+        "steps": run["timed_steps"], "warmup": 1, "requested_steps": args.steps, "requested_warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": False,
         "scaling": "strong", "vs_baseline": ms / PUBLISHED_LLAMA_1_5B_MS if args.workload == "llama_1_5b" else None,
         "dtype": "bf16" if cfg["dtype"] == torch.bfloat16 else "f32", "data": "synthetic",
-        "config": workload_config(args, cfg, world, len(shapes), run["elements"], periods, period_census(shapes, periods),
-                                  algo_bytes),
-        "timed_steps": run["timed_steps"], "timed_warmup": 1,
-        "timed_steps_note": "a CPU step of this workload takes seconds: {} steady-state steps are timed after one "
-                            "untimed step, whatever --steps asks for; nothing is sampled or scaled".format(run["timed_steps"]),
+        "config": workload_config(args, cfg, world, len(shapes), run["elements"]),
+        "periods": periods_found(shapes, periods), "algorithmic_bytes_per_step": algo_bytes,
+        "timed_steps_note": "a CPU step of this workload takes seconds: {} steady-state steps were timed after one "
+                            "untimed step (the arm stops after {:.0f} s of timed steps); nothing is sampled or scaled"
+                            .format(run["timed_steps"], REFERENCE_ARM_BUDGET_S),
         "calibration_s": run["calibration_s"],
         "cpu_baseline": {"value": ms, "unit": "ms", "cores": run["cores"], "kind": "port",
                          "sample": "the whole workload ({} elements, {} tensors): the C oracle with OpenMP, its own "
@@ -920,8 +931,8 @@ def main():
             "vs_baseline": ms / PUBLISHED_LLAMA_1_5B_MS if args.workload == "llama_1_5b" else None,
             "vs_baseline_note": "reference README: Gefen step 29 ms for Llama 3 1.5B, hardware not stated",
             "dtype": "bf16" if cfg["dtype"] == torch.bfloat16 else "f32", "data": "synthetic",
-            "config": workload_config(args, cfg, world, result["n_tensors"], result["total_elems"], periods,
-                                      period_census(shapes, periods), result["algo_bytes"]),
+            "config": workload_config(args, cfg, world, result["n_tensors"], result["total_elems"]),
+            "periods": periods_found(shapes, periods),
             "effective_hbm_gbs": eff_gbs, "effective_hbm_frac_of_{}".format(peak_kind): eff_gbs * (1 if world == 1 else 1.0 / world) / peak,
             "algorithmic_bytes_per_step": result["algo_bytes"],
             "calibration_first_step_ms": result["calibration_ms"],

@@ -181,14 +181,21 @@ class device_guard:
 # ------------------------------------------------------------------ codebook workspaces
 def codebook_workspace(codebook: torch.Tensor) -> torch.Tensor:
     """Device workspace (thresholds + lookup table) for `codebook`. It is kept on the tensor object
-    and rebuilt when the tensor is modified in place (its version counter moves) or reallocated."""
+    and rebuilt when the tensor is modified in place (its version counter moves) or reallocated. The
+    tables are built on the stream that is current at that moment; an event recorded behind the build makes
+    every later consumer on another stream wait for it."""
     tag = (codebook._version, codebook.data_ptr(), codebook.numel())
     hit = getattr(codebook, "_gefen_b200_ws", None)
+    stream = torch.cuda.current_stream(codebook.device)
     if hit is not None and hit[0] == tag:
+        if hit[3] != stream.cuda_stream:
+            stream.wait_event(hit[2])
         return hit[1]
     ws = torch.empty(CODEBOOK_WS_BYTES, dtype=torch.uint8, device=codebook.device)
     with device_guard(codebook.device):
         check(load().gefen_b200_codebook_prepare(ptr(codebook), codebook.numel(), ptr(ws),
                                                  current_stream(codebook.device)))
-    codebook._gefen_b200_ws = (tag, ws)
+    built = torch.cuda.Event()
+    built.record(stream)
+    codebook._gefen_b200_ws = (tag, ws, built, stream.cuda_stream)
     return ws

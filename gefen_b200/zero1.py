@@ -15,9 +15,15 @@ the gradients first. Two one-element all-reduces order the ranks around the step
 
 The reference has no communication code at all (its only distributed awareness is unwrapping
 DTensor shards, gefen.py:692-706); this module is the exchange step the data-parallel use of the
-optimizer needs. Two properties are kept so that N ranks reproduce one rank bit for bit:
+optimizer needs. Two properties are kept so that N ranks reproduce one rank bit for bit on the state
+and parameters of every piece, given the same reduced gradients and periods:
   * segments are cut at ROW boundaries of the 2-D tensors, so every partition block of the
-    optimizer (a run of `period` elements inside a row) lives on exactly one rank;
+    optimizer lives on exactly one rank whenever the period divides the row length (the periods
+    that row-scaled gradients give). The reference picks a tensor's period from the divisors of its
+    whole flattened length (partitioning.py:147, :253); a piece scores the divisors of ITS length, a
+    smaller candidate set, so a split tensor can come out with another period than one process would
+    choose. The largest piece decides, disagreements are kept in `period_mismatches` and a warning
+    names them;
   * the codebook is fitted from the histogram of ALL tensors: per-piece int64 histograms are
     gathered, pieces of one tensor are added exactly, and tensors are accumulated in float32 in
     parameter order, which is the single-process arithmetic (reference: gefen.py:331-347).
@@ -470,6 +476,12 @@ class Zero1Gefen:
                 if any(v[0] % period for v in votes):
                     period = math.gcd(*[v[2] for v in votes])
             chosen[t] = period
+        if self.period_mismatches and self.rank == 0:
+            import warnings
+
+            warnings.warn("Zero1Gefen: the pieces of {} tensor(s) voted for different periods ({}); the largest piece "
+                          "decided, a single process might choose otherwise".format(
+                              len(self.period_mismatches), ", ".join(n for n, _ in self.period_mismatches[:4])))
         flats = [(g.reshape(-1), chosen[pc.tensor]) for pc, g in zip(self.pieces, grads)]
         hist = self.ops.histograms(flats, HISTOGRAM_BINS)
         mine_h = {(pc.tensor, pc.row0): hist[i] for i, pc in enumerate(self.pieces)}

@@ -105,7 +105,8 @@ def test_config3_flat_large_properties(cuda_device, log2n):
 def test_config2_llama_layer_multi_tensor_equals_per_tensor(cuda_device):
     """bf16, weight decay: one multi-tensor fused launch over a Llama-1.5B layer plus an embedding
     slice must give bit-identical codes and magnitudes to stepping each tensor with the per-tensor
-    (reference-shaped) entry points, and parameters within one bf16 rounding of the fused second moment."""
+    (reference-shaped) entry points, and parameters within what one bf16 rounding of a block's second moment
+    can move them (observed: identical; bound 1e-4 relative L2, against the north-star's 1e-2)."""
     from gefen_b200 import Gefen
 
     shapes = [("embed", (8192, 2048))] + workloads.llama_1_5b()[1:10]
@@ -120,12 +121,15 @@ def test_config2_llama_layer_multi_tensor_equals_per_tensor(cuda_device):
         fused.step()
         per_tensor.step()
     assert torch.equal(fused._gefen_codebook, per_tensor._gefen_codebook)
+    worst = 0.0
     for pa, pb in zip(params_a, params_b):
         sa, sb = fused.state[pa], per_tensor.state[pb]
         assert sa["automatic_period"] == sb["automatic_period"]
         assert torch.equal(sa["m_codebook"], sb["m_codebook"])
         assert torch.equal(sa["m_magnitude"], sb["m_magnitude"])
-        assert rel_l2(pa.detach().float().cpu(), pb.detach().float().cpu()) <= 2e-3
+        err = rel_l2(pa.detach().float().cpu(), pb.detach().float().cpu())
+        worst = max(worst, err)
+        assert err <= 1e-4, "parameters differ by {:.3e} (relative L2)".format(err)
 
 
 def test_config4_llama_32b_layer_multi_tensor_equals_per_tensor(cuda_device):
@@ -146,11 +150,14 @@ def test_config4_llama_32b_layer_multi_tensor_equals_per_tensor(cuda_device):
         per_tensor.step()
     assert torch.equal(fused._gefen_codebook, per_tensor._gefen_codebook)
     periods = set()
+    worst = 0.0
     for pa, pb in zip(params_a, params_b):
         sa, sb = fused.state[pa], per_tensor.state[pb]
         periods.add(sa["automatic_period"])
         assert sa["automatic_period"] == sb["automatic_period"]
         assert torch.equal(sa["m_codebook"], sb["m_codebook"])
         assert torch.equal(sa["m_magnitude"], sb["m_magnitude"])
-        assert rel_l2(pa.detach().float().cpu(), pb.detach().float().cpu()) <= 2e-3
+        err = rel_l2(pa.detach().float().cpu(), pb.detach().float().cpu())
+        worst = max(worst, err)
+        assert err <= 1e-4, "parameters differ by {:.3e} (relative L2)".format(err)
     assert periods & {1664, 1120, 3328, 2240, 6656, 8960, 17920} or max(periods) > 1024
