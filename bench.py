@@ -872,7 +872,7 @@ def main():
     ap.add_argument("--cpu-sample-elems", type=int, default=62_000_000,
                     help="size of the CPU baseline's sample of the workload, in elements")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--e2e-buckets", type=int, default=8)
+    ap.add_argument("--e2e-buckets", type=int, default=16)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-reference-cuda", action="store_true", help="skip timing the reference's CUDA kernels")
     ap.add_argument("--no-muon", action="store_true", help="skip the GefenMuon summary of the default line")

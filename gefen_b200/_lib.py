@@ -179,15 +179,21 @@ class device_guard:
 
 
 # ------------------------------------------------------------------ codebook workspaces
+_WORKSPACES = {}   # id(codebook tensor) -> (tag, workspace, event, stream handle, weak reference)
+
+
 def codebook_workspace(codebook: torch.Tensor) -> torch.Tensor:
-    """Device workspace (thresholds + lookup table) for `codebook`. It is kept on the tensor object
-    and rebuilt when the tensor is modified in place (its version counter moves) or reallocated. The
-    tables are built on the stream that is current at that moment; an event recorded behind the build makes
-    every later consumer on another stream wait for it."""
+    """Device workspace (thresholds + lookup table) for `codebook`. It is kept for as long as the tensor
+    object lives and rebuilt when the tensor is modified in place (its version counter moves) or
+    reallocated. The tables are built on the stream that is current at that moment; an event recorded behind
+    the build makes every later consumer on another stream wait for it."""
+    import weakref
+
+    key = id(codebook)
     tag = (codebook._version, codebook.data_ptr(), codebook.numel())
-    hit = getattr(codebook, "_gefen_b200_ws", None)
+    hit = _WORKSPACES.get(key)
     stream = torch.cuda.current_stream(codebook.device)
-    if hit is not None and hit[0] == tag:
+    if hit is not None and hit[0] == tag and hit[4]() is codebook:
         if hit[3] != stream.cuda_stream:
             stream.wait_event(hit[2])
         return hit[1]
@@ -197,5 +203,5 @@ def codebook_workspace(codebook: torch.Tensor) -> torch.Tensor:
                                                  current_stream(codebook.device)))
     built = torch.cuda.Event()
     built.record(stream)
-    codebook._gefen_b200_ws = (tag, ws, built, stream.cuda_stream)
+    _WORKSPACES[key] = (tag, ws, built, stream.cuda_stream, weakref.ref(codebook, lambda _ref, k=key: _WORKSPACES.pop(k, None)))
     return ws

@@ -137,40 +137,7 @@ __global__ void __launch_bounds__(kThreads) histogram_kernel(const S* __restrict
 
     for (long long b = group0; b < num_blocks; b += stride) {
         const S* gb = g + b * period;
-        if (VEC && sizeof(S) == 2 && period <= 2048) {
-            // 2-byte elements, at most eight chunks per lane: the block stays in registers between the absmax
-            // and the binning, so it is read exactly once
-            const int nchunks = static_cast<int>(period >> 3);
-            uint4 raw[8];
-            float m = 0.0f;
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int c = lane + 32 * u;
-                if (c < nchunks) raw[u] = *reinterpret_cast<const uint4*>(gb + 8 * c);
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int c = lane + 32 * u;
-                if (c < nchunks) m = absmax8<S>(reinterpret_cast<const S*>(&raw[u]), m);
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-            const BlockDivider divide(m);
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int c = lane + 32 * u;
-                if (c < nchunks) {
-                    float f[8];
-                    load8<S>(reinterpret_cast<const S*>(&raw[u]), f);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float x = divide(f[i]);
-                        const float y = POW2 ? fmaf(x, scale, scale) : (x + 1.0f) * scale;
-                        atomicAdd(&hist[__float2uint_rz(y)], 1u);
-                    }
-                }
-            }
-        } else if (VEC) {   // GROUP == 32, period a multiple of 8, 16-byte aligned blocks
+        if (VEC) {   // GROUP == 32, period a multiple of 8, 16-byte aligned blocks
             const int nchunks = static_cast<int>(period >> 3);
             float m = 0.0f;
             for (int c = lane; c < nchunks; c += 32) m = absmax8<S>(gb + 8 * c, m);

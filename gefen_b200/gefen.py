@@ -428,10 +428,11 @@ class Gefen(torch.optim.Optimizer):
                 work.append((group, name, p, local_p, grad))
         return work
 
-    def _step_tables(self, work, muon: bool = False):
+    def _step_tables(self, work, muon: bool = False, ranges=None):
         """Builds (or reuses) the launch tables for `work`. Static columns are cached; the pointer
-        and scalar columns are refreshed by the caller every step."""
-        key = (muon,) + tuple(id(item[2]) for item in work)
+        and scalar columns are refreshed by the caller every step. ranges: {id(param): (first block, end
+        block)} restricts a tensor's row to a run of its blocks (blocks are independent of each other)."""
+        key = (muon,) + tuple((id(item[2]),) + tuple((ranges or {}).get(id(item[2]), ())) for item in work)
         plan = self._plans.get(key)
         if plan is not None:
             self._plan = plan
@@ -462,19 +463,23 @@ class Gefen(torch.optim.Optimizer):
                 else:
                     flags |= _lib.STEP_FUSE_VMEAN
                     block = period
-                rows[r]["codes"] = state["m_codebook"].data_ptr()
-                rows[r]["mag"] = state["m_magnitude"].data_ptr()
+                b0, b1 = (ranges or {}).get(id(p), (0, numel // block))
+                if (b0, b1) != (0, numel // block) and (period == 1 or muon):
+                    raise ValueError("block ranges are for Gefen tensors with a period above 1, got {}".format(name))
+                state_bytes = state["m_magnitude"].element_size()
+                rows[r]["codes"] = state["m_codebook"].data_ptr() + b0 * block
+                rows[r]["mag"] = state["m_magnitude"].data_ptr() + b0 * state_bytes
                 rows[r]["mag_dtype"] = _lib.dtype_tag(state["m_magnitude"].dtype)
                 if muon:
                     rows[r]["v_dtype"] = _lib.F32
                 else:
-                    rows[r]["v"] = state["vmean"].data_ptr()
+                    rows[r]["v"] = state["vmean"].data_ptr() + (b0 * state["vmean"].element_size() if period != 1 else 0)
                     rows[r]["v_dtype"] = _lib.dtype_tag(state["vmean"].dtype)
                 rows[r]["period"] = block
-                rows[r]["num_blocks"] = numel // block
+                rows[r]["num_blocks"] = b1 - b0
                 rows[r]["flags"] = flags
-                rows[r]["p"] = local_p.data_ptr()
-                rows[r]["g"] = grad.data_ptr()
+                rows[r]["p"] = local_p.data_ptr() + b0 * block * local_p.element_size()
+                rows[r]["g"] = grad.data_ptr() + b0 * block * grad.element_size()
             classes = [lib.gefen_b200_step_tensor_class(rows[r:r + 1].ctypes.data, tag) for r in range(len(idxs))]
             order = sorted(range(len(idxs)), key=lambda r: classes[r])
             rows = np.ascontiguousarray(rows[order])
@@ -485,15 +490,22 @@ class Gefen(torch.optim.Optimizer):
                 "static_flags": rows["flags"].copy(),
                 "entries": [idxs[r] for r in order],
                 "classes": [classes[r] for r in order],
+                # byte offset of each row's first element in its tensor (0 unless a block range was given)
+                "offsets": [int((ranges or {}).get(id(work[idxs[r]][2]), (0, 0))[0]) * int(rows[i]["period"])
+                            for i, r in enumerate(order)],
                 "device_table": torch.empty(rows.nbytes, dtype=torch.uint8, device=device),
             })
         plan.key = key
         plan.tables = tables
         return tables
 
-    def _step_multi_tensor(self, only=None) -> None:
+    def _step_multi_tensor(self, only=None, ranges=None, advance=None) -> None:
         """One multi-tensor launch per dtype and kernel class over every parameter with a gradient,
-        or over those whose id() is in `only` (callers that stream the model through in pieces)."""
+        or over those whose id() is in `only` (callers that stream the model through in pieces). Such a
+        caller may also cut a tensor into runs of blocks: ranges = {id(param): (first block, end block)}
+        steps only those blocks, and `advance` (a set of ids) names the tensors whose step counter moves
+        in this call (the call that takes a tensor's first run); the other runs of the same optimizer step
+        use the counter as that call left it."""
         work = self._collect()
         if only is not None:
             work = [item for item in work if id(item[2]) in only]
@@ -512,7 +524,7 @@ class Gefen(torch.optim.Optimizer):
             work[i] = (group, name, p, fused_p, grad)
         lib = _lib.load()
         ws = _lib.codebook_workspace(self._gefen_codebook)
-        for table in self._step_tables(work):
+        for table in self._step_tables(work, ranges=ranges):
             rows = table["rows"]
             n = len(table["entries"])
             cols = {k: [0.0] * n for k in ("beta1", "beta2", "lr", "bc1", "bc2", "eps", "wd_mul")}
@@ -520,7 +532,8 @@ class Gefen(torch.optim.Optimizer):
             for r, idx in enumerate(table["entries"]):
                 group, name, p, fused_p, grad = work[idx]
                 state = self.state[p]
-                state["step"] += 1
+                if advance is None or id(p) in advance:
+                    state["step"] += 1
                 beta1, beta2, lr, wd = group["beta1"], group["beta2"], float(group["lr"]), group["weight_decay"]
                 cols["beta1"][r] = beta1
                 cols["beta2"][r] = beta2
@@ -533,8 +546,8 @@ class Gefen(torch.optim.Optimizer):
                     flags[r] |= _lib.STEP_WEIGHT_DECAY
                 else:
                     cols["wd_mul"][r] = 1.0
-                p_ptr[r] = fused_p.data_ptr()
-                g_ptr[r] = grad.data_ptr()
+                p_ptr[r] = fused_p.data_ptr() + table["offsets"][r] * fused_p.element_size()
+                g_ptr[r] = grad.data_ptr() + table["offsets"][r] * grad.element_size()
             for k, v in cols.items():
                 rows[k] = v
             rows["p"] = p_ptr

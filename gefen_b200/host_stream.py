@@ -3,7 +3,8 @@ memory every step (optimizer state and a working copy of the parameters stay on 
 
 The reference optimizer only sees tensors where they already live (gefen.py:1399-1420); moving them is
 its caller's business, done whole: all gradients in, step, all parameters out. Here the model is cut
-into buckets of consecutive parameters and three streams work on different buckets at once:
+into buckets of about equal bytes (consecutive parameters; a large tensor is cut between blocks, which
+the step treats independently) and three streams work on different buckets at once:
 
     copy-in stream   : gradients of bucket k+1  host -> device
     compute stream   : Gefen step of bucket k    (one multi-tensor launch per dtype and kernel class)
@@ -45,28 +46,59 @@ class HostStreamedGefen:
         self.host_grads = list(host_grads)
         self.host_params = list(host_params)
         self.device = self.params[0].device
-        # consecutive parameters, about equal bytes per bucket
-        total = sum(p.numel() * p.element_size() for p in self.params)
-        target = max(1, total // max(1, buckets))
-        self.buckets: List[List[int]] = [[]]
-        acc = 0
-        for i, p in enumerate(self.params):
-            if acc >= target and len(self.buckets) < buckets:
-                self.buckets.append([])
-                acc = 0
-            self.buckets[-1].append(i)
-            acc += p.numel() * p.element_size()
-        self._ids = [set(id(self.params[i]) for i in b) for b in self.buckets]
+        self.n_buckets = max(1, int(buckets))
+        self.buckets = None          # built after calibration: the cut points are block boundaries
         self._in = torch.cuda.Stream(self.device)
         self._out = torch.cuda.Stream(self.device)
 
-    def _copy_in(self, bucket: List[int]) -> None:
-        for i in bucket:
-            self.params[i].grad.copy_(self.host_grads[i], non_blocking=True)
+    def _build_buckets(self) -> None:
+        """Cuts the model, in parameter order, into `n_buckets` runs of about equal bytes. A tensor larger
+        than what is left of a bucket is cut at a block boundary (the blocks of a tensor are independent in
+        the step), so that no bucket is much larger than the others: the first bucket's copy-in and the last
+        bucket's copy-out are the parts of a step that nothing overlaps. Period-1 tensors (tiny) stay whole.
+        A bucket is a list of (parameter index, first block, end block, whole tensor?)."""
+        opt = self.opt
+        sizes = [p.numel() * p.element_size() for p in self.params]
+        target = max(1, sum(sizes) // self.n_buckets)
+        buckets, cur, room = [], [], target
+        for i, p in enumerate(self.params):
+            period = int(opt.state[p]["automatic_period"])
+            nb = p.numel() // period if period > 1 else 1
+            block_bytes = (period if period > 1 else p.numel()) * p.element_size()
+            b0 = 0
+            while b0 < nb:
+                fit = max(1, room // block_bytes) if period > 1 else nb
+                b1 = min(nb, b0 + fit)
+                if period > 1 and nb - b1 < max(1, nb // 64):   # do not leave a sliver for the next bucket
+                    b1 = nb
+                cur.append((i, b0, b1, b0 == 0 and b1 == nb))
+                room -= (b1 - b0) * block_bytes
+                b0 = b1
+                if room <= 0 and len(buckets) < self.n_buckets - 1:
+                    buckets.append(cur)
+                    cur, room = [], target
+        if cur:
+            buckets.append(cur)
+        self.buckets = buckets
+        self._ids = [set(id(self.params[i]) for i, _, _, _ in b) for b in buckets]
+        self._ranges = [{id(self.params[i]): (b0, b1) for i, b0, b1, whole in b if not whole} for b in buckets]
+        self._advance = [set(id(self.params[i]) for i, b0, _, _ in b if b0 == 0) for b in buckets]
 
-    def _copy_out(self, bucket: List[int]) -> None:
-        for i in bucket:
-            self.host_params[i].copy_(self.params[i].detach(), non_blocking=True)
+    def _span(self, i: int, b0: int, b1: int, whole: bool):
+        if whole:
+            return slice(None)
+        period = int(self.opt.state[self.params[i]]["automatic_period"])
+        return slice(b0 * period, b1 * period)
+
+    def _copy_in(self, bucket) -> None:
+        for i, b0, b1, whole in bucket:
+            span = self._span(i, b0, b1, whole)
+            self.params[i].grad.view(-1)[span].copy_(self.host_grads[i].view(-1)[span], non_blocking=True)
+
+    def _copy_out(self, bucket) -> None:
+        for i, b0, b1, whole in bucket:
+            span = self._span(i, b0, b1, whole)
+            self.host_params[i].view(-1)[span].copy_(self.params[i].detach().view(-1)[span], non_blocking=True)
 
     @torch.no_grad()
     def step(self) -> None:
@@ -76,12 +108,14 @@ class HostStreamedGefen:
         cur = torch.cuda.current_stream(self.device)
         if opt._gefen_codebook is None:
             # the calibrating step needs every gradient at once: whole model in, step, whole model out
-            for b in self.buckets:
-                self._copy_in(b)
+            for p, hg in zip(self.params, self.host_grads):
+                p.grad.copy_(hg, non_blocking=True)
             opt.step()
-            for b in self.buckets:
-                self._copy_out(b)
+            for p, hp in zip(self.params, self.host_params):
+                hp.copy_(p.detach(), non_blocking=True)
             return
+        if self.buckets is None:
+            self._build_buckets()
         opt._maybe_refresh_gefen_codebook()
         start = torch.cuda.Event()
         start.record(cur)
@@ -96,7 +130,7 @@ class HostStreamedGefen:
                 arrived.append(e)
         for k, b in enumerate(self.buckets):
             cur.wait_event(arrived[k])
-            opt._step_multi_tensor(only=self._ids[k])
+            opt._step_multi_tensor(only=self._ids[k], ranges=self._ranges[k], advance=self._advance[k])
             done = torch.cuda.Event()
             done.record(cur)
             with torch.cuda.stream(self._out):

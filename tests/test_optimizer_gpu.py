@@ -153,7 +153,8 @@ def test_host_streamed_step_equals_plain_step(cuda_device):
     three streams: same results as copying everything, stepping, copying everything back."""
     from gefen_b200 import Gefen, HostStreamedGefen
 
-    shapes = [(64, 512), (2048,), (96, 768), (40, 2048), (33, 24), (128, 1024), (7,), (256, 256)]
+    # (the 600 x 2048 tensor is larger than a bucket: it is cut between blocks and spread over several)
+    shapes = [(64, 512), (2048,), (96, 768), (600, 2048), (33, 24), (128, 1024), (7,), (256, 256)]
 
     def build():
         params = [torch.nn.Parameter(make_param(s, 3, i, torch.bfloat16).to(cuda_device)) for i, s in enumerate(shapes)]
@@ -165,8 +166,7 @@ def test_host_streamed_step_equals_plain_step(cuda_device):
     stream_params, streamed_opt = build()
     host_g = [torch.empty(s, dtype=torch.bfloat16).pin_memory() for s in shapes]
     host_p = [torch.empty(s, dtype=torch.bfloat16).pin_memory() for s in shapes]
-    streamed = HostStreamedGefen(streamed_opt, host_g, host_p, buckets=3)
-    assert len(streamed.buckets) == 3 and sorted(i for b in streamed.buckets for i in b) == list(range(len(shapes)))
+    streamed = HostStreamedGefen(streamed_opt, host_g, host_p, buckets=4)
     for step in range(4):
         grads = [make_grad(s, 3, i, step, torch.bfloat16) for i, s in enumerate(shapes)]
         for p, g, h in zip(plain_params, grads, host_g):
@@ -180,7 +180,20 @@ def test_host_streamed_step_equals_plain_step(cuda_device):
             assert torch.equal(h, p.detach().cpu())
     for p, q in zip(plain_params, stream_params):
         assert torch.equal(plain.state[p]["m_codebook"], streamed_opt.state[q]["m_codebook"])
+        assert torch.equal(plain.state[p]["vmean"], streamed_opt.state[q]["vmean"])
+        assert plain.state[p]["step"] == streamed_opt.state[q]["step"] == 4
     assert plain._gefen_global_step == streamed_opt._gefen_global_step == 4
+    # the buckets cover every block of every tensor exactly once, and the large tensor is cut
+    assert len(streamed.buckets) == 4
+    covered = {}
+    for bucket in streamed.buckets:
+        for i, b0, b1, whole in bucket:
+            covered.setdefault(i, []).append((b0, b1))
+    assert sorted(covered) == list(range(len(shapes)))
+    for i, runs in covered.items():
+        runs.sort()
+        assert runs[0][0] == 0 and all(a[1] == b[0] for a, b in zip(runs, runs[1:]))
+    assert len(covered[3]) >= 2
 
 
 class _ShardedParam(torch.nn.Parameter):
