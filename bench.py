@@ -418,7 +418,10 @@ def run_gpu_arm(args, cfg, rank, world, local_rank):
         e2e_step()
         e2e_ms = timed(e2e_step, max(2, min(args.steps, 5)))
         nbytes = sum(g.numel() * g.element_size() for g in grads)
-        e2e = {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
+        e2e = {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
+               "buckets": len(streamed.buckets or []),
+               # after the timed steps the host copies must be the device's parameters, element for element
+               "host_params_match_device": all(torch.equal(h, p.detach().cpu()) for h, p in zip(host_p, params))}
         del streamed, host_g, host_p
 
     # ---- the reference's own CUDA kernels on the same tensors, in the reference's launch order
@@ -872,7 +875,7 @@ def main():
     ap.add_argument("--cpu-sample-elems", type=int, default=62_000_000,
                     help="size of the CPU baseline's sample of the workload, in elements")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--e2e-buckets", type=int, default=16)
+    ap.add_argument("--e2e-buckets", type=int, default=32)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-reference-cuda", action="store_true", help="skip timing the reference's CUDA kernels")
     ap.add_argument("--no-muon", action="store_true", help="skip the GefenMuon summary of the default line")

@@ -437,7 +437,7 @@ class Gefen(torch.optim.Optimizer):
         if plan is not None:
             self._plan = plan
             return plan.tables
-        if len(self._plans) >= 64:   # callers that keep changing the set of tensors: start over
+        if len(self._plans) >= 512:   # callers that keep changing the set of tensors: start over
             self._plans.clear()
         plan = self._plans[key] = self._plan = _StepPlan()
         lib = _lib.load()

@@ -23,6 +23,37 @@ import torch
 from .gefen import Gefen
 
 
+def cut_buckets(numels, element_sizes, periods, n_buckets):
+    """Cuts a model, in parameter order, into at most `n_buckets` runs of about equal bytes. A tensor larger
+    than what is left of a bucket is cut at a block boundary (the blocks of a tensor are independent in
+    the step), so that no bucket is much larger than the others: the first bucket's copy-in and the last
+    bucket's copy-out are the parts of a step that nothing overlaps. Period-1 tensors (tiny) stay whole.
+    Returns a list of buckets; a bucket is a list of (parameter index, first block, end block, whole
+    tensor?) in which a parameter appears at most once."""
+    sizes = [n * e for n, e in zip(numels, element_sizes)]
+    target = max(1, sum(sizes) // max(1, n_buckets))
+    buckets, cur, room = [], [], target
+    for i, (numel, esize, period) in enumerate(zip(numels, element_sizes, periods)):
+        nb = numel // period if period > 1 else 1
+        block_bytes = (period if period > 1 else numel) * esize
+        b0 = 0
+        while b0 < nb:
+            last = len(buckets) >= n_buckets - 1        # the last bucket takes all that is left
+            fit = nb if (period <= 1 or last) else max(1, -(-room // block_bytes))   # rounds up: the bucket closes
+            b1 = min(nb, b0 + fit)
+            if period > 1 and nb - b1 < max(1, nb // 64):   # do not leave a sliver for the next bucket
+                b1 = nb
+            cur.append((i, b0, b1, b0 == 0 and b1 == nb))
+            room -= (b1 - b0) * block_bytes
+            b0 = b1
+            if room <= 0 and not last:
+                buckets.append(cur)
+                cur, room = [], target
+    if cur:
+        buckets.append(cur)
+    return buckets
+
+
 class HostStreamedGefen:
     """optimizer: a `Gefen(fused=True)` over CUDA parameters that have `.grad` tensors allocated.
     host_grads / host_params: pinned host tensors, one per optimizer parameter, in the order of
@@ -52,34 +83,10 @@ class HostStreamedGefen:
         self._out = torch.cuda.Stream(self.device)
 
     def _build_buckets(self) -> None:
-        """Cuts the model, in parameter order, into `n_buckets` runs of about equal bytes. A tensor larger
-        than what is left of a bucket is cut at a block boundary (the blocks of a tensor are independent in
-        the step), so that no bucket is much larger than the others: the first bucket's copy-in and the last
-        bucket's copy-out are the parts of a step that nothing overlaps. Period-1 tensors (tiny) stay whole.
-        A bucket is a list of (parameter index, first block, end block, whole tensor?)."""
-        opt = self.opt
-        sizes = [p.numel() * p.element_size() for p in self.params]
-        target = max(1, sum(sizes) // self.n_buckets)
-        buckets, cur, room = [], [], target
-        for i, p in enumerate(self.params):
-            period = int(opt.state[p]["automatic_period"])
-            nb = p.numel() // period if period > 1 else 1
-            block_bytes = (period if period > 1 else p.numel()) * p.element_size()
-            b0 = 0
-            while b0 < nb:
-                fit = max(1, room // block_bytes) if period > 1 else nb
-                b1 = min(nb, b0 + fit)
-                if period > 1 and nb - b1 < max(1, nb // 64):   # do not leave a sliver for the next bucket
-                    b1 = nb
-                cur.append((i, b0, b1, b0 == 0 and b1 == nb))
-                room -= (b1 - b0) * block_bytes
-                b0 = b1
-                if room <= 0 and len(buckets) < self.n_buckets - 1:
-                    buckets.append(cur)
-                    cur, room = [], target
-        if cur:
-            buckets.append(cur)
-        self.buckets = buckets
+        periods = [int(self.opt.state[p]["automatic_period"]) for p in self.params]
+        self.buckets = cut_buckets([p.numel() for p in self.params], [p.element_size() for p in self.params],
+                                   periods, self.n_buckets)
+        buckets = self.buckets
         self._ids = [set(id(self.params[i]) for i, _, _, _ in b) for b in buckets]
         self._ranges = [{id(self.params[i]): (b0, b1) for i, b0, b1, whole in b if not whole} for b in buckets]
         self._advance = [set(id(self.params[i]) for i, b0, _, _ in b if b0 == 0) for b in buckets]
