@@ -302,6 +302,19 @@ __device__ __forceinline__ void staged_momenta(const float4* stage_a, const floa
 }
 
 // --------------------------------------------------------------------------- fast path
+// lut_query_fast with the table's shared-memory address folded into the rounding constant: the low mantissa
+// bits of fma(x, 16384, magic) are then the address of x's table entry itself (the address is a multiple of
+// eight, so the cell, the value with its low three bits cleared, is the same one) and the query needs no add.
+__device__ __forceinline__ float lut_magic(const unsigned char* lut) {
+    return 12582912.0f + 16384.0f + static_cast<float>(static_cast<uint32_t>(__cvta_generic_to_shared(lut)));
+}
+__device__ __forceinline__ uint32_t lut_query_shared(float x, float magic) {
+    const uint32_t addr = __float_as_uint(fmaf(x, 16384.0f, magic)) & 0x3FFF8u;
+    uint32_t thr_bits, below;
+    asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(thr_bits), "=r"(below) : "r"(addr));
+    return below + (x > __uint_as_float(thr_bits) ? 1u : 0u);
+}
+
 // Lanes that share one block, a power of two, so that a warp works on 32 / lanes blocks at once. Blocks of
 // up to 256 elements: the smallest power of two that covers the block's chunks (one chunk per lane). Longer
 // blocks: about eight chunks per lane, as in a 2048-element block, so that the per-block work (reductions,
@@ -459,6 +472,71 @@ __device__ __forceinline__ void reduce_pass(const StepLaunch& L, const S* g_blk,
     }
 }
 
+// The re-encode and update loop of the common case (finite block, Gefen update of the parameters) with
+// everything that is fixed per launch or per tensor decided at compile time, so that the loop body carries no
+// branch but the rare one into the exact quantiser: WD = the decoupled weight decay of the reference's
+// separate multiply, STORE = 0 this GPU's copy only, 1 peer stores as well, 2 one multicast store.
+// The parameters of the next chunk are fetched while this one is encoded.
+template <typename S, bool WD, int STORE>
+__device__ __forceinline__ void second_pass_common(const StepLaunch& L, const SmemView& s, const float* rep,
+                                                   const float4* stage_a, const float4* stage_b, uint2* codes_out,
+                                                   S* p_blk, Chunk<S> pnext, int lane, int LANES, int nchunks,
+                                                   float absmax, float rinv, float step, float lr, float wd_mul) {
+    const float neg_step = -step;
+    const float magic = lut_magic(s.lut);
+    for (int c = lane; c < nchunks; c += LANES) {
+        Chunk<S> praw = pnext;
+        if (c + LANES < nchunks) pnext.load(p_blk, c + LANES);
+        float m[8];
+        staged_momenta(stage_a, stage_b, c, m);
+        uint32_t code[8];
+        uint32_t any = 0u;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float x = div_by_block_constant(m[i], absmax, rinv);
+            code[i] = lut_query_shared(x, magic);
+            any |= code[i];
+        }
+        if (any & kLutSlowBit) {   // rare: a cell with two thresholds, or values above the last entry
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (code[i] & kLutSlowBit) {
+                    const float x = div_by_block_constant(m[i], absmax, rinv);
+                    code[i] = static_cast<uint32_t>(entry_exact(x, s.thr, s.cb, s.k));
+                }
+            }
+        }
+        uint2 cw;
+        cw.x = __byte_perm(__byte_perm(code[0], code[1], 0x0040), __byte_perm(code[2], code[3], 0x0040), 0x5410);
+        cw.y = __byte_perm(__byte_perm(code[4], code[5], 0x0040), __byte_perm(code[6], code[7], 0x0040), 0x5410);
+        codes_out[c] = cw;
+        float pv[8];
+        praw.unpack(pv);
+        if (WD) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) pv[i] *= wd_mul;
+            Chunk<S> rounded;       // the separate multiply of the reference rounds to the parameter dtype
+            rounded.pack(pv);
+            rounded.unpack(pv);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float q = rep[code[i] * kRepCopies] * absmax;
+            pv[i] = fmaf(q * neg_step, lr, pv[i]);   // = fma(-(q * step), lr, p)
+        }
+        praw.pack(pv);
+        if (STORE == 2) {
+            praw.store_all(peer_ptr(p_blk, L.param_mc_delta), c);   // every rank's copy, this one included
+        } else {
+            praw.store(p_blk, c);
+            if (STORE == 1) {
+                const int n_peers = L.n_peers;
+                for (int r = 0; r < n_peers; ++r) praw.store(peer_ptr(p_blk, L.peer_delta[r]), c);
+            }
+        }
+    }
+}
+
 // One warp, one unit: 32 / LANES consecutive blocks of t.period = 8 * nchunks elements, LANES lanes
 // each (LANES = lanes_per_block(t.period), uniform over the warp; FULL fixes it to 32 at compile
 // time, for blocks of more than 1024 elements). A block's slice of `stage` holds period floats: the first halves of all chunks, then the
@@ -580,6 +658,22 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
 
     // ---- re-encode and update; the parameters of the next chunk are fetched while this one is encoded
     if (!kEarlyParams && load_p && lane < nchunks) pnext.load(p_blk, lane);
+    // The common case takes the loop that was compiled for it (the conditions are uniform over the warp: they
+    // come from the launch and the tensor's descriptor, and a warp's blocks go one way together).
+    if (__all_sync(0xffffffffu, fastdiv || !valid) && !muon && do_update) {
+        const int store = param_mc != 0 ? 2 : (n_peers > 0 ? 1 : 0);
+#define GEFEN_SECOND_PASS(WD_, STORE_)                                                                                      \
+    second_pass_common<S, WD_, STORE_>(L, s, rep, stage_a, stage_b, codes_out, p_blk, pnext, lane, LANES, nchunks, absmax, \
+                                       rinv, step, lr, wd_mul)
+        if (store == 0) { if (wd) GEFEN_SECOND_PASS(true, 0); else GEFEN_SECOND_PASS(false, 0); }
+        else if (store == 1) { if (wd) GEFEN_SECOND_PASS(true, 1); else GEFEN_SECOND_PASS(false, 1); }
+        else { if (wd) GEFEN_SECOND_PASS(true, 2); else GEFEN_SECOND_PASS(false, 2); }
+#undef GEFEN_SECOND_PASS
+        __syncwarp();  // the staging slice is free for this warp's next block
+        return;
+    }
+    // Everything else (GefenMuon's momentum, lr == 0, blocks that are all zero or hold NaN or Inf, magnitudes
+    // outside the range of the reciprocal): the general loop.
     for (int c = lane; c < nchunks; c += LANES) {
         Chunk<S> praw = pnext;
         if (load_p && c + LANES < nchunks) pnext.load(p_blk, c + LANES);
