@@ -10,8 +10,12 @@ gradient chunk arrives with one `multimem.ld_reduce` (the switch adds the ranks'
 updated parameter chunk leaves with one `multimem.st` (the switch delivers it to every copy): each
 rank pulls 1/N of the gradient bytes and pushes 1/N of the parameter bytes that the unicast
 collectives move, and the two directions of the links are busy at the same time inside one kernel.
-Without multicast the kernels store to every peer copy (plain peer stores) and NCCL reduce-scatters
-the gradients first. Two one-element all-reduces order the ranks around the step.
+Without multicast (two or three ranks, where the switch's loop back to the sender costs more than it saves)
+the kernels store to every peer copy (plain peer stores), and the gradients reach their owners by
+device-to-device copies: every rank pushes the segments it does not own into a receive buffer on their
+owners, bucket by bucket on a side stream, and the step kernels sum the local copies in rank order while
+they read them, taking bucket k while bucket k + 1 is on the wire. Where the receive buffer ((N-1)/N of one
+buffer) does not fit, NCCL reduce-scatters the gradients first. One-element all-reduces order the ranks.
 
 The reference has no communication code at all (its only distributed awareness is unwrapping
 DTensor shards, gefen.py:692-706); this module is the exchange step the data-parallel use of the
@@ -223,7 +227,7 @@ class Zero1Gefen:
     def __init__(self, named_params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, *, group=None,
                  ops=None, average_gradients: bool = True, fused_all_gather: Optional[bool] = None,
                  fused_reduce_scatter: Optional[bool] = None, multicast: Optional[bool] = None, device=None,
-                 dtype=None):
+                 dtype=None, push_reduce_scatter: Optional[bool] = None):
         self.group = group
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -281,6 +285,14 @@ class Zero1Gefen:
         use_grad_srcs = grad_ptrs is not None and (self._grad_mc_delta != 0 or peer_rs)
         self._grad_deltas = np.array([grad_ptrs[r] - grad_ptrs[self.rank] for r in range(self.world)], dtype=np.int64) \
             if use_grad_srcs else None
+        # Two or three ranks (no multicast): instead of NCCL's reduce-scatter, every rank pushes the segments it
+        # does not own into a receive buffer on their owners with plain device-to-device copies (the copy
+        # engines, at the full peer-copy rate), and the step kernels sum the local copies in rank order while
+        # they read them. Costs (N-1)/N of one buffer in memory; off where that is too much.
+        self._recv = None
+        self._push_views = []
+        if self._grad_deltas is None and grad_ptrs is not None and fused_reduce_scatter is None:
+            self._setup_push(push_reduce_scatter, grad_ptrs)
         with torch.no_grad():
             for t, (n, p) in enumerate(self.named):
                 off = self.layout.tensor_offset[t]
@@ -322,6 +334,49 @@ class Zero1Gefen:
 
     def _make_layout(self, shapes):
         return FlatLayout(shapes, self.world)
+
+    def _setup_push(self, requested: Optional[bool], grad_ptrs) -> None:
+        """Receive buffer of the pushed reduce-scatter: slot k of rank q holds the copy of q's segment that the
+        k-th other rank (rank order) computed. All ranks take the same decision."""
+        import os
+
+        env = os.environ.get("GEFEN_B200_ZERO1_PUSH_RS", "auto")
+        want = requested if requested is not None else (env != "0")
+        seg = self.layout.segment
+        nbytes = (self.world - 1) * seg * self.flat_grad.element_size()
+        if requested is None and env == "auto":
+            total_memory = torch.cuda.get_device_properties(self.device).total_memory
+            want = self.world <= 3 and nbytes * 6 <= total_memory and torch.cuda.mem_get_info(self.device)[0] > nbytes + (8 << 30)
+        votes = self._gather_objects(bool(want))
+        if not all(votes):
+            return
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            group = self.group if self.group is not None else dist.group.WORLD
+            recv = symm_mem.empty((self.world - 1) * seg, dtype=self.dtype, device=self.device)
+            handle = symm_mem.rendezvous(recv, group)
+            views = []
+            for k in range(1, self.world):   # ring order: concurrent ranks write to different GPUs
+                q = (self.rank + k) % self.world
+                slot = self.rank if self.rank < q else self.rank - 1
+                views.append((q, handle.get_buffer(q, (seg,), self.dtype, slot * seg)))
+            own = grad_ptrs[self.rank] + self.rank * seg * recv.element_size()
+            deltas = []
+            for r in range(self.world):
+                slot = r if r < self.rank else r - 1
+                deltas.append(0 if r == self.rank else recv.data_ptr() + slot * seg * recv.element_size() - own)
+            ok = all(d % 16 == 0 for d in deltas)
+        except Exception as exc:
+            self.fused_errors["push_reduce_scatter"] = "{}: {}".format(type(exc).__name__, exc)
+            ok = False
+        if not all(self._gather_objects(bool(ok))):
+            self.fused_errors.setdefault("push_reduce_scatter", "another rank could not set up its receive buffer")
+            return
+        self._symm_handle_push = handle
+        self._recv = recv
+        self._push_views = views
+        self._push_deltas = np.array(deltas, dtype=np.int64)
 
     def _make_local(self, named_pieces, **kwargs):
         return self.ops.make_optimizer(named_pieces, **kwargs)
@@ -385,6 +440,8 @@ class Zero1Gefen:
     def reduce_scatter_mode(self) -> str:
         if self.world == 1:
             return "none"
+        if self._recv is not None:
+            return "device-to-device pushes + sum of the local copies in the step kernels"
         if self._grad_deltas is None:
             return "nccl reduce_scatter"
         return "multimem.ld_reduce in the step kernels" if self._grad_mc_delta else "peer loads in the step kernels"
@@ -510,8 +567,90 @@ class Zero1Gefen:
         e.record()
         return e
 
+    def _plan_push(self) -> None:
+        """Cuts every rank's segment into the buckets of the pushed reduce-scatter (every rank computes all
+        ranks' cuts: a pusher must know its receivers' bucket limits). A bucket is a run of whole blocks of
+        consecutive pieces, about equal in bytes; `_push_ranges[q][k]` is its range of elements relative to
+        the start of q's segment, `_push_steps[k]` what this rank steps once bucket k has arrived."""
+        import os
+
+        from .host_stream import cut_buckets
+
+        seg = self.layout.segment
+        n_buckets = max(1, int(os.environ.get("GEFEN_B200_ZERO1_PUSH_BUCKETS", "8")))
+        esize = self.flat_grad.element_size()
+        self._push_ranges, self._push_steps = {}, []
+        for q in range(self.world):
+            pieces = sorted(self.layout.owned(q), key=lambda pc: pc.offset)
+            periods = []
+            for pc in pieces:
+                period = int(self.periods[pc.tensor])
+                periods.append(period if period > 1 and pc.numel % period == 0 else 1)
+            cuts = cut_buckets([pc.numel for pc in pieces], [esize] * len(pieces), periods, n_buckets) if pieces else []
+            ranges = []
+            for bucket in cuts:
+                lo = min(pieces[i].offset + (0 if whole else b0 * periods[i]) for i, b0, b1, whole in bucket)
+                hi = max(pieces[i].offset + (pieces[i].numel if whole else b1 * periods[i]) for i, b0, b1, whole in bucket)
+                ranges.append((lo - q * seg, hi - q * seg))
+            ranges += [(0, 0)] * (n_buckets - len(ranges))
+            self._push_ranges[q] = ranges
+            if q == self.rank:
+                by_offset = {pc.offset: prm for pc, prm in zip(self.pieces, self.piece_params)}
+                for bucket in cuts:
+                    prms = [(by_offset[pieces[i].offset], b0, b1, whole) for i, b0, b1, whole in bucket]
+                    self._push_steps.append((set(id(p) for p, _, _, _ in prms),
+                                             {id(p): (b0, b1) for p, b0, b1, whole in prms if not whole},
+                                             set(id(p) for p, b0, _, _ in prms if b0 == 0)))
+                self._push_steps += [None] * (n_buckets - len(self._push_steps))
+        self._push_stream = torch.cuda.Stream(self.device)
+        self._push_token = torch.zeros(1, dtype=torch.float32, device=self.device)
+
+    def _step_pushed(self) -> None:
+        """The step with the pushed reduce-scatter, bucket by bucket: on a side stream the copy engines push
+        bucket k of every segment this rank does not own to its owner, followed by a barrier of the ranks;
+        the step kernels (which also store the updated parameters to every rank) take bucket k as soon as it
+        is complete, while the pushes of bucket k + 1 are on the wire."""
+        if getattr(self, "_push_ranges", None) is None:
+            self._plan_push()
+        seg = self.layout.segment
+        main = torch.cuda.current_stream(self.device)
+        start = torch.cuda.Event()
+        start.record(main)   # gradients are final; the receive buffers' readers (the previous step) are done
+        self._push_stream.wait_event(start)
+        arrived = []
+        with torch.cuda.stream(self._push_stream):
+            for k in range(len(self._push_ranges[self.rank])):
+                for q, view in self._push_views:
+                    lo, hi = self._push_ranges[q][k]
+                    if hi > lo:
+                        view[lo:hi].copy_(self.flat_grad[q * seg + lo:q * seg + hi], non_blocking=True)
+                dist.all_reduce(self._push_token, group=self.group)   # every rank's pushes of bucket k have landed
+                e = torch.cuda.Event()
+                e.record(self._push_stream)
+                arrived.append(e)
+        if self.local is not None:
+            self.local._maybe_refresh_gefen_codebook()
+            self.local._grad_src_deltas = self._push_deltas
+            self.local._grad_multicast_delta = 0
+            self.local._grad_src_scale = (1.0 / self.world) if self.average else 1.0
+        for k, e in enumerate(arrived):
+            main.wait_event(e)
+            if self.local is not None and self._push_steps[k] is not None:
+                only, ranges, advance = self._push_steps[k]
+                self.local._step_multi_tensor(only=only, ranges=ranges, advance=advance)
+        if self.local is not None:
+            self.local._gefen_global_step += 1
+
     @torch.no_grad()
     def step(self):
+        if self._recv is not None and self._calibrated and not getattr(self, "_materialize_gradients", False):
+            marks = [self._mark(), self._mark()]
+            self._step_pushed()
+            marks.append(self._mark())
+            self._all_gather()
+            marks.append(self._mark())
+            self._events = marks
+            return
         marks = [self._mark()]
         self._reduce_scatter()
         marks.append(self._mark())
@@ -634,6 +773,26 @@ class Zero1Gefen:
                         and torch.equal(a["m_magnitude"], b["m_magnitude"]) and torch.equal(a["vmean"], b["vmean"])
                 verdict["in_kernel_reduce_bit_identical"] = same
                 verdict["in_kernel_reduce_tensors"] = len(keep)
+        elif self._recv is not None:
+            # the production gradient path: pushed copies summed in rank order inside the kernel
+            if single is not None:
+                scale = (1.0 / self.world) if self.average else 1.0
+                seg = self.layout.segment
+            self.step()
+            if single is not None:
+                for (pc, prm), clone in zip(chosen, mine):
+                    acc = torch.zeros(pc.numel, dtype=torch.float32, device=self.device)
+                    for r in range(self.world):
+                        if r == self.rank:
+                            acc += self.flat_grad[pc.offset:pc.offset + pc.numel].float()
+                        else:
+                            slot = r if r < self.rank else r - 1
+                            begin = slot * seg + pc.offset - self.rank * seg
+                            acc += self._recv[begin:begin + pc.numel].float()
+                    clone.grad.copy_((acc * scale).to(self.dtype).view_as(clone.grad))
+                single.step()
+                verdict["in_kernel_reduce_bit_identical"] = identical()
+                verdict["in_kernel_reduce_tensors"] = len(chosen)
         # every rank ends with the same parameters
         # (summed in slices: the int64 copy torch makes of a slice stays small beside a buffer that may fill the GPU)
         bits = torch.int16 if self.flat_param.element_size() == 2 else torch.int32
@@ -656,7 +815,7 @@ class Zero1Gefen:
             dist.all_reduce(worst, op=dist.ReduceOp.MIN, group=self.group)
             dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=self.group)
         verdict["bit_identical"] = bool(worst[0] > 0)
-        if self._grad_mc_delta:
+        if self._grad_mc_delta or self._recv is not None:
             verdict["in_kernel_reduce_bit_identical"] = bool(worst[1] > 0)
             verdict["in_kernel_reduce_tensors"] = int(sums[2])
         verdict["tensors"], verdict["elements"] = int(sums[0]), int(sums[1])

@@ -47,16 +47,18 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
     # own gradients + NCCL / own gradients + fused all-gather / pre-averaged gradients + fused all-gather /
     # own gradients + both collectives fused
     # ... / both collectives on the switch's multicast (where the machine has it; otherwise the defaults)
+    # ... / gradients pushed to their owners by device-to-device copies and summed by the step kernels
     for name, fused_ag, fused_rs, pre_averaged, mc in (("nccl", False, False, False, False), ("fused_ag", True, False, False, False),
                                                        ("averaged_inputs", True, False, True, False),
                                                        ("fused_both", True, True, False, False),
-                                                       ("multicast", None, None, False, True)):
+                                                       ("multicast", None, None, False, True),
+                                                       ("push", True, None, False, False)):
         params = [torch.nn.Parameter(make_param(s, 5, i, torch.bfloat16).to(dev)) for i, s in enumerate(shapes)]
         named = [("p{}".format(i), p) for i, p in enumerate(params)]
         for i, (p, s) in enumerate(zip(params, shapes)):
             p.grad = torch.zeros(s, dtype=torch.bfloat16, device=dev)
         opt = Zero1Gefen(named, lr=1e-3, weight_decay=0.1, fused_all_gather=fused_ag, fused_reduce_scatter=fused_rs,
-                         multicast=mc)
+                         multicast=mc, push_reduce_scatter=(name == "push"))
         for step in range(4):
             for i, (p, s) in enumerate(zip(params, shapes)):
                 g = averaged(i, s, step) if pre_averaged else grad_of(rank, i, s, step)
@@ -89,6 +91,9 @@ def test_fused_collectives_equal_nccl_collectives(tmp_path):
         assert torch.equal(res["fused_both"][3], res["averaged_inputs"][3])
         # and it is close to NCCL's own bf16 average
         assert (res["fused_both"][3].float() - res["nccl"][3].float()).abs().max() < 1e-2
+        # pushed copies summed by the kernels: the same rank-order mean
+        assert res["push"][1].startswith("device-to-device pushes"), res["push"][2]
+        assert torch.equal(res["push"][3], res["averaged_inputs"][3])
         # both collectives on the switch's multicast, where the machine offers it: the switch's sum is rounded
         # its own way (not the fp32 rank-order sum rounded to nearest even, even for two ranks), so this
         # is a tolerance check against the rank-order mean and against NCCL's average
@@ -97,7 +102,7 @@ def test_fused_collectives_equal_nccl_collectives(tmp_path):
         assert (res["multicast"][3].float() - res["averaged_inputs"][3].float()).abs().max() < 1e-2
         assert (res["multicast"][3].float() - res["nccl"][3].float()).abs().max() < 1e-2
     print("collectives with the defaults:", ranks[0]["multicast"][:3])
-    for name in ("nccl", "fused_ag", "fused_both", "multicast"):
+    for name in ("nccl", "fused_ag", "fused_both", "multicast", "push"):
         assert torch.equal(ranks[0][name][3], ranks[1][name][3]), name
     assert float(ranks[0]["fused_both"][3].float().abs().sum()) > 0
 
