@@ -592,7 +592,7 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
     float absmax = 0.0f;
     float sumsq = 0.0f;
     if (GSRC == 2) {
-        constexpr int U = FULL ? 4 : 1;
+        constexpr int U = 4;
         const S* const g_sum = peer_ptr(g_blk, L.grad_mc_delta);
         for (int c0 = lane; c0 < nchunks; c0 += LANES * U)
             first_pass_group<S, U, true, true>(g_sum, codes_in, stage_a, stage_b, rep, c0, LANES, nchunks, old_mag, beta1, omb1,
@@ -606,7 +606,10 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
         else if (n_src <= 4) reduce_pass<S, 4>(L, g_blk, codes_in, stage_a, stage_b, rep, lane, LANES, nchunks, old_mag, beta1, omb1, absmax, sumsq);
         else reduce_pass<S, 8>(L, g_blk, codes_in, stage_a, stage_b, rep, lane, LANES, nchunks, old_mag, beta1, omb1, absmax, sumsq);
     } else {
-        constexpr int U = FULL ? 4 : 1;  // chunks in flight per lane (short blocks: one chunk per lane)
+        // up to four chunks in flight per lane (blocks of up to 256 elements have one chunk per lane). With the
+        // kernels of the two block kinds compiled apart, four fit the registers of both (measured on blocks of
+        // 512 / 1024 bf16 elements: 0.549 -> 0.599 / 0.566 -> 0.620 of the copy bandwidth against one in flight)
+        constexpr int U = 4;
         // (a separate loop without bounds tests for the complete groups was measured: slower, it
         // costs registers)
         for (int c0 = lane; c0 < nchunks; c0 += LANES * U)
@@ -762,8 +765,10 @@ template <typename S, int GSRC> __host__ __device__ constexpr int vec_max_thread
     return (sizeof(S) == 2 && GSRC != 1) ? 640 : 512;
 }
 
-// GSRC: see warp_block_step.
-template <typename S, int GSRC>
+// GSRC: see warp_block_step. FULL: every tensor of the launch has whole-warp blocks (lanes_per_block == 32);
+// otherwise none has. The two kinds are separate kernels so that each is compiled (registers, code size) for
+// its own loop structure.
+template <typename S, int GSRC, bool FULL>
 __global__ void __launch_bounds__(vec_max_threads<S, GSRC>(), 1) step_vec_kernel(const __grid_constant__ StepLaunch L,
                                                            const __grid_constant__ gefen_b200_step_tensor_t single) {
     extern __shared__ __align__(128) unsigned char smem[];
@@ -804,8 +809,7 @@ __global__ void __launch_bounds__(vec_max_threads<S, GSRC>(), 1) step_vec_kernel
             if (!(t.flags & GEFEN_B200_STEP_MUON))
                 prefetch_l2_range(static_cast<const char*>(t.p) + elem0 * sizeof(S), unit_elems * sizeof(S), lane);
         }
-        if (lanes_per_block(t.period) == 32) warp_block_step<S, GSRC, true>(t, nb_local, L, s, stage, lane);
-        else warp_block_step<S, GSRC, false>(t, nb_local, L, s, stage, lane);
+        warp_block_step<S, GSRC, FULL>(t, nb_local, L, s, stage, lane);
     }
 }
 
@@ -1102,11 +1106,11 @@ static int warps_override() {
 constexpr unsigned int kDefaultStageSpinLimit = 4000000u;
 static unsigned int g_stage_spin_limit = kDefaultStageSpinLimit;
 
-template <typename S, int GSRC>
+template <typename S, int GSRC, bool FULL>
 static int launch_vec_variant(StepLaunch L, const gefen_b200_step_tensor_t& single, long long max_period,
                               cudaStream_t stream) {
     static bool configured[kMaxDevices];
-    auto kernel = step_vec_kernel<S, GSRC>;
+    auto kernel = step_vec_kernel<S, GSRC, FULL>;
     {
         int dev = 0;
         const int rc = current_device(&dev);
@@ -1137,11 +1141,11 @@ static int launch_vec_variant(StepLaunch L, const gefen_b200_step_tensor_t& sing
     return GEFEN_B200_OK;
 }
 
-template <typename S>
+template <typename S, bool FULL>
 static int launch_vec(StepLaunch L, const gefen_b200_step_tensor_t& single, long long max_period, cudaStream_t stream) {
-    if (L.grad_mc_delta != 0) return launch_vec_variant<S, 2>(L, single, max_period, stream);
-    if (L.n_grad_srcs > 0) return launch_vec_variant<S, 1>(L, single, max_period, stream);
-    return launch_vec_variant<S, 0>(L, single, max_period, stream);
+    if (L.grad_mc_delta != 0) return launch_vec_variant<S, 2, FULL>(L, single, max_period, stream);
+    if (L.n_grad_srcs > 0) return launch_vec_variant<S, 1, FULL>(L, single, max_period, stream);
+    return launch_vec_variant<S, 0, FULL>(L, single, max_period, stream);
 }
 
 template <typename S>
@@ -1171,28 +1175,34 @@ static int launch_generic(bool cta_per_block, const StepLaunch& L, const gefen_b
     return GEFEN_B200_OK;
 }
 
-// Class of a tensor: 1 = vectorised staged path, 0 = generic warp per block, -1 = generic CTA per block.
+// Class of a tensor: 1 = vectorised staged path with whole-warp blocks, 2 = the same path with several blocks
+// per warp pass (blocks of up to 1024 elements), 0 = generic warp per block, -1 = generic CTA per block.
 static int tensor_class(const gefen_b200_step_tensor_t& t, int dtype) {
     const bool vec_dtype = dtype == GEFEN_B200_F32 || dtype == GEFEN_B200_BF16 || dtype == GEFEN_B200_F16;
     const bool period1 = (t.flags & GEFEN_B200_STEP_PERIOD1) != 0;
     const bool packed = (t.flags & GEFEN_B200_STEP_PACKED) != 0;
     if (vec_dtype && !period1 && !packed && t.period % 8 == 0 && t.period <= kFastMaxPeriod && aligned16(t.g) && aligned16(t.p) &&
         (reinterpret_cast<uintptr_t>(t.codes) & 7u) == 0) {
-        return 1;
+        return lanes_per_block(t.period) == 32 ? 1 : 2;
     }
     return t.period > 2048 ? -1 : 0;
 }
 // Units of a tensor in its launch's index space: passes of a warp on the staged path, blocks elsewhere.
 static long long class_units(const gefen_b200_step_tensor_t& t, int cls) {
-    return cls == 1 ? vec_units(t.num_blocks, t.period) : t.num_blocks;
+    return cls >= 1 ? vec_units(t.num_blocks, t.period) : t.num_blocks;
 }
 
 static int launch_class(int cls, int dtype, const StepLaunch& L, const gefen_b200_step_tensor_t& single,
                         long long max_period, cudaStream_t stream) {
-    if (cls >= 1) {
-        if (dtype == GEFEN_B200_BF16) return launch_vec<__nv_bfloat16>(L, single, max_period, stream);
-        if (dtype == GEFEN_B200_F16) return launch_vec<__half>(L, single, max_period, stream);
-        return launch_vec<float>(L, single, max_period, stream);
+    if (cls == 1) {
+        if (dtype == GEFEN_B200_BF16) return launch_vec<__nv_bfloat16, true>(L, single, max_period, stream);
+        if (dtype == GEFEN_B200_F16) return launch_vec<__half, true>(L, single, max_period, stream);
+        return launch_vec<float, true>(L, single, max_period, stream);
+    }
+    if (cls == 2) {
+        if (dtype == GEFEN_B200_BF16) return launch_vec<__nv_bfloat16, false>(L, single, max_period, stream);
+        if (dtype == GEFEN_B200_F16) return launch_vec<__half, false>(L, single, max_period, stream);
+        return launch_vec<float, false>(L, single, max_period, stream);
     }
     const bool cta = cls < 0;
     switch (dtype) {
@@ -1240,7 +1250,7 @@ static int run_single(gefen_b200_step_tensor_t& t, int param_dtype, const float*
     L.grad_mc_delta = 0;
     L.param_mc_delta = 0;
     L.spin_limit = g_stage_spin_limit;
-    return launch_class(cls, param_dtype, L, t, cls == 1 ? unit_elements(t.period) : t.period, stream);
+    return launch_class(cls, param_dtype, L, t, cls >= 1 ? unit_elements(t.period) : t.period, stream);
 }
 
 }  // namespace gefen
@@ -1576,7 +1586,7 @@ int gefen_b200_multi_tensor_step_multicast(gefen_b200_step_tensor_t* host_table,
         const long long total = last.first_block + class_units(last, last.reserved_[0]);
         long long max_period = 0;   // largest staging need of a warp: the elements of one unit on the staged path
         for (int i = begin; i < begin + run; ++i) {
-            const long long need = host_table[begin].reserved_[0] == 1 ? unit_elements(host_table[i].period) : host_table[i].period;
+            const long long need = host_table[begin].reserved_[0] >= 1 ? unit_elements(host_table[i].period) : host_table[i].period;
             max_period = need > max_period ? need : max_period;
         }
         if (total > 0) {

@@ -199,6 +199,7 @@ class Gefen(torch.optim.Optimizer):
         self._gefen_global_step = 0
         self._plan = _StepPlan()
         self._plans = {}
+        self._steady = None
         if verbose:
             print("Initializing Gefen optimizer (fused={}).".format(self.fused))
         super().__init__(groups, dict(lr=lr, beta1=betas[0], beta2=betas[1], eps=eps))
@@ -506,6 +507,9 @@ class Gefen(torch.optim.Optimizer):
         steps only those blocks, and `advance` (a set of ids) names the tensors whose step counter moves
         in this call (the call that takes a tensor's first run); the other runs of the same optimizer step
         use the counter as that call left it."""
+        if only is None and ranges is None and advance is None and self._steady is not None:
+            if self._gefen_codebook is not None and self._step_steady():
+                return
         work = self._collect()
         if only is not None:
             work = [item for item in work if id(item[2]) in only]
@@ -522,9 +526,9 @@ class Gefen(torch.optim.Optimizer):
             if fused_p is not local_p:
                 copies.append((local_p, fused_p))
             work[i] = (group, name, p, fused_p, grad)
-        lib = _lib.load()
         ws = _lib.codebook_workspace(self._gefen_codebook)
-        for table in self._step_tables(work, ranges=ranges):
+        tables = self._step_tables(work, ranges=ranges)
+        for table in tables:
             rows = table["rows"]
             n = len(table["entries"])
             cols = {k: [0.0] * n for k in ("beta1", "beta2", "lr", "bc1", "bc2", "eps", "wd_mul")}
@@ -553,30 +557,91 @@ class Gefen(torch.optim.Optimizer):
             rows["p"] = p_ptr
             rows["g"] = g_ptr
             rows["flags"] = flags
-            device = table["device"]
-            # set by a ZeRO-1 wrapper whose parameter and gradient buffers are mapped between the ranks'
-            # GPUs: byte distances to the peers' parameter copies, which the kernels then store to as
-            # well, and to all ranks' gradient buffers, which the kernels then average themselves
-            peers = getattr(self, "_peer_param_deltas", None)
-            grad_srcs = getattr(self, "_grad_src_deltas", None)
-            with _lib.device_guard(device):
-                if (peers is not None and len(peers)) or (grad_srcs is not None and len(grad_srcs)):
-                    n_peers = 0 if peers is None else len(peers)
-                    n_srcs = 0 if grad_srcs is None else len(grad_srcs)
-                    # multicast (NVSwitch) addresses of the same buffers, where the wrapper found them
-                    param_mc = int(getattr(self, "_param_multicast_delta", 0) or 0) if n_peers else 0
-                    grad_mc = int(getattr(self, "_grad_multicast_delta", 0) or 0) if n_srcs else 0
-                    _lib.check(lib.gefen_b200_multi_tensor_step_multicast(
-                        rows.ctypes.data, _lib.ptr(table["device_table"]), n, table["tag"], _lib.ptr(ws),
-                        peers.ctypes.data if n_peers else None, n_peers,
-                        grad_srcs.ctypes.data if n_srcs else None, n_srcs, float(getattr(self, "_grad_src_scale", 1.0)),
-                        param_mc, grad_mc, _lib.current_stream(device)))
-                else:
-                    _lib.check(lib.gefen_b200_multi_tensor_step(
-                        rows.ctypes.data, _lib.ptr(table["device_table"]), n, table["tag"], _lib.ptr(ws),
-                        _lib.current_stream(device)))
+            self._launch_table(table, ws)
         for local_p, fused_p in copies:
             local_p.copy_(fused_p)
+        # A whole step over plain contiguous tensors: remember what the next call can reuse as it is.
+        self._steady = None
+        if only is None and ranges is None and advance is None and not copies and \
+                all(type(item[2].grad) is torch.Tensor and not hasattr(item[2], "to_local") for item in work):
+            in_plan = {id(item[2]) for item in work}
+            self._steady = {
+                "codebook": self._gefen_codebook,
+                "n_groups": len(self.param_groups),
+                "n_params": sum(len(g["params"]) for g in self.param_groups),
+                "idle": [p for g in self.param_groups for p in g["params"] if id(p) not in in_plan],
+                "tables": [(table, [(work[idx][2], self.state[work[idx][2]], work[idx][0], int(table["rows"]["g"][r]),
+                                     int(table["rows"]["p"][r]), work[idx][4].numel(), work[idx][4].dtype)
+                                    for r, idx in enumerate(table["entries"])])
+                           for table in tables],
+            }
+
+    def _step_steady(self) -> bool:
+        """The step of a training loop in its steady state: the same tensors at the same addresses as in the
+        previous call, so only the step counters and the scalars derived from them change. Checks exactly
+        that first (and returns False, having changed nothing, if anything differs)."""
+        st = self._steady
+        if st["codebook"] is not self._gefen_codebook or st["n_groups"] != len(self.param_groups) or \
+                st["n_params"] != sum(len(g["params"]) for g in self.param_groups):
+            return False
+        for p in st["idle"]:
+            if p.grad is not None:
+                return False
+        for table, items in st["tables"]:
+            for p, state, group, g_ptr, p_ptr, numel, dtype in items:
+                g = p.grad
+                if g is None or type(g) is not torch.Tensor or g.data_ptr() != g_ptr or p.data_ptr() != p_ptr or \
+                        g.numel() != numel or g.dtype != dtype or not g.is_contiguous() or not p.is_contiguous():
+                    return False
+        ws = _lib.codebook_workspace(self._gefen_codebook)
+        memo = {}
+        for table, items in st["tables"]:
+            vals = []
+            for p, state, group, g_ptr, p_ptr, numel, dtype in items:
+                step = state["step"] + 1
+                state["step"] = step
+                key = (group["beta1"], group["beta2"], float(group["lr"]), group["weight_decay"], group["eps"], step)
+                v = memo.get(key)
+                if v is None:
+                    beta1, beta2, lr, wd, eps, _ = key
+                    v = memo[key] = (beta1, beta2, lr, 1 - beta1 ** step, 1 - beta2 ** step, eps,
+                                     (1 - lr * wd) if wd > 0.0 else 1.0, 1.0 if wd > 0.0 else 0.0)
+                vals.append(v)
+            cols = np.array(vals, dtype=np.float64)
+            rows = table["rows"]
+            for c, k in enumerate(("beta1", "beta2", "lr", "bc1", "bc2", "eps", "wd_mul")):
+                rows[k] = cols[:, c]
+            rows["flags"] = table["static_flags"] | (cols[:, 7].astype(table["static_flags"].dtype) * _lib.STEP_WEIGHT_DECAY)
+            self._launch_table(table, ws)
+        return True
+
+    def _launch_table(self, table, ws) -> None:
+        """One multi-tensor call of the library for a filled table (one launch per kernel class in it)."""
+        lib = _lib.load()
+        rows = table["rows"]
+        n = len(table["entries"])
+        device = table["device"]
+        # set by a ZeRO-1 wrapper whose parameter and gradient buffers are mapped between the ranks'
+        # GPUs: byte distances to the peers' parameter copies, which the kernels then store to as
+        # well, and to all ranks' gradient buffers, which the kernels then average themselves
+        peers = getattr(self, "_peer_param_deltas", None)
+        grad_srcs = getattr(self, "_grad_src_deltas", None)
+        with _lib.device_guard(device):
+            if (peers is not None and len(peers)) or (grad_srcs is not None and len(grad_srcs)):
+                n_peers = 0 if peers is None else len(peers)
+                n_srcs = 0 if grad_srcs is None else len(grad_srcs)
+                # multicast (NVSwitch) addresses of the same buffers, where the wrapper found them
+                param_mc = int(getattr(self, "_param_multicast_delta", 0) or 0) if n_peers else 0
+                grad_mc = int(getattr(self, "_grad_multicast_delta", 0) or 0) if n_srcs else 0
+                _lib.check(lib.gefen_b200_multi_tensor_step_multicast(
+                    rows.ctypes.data, _lib.ptr(table["device_table"]), n, table["tag"], _lib.ptr(ws),
+                    peers.ctypes.data if n_peers else None, n_peers,
+                    grad_srcs.ctypes.data if n_srcs else None, n_srcs, float(getattr(self, "_grad_src_scale", 1.0)),
+                    param_mc, grad_mc, _lib.current_stream(device)))
+            else:
+                _lib.check(lib.gefen_b200_multi_tensor_step(
+                    rows.ctypes.data, _lib.ptr(table["device_table"]), n, table["tag"], _lib.ptr(ws),
+                    _lib.current_stream(device)))
 
     def check(self) -> None:
         """Raises if a kernel of an earlier step gave up one of its bounded waits, which leaves that
@@ -611,6 +676,7 @@ class Gefen(torch.optim.Optimizer):
         self._gefen_codebook = codebook
         self._plan = _StepPlan()
         self._plans = {}
+        self._steady = None
         id_map = dict(zip(chain.from_iterable(g["params"] for g in state_dict["param_groups"]),
                           chain.from_iterable(g["params"] for g in self.param_groups)))
         for param_id, saved in saved_state.items():

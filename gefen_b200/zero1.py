@@ -837,7 +837,7 @@ class Zero1Gefen:
         for table in plan.tables or []:
             for entry, cls in zip(table["entries"], table["classes"]):
                 if entry < len(params) and params[entry] is prm:
-                    return cls == 1
+                    return cls >= 1
         return False
 
     def state_dict(self):
@@ -938,6 +938,7 @@ class Zero1Gefen:
             self.local._gefen_global_step = int(full.get("gefen_global_step", 0))
         if hasattr(self.local, "_plans"):
             self.local._plans = {}
+            self.local._steady = None
         self._calibrated = self.codebook is not None
 
 

@@ -191,7 +191,8 @@ int gefen_b200_multicast_sum(void* dst, const void* src_multicast, int dtype, in
                              void* stream);
 /* sizeof(gefen_b200_step_tensor_t) as compiled, for binding-side layout checks. */
 int gefen_b200_step_tensor_size(void);
-/* Kernel class the library would use for one table entry: 1 = vectorised staged path,
+/* Kernel class the library would use for one table entry: 1 = vectorised staged path with one block per
+ * warp pass, 2 = the same path with several blocks (of up to 1024 elements) per warp pass,
  * 0 = generic warp-per-block, -1 = generic CTA-per-block. Rows of equal
  * class that are adjacent in the table share one launch. */
 int gefen_b200_step_tensor_class(const gefen_b200_step_tensor_t* host_entry, int param_dtype);

@@ -252,7 +252,7 @@ def test_multi_tensor_step_matches_per_tensor_sequence(oracle, cuda_device, dtyp
         rows[k] = val
     tag = _lib.dtype_tag(dtype)
     classes = [lib.gefen_b200_step_tensor_class(rows[r:r + 1].ctypes.data, tag) for r in range(len(shapes))]
-    assert set(classes) == {1, 0, -1}
+    assert set(classes) >= {1, 0, -1} and set(classes) <= {2, 1, 0, -1}
     order = sorted(range(len(shapes)), key=lambda r: classes[r])
     rows = np.ascontiguousarray(rows[order])
     table = torch.empty(rows.nbytes, dtype=torch.uint8, device=cuda_device)
