@@ -328,7 +328,7 @@ def run_sharded_arm(args, cfg, rank, world, local_rank):
 
 # DRAM bytes (read + write) per algorithmic byte of one launch of the staged step kernel, from an ncu
 # capture of a 134 M-element launch of the same kernel (traffic grows in proportion to the elements).
-STEP_KERNEL_DRAM_BYTES_PER_ALGORITHMIC_BYTE = {2: 0.971}
+STEP_KERNEL_DRAM_BYTES_PER_ALGORITHMIC_BYTE = {2: 0.967}
 
 
 def run_gpu_arm(args, cfg, rank, world, local_rank):
