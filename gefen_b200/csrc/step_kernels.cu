@@ -848,10 +848,16 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
 
     for (long long gb = group_global; gb < L.total_blocks; gb += group_stride) {
         const gefen_b200_step_tensor_t* tp = table + find_tensor(table, L.n_tensors, gb);
-        const long long b = gb - tp->first_block;
         const int period = static_cast<int>(tp->period);
-        const long long start = b * period;
         const uint32_t flags = tp->flags;
+        // 4-bit codes with an odd period: blocks 2k and 2k + 1 share the byte between them (and with no other
+        // block), so the pair is one unit of work and its two blocks are taken one after the other by the same
+        // threads; see paired_units.
+        const int halves = ((flags & GEFEN_B200_STEP_PACKED) != 0 && (period & 1) != 0) ? 2 : 1;
+        for (int half = 0; half < halves; ++half) {
+        const long long b = (gb - tp->first_block) * halves + half;
+        if (b >= tp->num_blocks) break;
+        const long long start = b * period;
         const bool muon = (flags & GEFEN_B200_STEP_MUON) != 0;
         const bool period1 = (flags & GEFEN_B200_STEP_PERIOD1) != 0;
         const bool fuse_v = (flags & GEFEN_B200_STEP_FUSE_VMEAN) != 0;
@@ -860,10 +866,13 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
         const S* g = static_cast<const S*>(tp->g) + start;
         S* prm = static_cast<S*>(tp->p) + start;
         // 4-bit codes (reference: automatic_gefen_fused_kernel.cu:14-57): two per byte over the whole
-        // tensor, low nibble first. The period is even here, so a block starts on a byte and a thread
-        // that owns an element pair owns its byte: no atomics.
+        // tensor, low nibble first. A thread owns a byte and the (one or two) elements of this block in it: no
+        // atomics (the reference uses atomicCAS). lead = 1: the block starts on the high nibble of its first
+        // byte, whose low nibble belongs to the block before; likewise the last byte's high nibble may belong
+        // to the block after. Such bytes are rewritten with the other block's nibble kept.
         const bool packed = (flags & GEFEN_B200_STEP_PACKED) != 0;
         const int per = packed ? 2 : 1;
+        const int lead = packed ? static_cast<int>(start & 1) : 0;
         uint8_t* codes = tp->codes + (packed ? start / 2 : start);
         void* mag_ptr = tp->mag;
         void* v_ptr = tp->v;
@@ -879,10 +888,11 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
         // period-1 tensors update their per-element second moment here
         // (reference: automatic_gefen_fused_kernel.cu:350-366).
         float absmax = 0.0f, sumsq = 0.0f;
-        for (int i0 = tig * per; i0 < period; i0 += GROUP * per) {
-            const uint32_t byte = codes[packed ? i0 / 2 : i0];
+        for (int i0 = tig * per - lead; i0 < period; i0 += GROUP * per) {
+            const uint32_t byte = codes[packed ? (i0 + lead) / 2 : i0];
             for (int e = 0; e < per; ++e) {
                 const int i = i0 + e;
+                if (i < 0 || i >= period) continue;   // the neighbouring block's nibble
                 const uint32_t old_code = packed ? ((byte >> (4 * e)) & 0xFu) : byte;
                 const float gi = gradient_element(g + i, L);
                 if (period1) {
@@ -934,11 +944,15 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
         const bool do_update = muon || period1 || lr != 0.0f;
 
         // pass 2: re-encode and update
-        for (int i0 = tig * per; i0 < period; i0 += GROUP * per) {
-            const uint32_t byte = codes[packed ? i0 / 2 : i0];
+        for (int i0 = tig * per - lead; i0 < period; i0 += GROUP * per) {
+            const uint32_t byte = codes[packed ? (i0 + lead) / 2 : i0];
             uint32_t new_byte = 0u;
             for (int e = 0; e < per; ++e) {
             const int i = i0 + e;
+            if (i < 0 || i >= period) {   // the neighbouring block's nibble stays
+                new_byte |= byte & (0xFu << (4 * e));
+                continue;
+            }
             const uint32_t old_code = packed ? ((byte >> (4 * e)) & 0xFu) : byte;
             const float gi = gradient_element(g + i, L);
             const float cur = old_mag * s.cb[old_code];
@@ -962,7 +976,11 @@ __global__ void __launch_bounds__(kThreads) step_generic_kernel(const __grid_con
                 for (int r = 0; r < L.n_peers; ++r) ScalarIO<S>::store(peer_ptr(prm + i, L.peer_delta[r]), updated);
             }
             }
-            codes[packed ? i0 / 2 : i0] = static_cast<uint8_t>(new_byte);
+            codes[packed ? (i0 + lead) / 2 : i0] = static_cast<uint8_t>(new_byte);
+        }
+        if (halves > 1) {   // the pair's second block reads the shared byte after this block has written it
+            if (GROUP > 32) __syncthreads(); else __syncwarp();
+        }
         }
     }
 }
@@ -1188,8 +1206,11 @@ static int tensor_class(const gefen_b200_step_tensor_t& t, int dtype) {
     return t.period > 2048 ? -1 : 0;
 }
 // Units of a tensor in its launch's index space: passes of a warp on the staged path, blocks elsewhere.
+// (4-bit codes with an odd period: a pair of blocks is one unit, see step_generic_kernel)
 static long long class_units(const gefen_b200_step_tensor_t& t, int cls) {
-    return cls >= 1 ? vec_units(t.num_blocks, t.period) : t.num_blocks;
+    if (cls >= 1) return vec_units(t.num_blocks, t.period);
+    const bool paired = (t.flags & GEFEN_B200_STEP_PACKED) != 0 && (t.period & 1) != 0;
+    return paired ? (t.num_blocks + 1) / 2 : t.num_blocks;
 }
 
 static int launch_class(int cls, int dtype, const StepLaunch& L, const gefen_b200_step_tensor_t& single,
@@ -1222,10 +1243,7 @@ static int check_common(const void* g, uint8_t* codes, void* mag, int mag_dtype,
                     "Expected m_magnitude to have dtype float32, float16, or bfloat16.");
     GEFEN_CHECK_ARG(num_blocks >= 0 && period > 0, "Expected a positive period and a non-negative block count.");
     GEFEN_CHECK_ARG(period <= 0x7FFFFFFFLL, "Period %lld is too large.", period);
-    if (packed_indices && period % 2 != 0) {
-        return fail(GEFEN_B200_EUNSUPPORTED,
-                    "packed_indices=True (4-bit codes) needs an even period: with an odd one two blocks share a byte.");
-    }
+    (void)packed_indices;   // any period: with an odd one, pairs of blocks share a byte and are stepped together
     return GEFEN_B200_OK;
 }
 
@@ -1561,8 +1579,8 @@ int gefen_b200_multi_tensor_step_multicast(gefen_b200_step_tensor_t* host_table,
         GEFEN_CHECK_ARG(is_state_dtype(t.mag_dtype) && is_state_dtype(t.v_dtype),
                         "Tensor %d of the table has a bad state dtype.", i);
         GEFEN_CHECK_ARG((t.flags & GEFEN_B200_STEP_MUON) || t.v != nullptr, "Tensor %d has a null vmean.", i);
-        GEFEN_CHECK_ARG(!(t.flags & GEFEN_B200_STEP_PACKED) || (t.period % 2 == 0 && !(t.flags & GEFEN_B200_STEP_PERIOD1)),
-                        "Tensor %d: 4-bit codes need an even period and are not defined for period-1 tensors.", i);
+        GEFEN_CHECK_ARG(!(t.flags & GEFEN_B200_STEP_PACKED) || !(t.flags & GEFEN_B200_STEP_PERIOD1),
+                        "Tensor %d: 4-bit codes are not defined for period-1 tensors.", i);
         GEFEN_CHECK_ARG(n_grad_srcs == 0 || !(t.flags & GEFEN_B200_STEP_MUON),
                         "Tensor %d: the momentum-only step does not average gradients over ranks.", i);
         t.reserved_[0] = tensor_class(t, param_dtype);

@@ -47,7 +47,7 @@ extern "C" {
 #define GEFEN_B200_STEP_PERIOD1 4u      /* per-element vmean; `period` is the magnitude block */
 #define GEFEN_B200_STEP_MUON 8u         /* write the dequantised momentum to `p`, no Adam update */
 #define GEFEN_B200_STEP_NESTEROV 16u    /* with MUON: p <- round(round(m*beta1) + (1-beta1)*g) */
-#define GEFEN_B200_STEP_PACKED 32u      /* codes are 4-bit, two per byte, low nibble first (even periods only) */
+#define GEFEN_B200_STEP_PACKED 32u      /* codes are 4-bit, two per byte over the whole tensor, low nibble first */
 
 const char* gefen_b200_last_error(void);
 int gefen_b200_version(void);

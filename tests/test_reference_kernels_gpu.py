@@ -111,11 +111,12 @@ def test_calibration_kernels_against_the_reference_kernels(ref_ext, oracle, cuda
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nb,period", [(64, 512), (33, 24), (5, 4096), (17, 130)])
+@pytest.mark.parametrize("nb,period", [(64, 512), (33, 24), (5, 4096), (17, 130), (33, 25), (8, 9), (5, 4097), (1, 7)])
 def test_packed_4bit_codes_against_the_reference_kernels(ref_ext, oracle, cuda_device, dtype, nb, period):
     """packed_indices=True: two 4-bit codes per byte, a 16-entry codebook (reference:
     automatic_gefen_fused_kernel.cu:14-57). Bit-identical codes, magnitudes and parameters for the
-    AdamW step and for GefenMuon's momentum."""
+    AdamW step and for GefenMuon's momentum. Odd periods, where neighbouring blocks share a byte (the reference
+    updates nibbles with atomicCAS), included."""
     from gefen_b200.kernels.automatic_gefen_fused import (
         automatic_gefen_fused_update_from_vmean_cuda,
         automatic_gefen_muon_momentum_cuda,
@@ -126,7 +127,7 @@ def test_packed_4bit_codes_against_the_reference_kernels(ref_ext, oracle, cuda_d
     dcb = cb.to(cuda_device)
     p, g, _, mag, v = _state(nb, period, dtype, seed=nb * 7 + period)
     gen = torch.Generator().manual_seed(nb + period)
-    packed = torch.randint(0, 256, (nb * period // 2,), dtype=torch.uint8, generator=gen)
+    packed = torch.randint(0, 256, ((nb * period + 1) // 2,), dtype=torch.uint8, generator=gen)
     args = (0.9, 3e-4, 1 - 0.9 ** 3, 1 - 0.999 ** 3, 1e-8)
     rp, rg, rc, rm, rv = (t.clone().to(cuda_device) for t in (p, g, packed, mag, v))
     mp, mg, mc, mm, mv = (t.clone().to(cuda_device) for t in (p, g, packed, mag, v))

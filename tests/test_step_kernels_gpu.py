@@ -274,16 +274,3 @@ def test_multi_tensor_step_matches_per_tensor_sequence(oracle, cuda_device, dtyp
             tol = 2e-6 if dtype == torch.float32 else 8e-3
             assert torch.allclose(dv.cpu().float(), v.float(), rtol=tol, atol=0)
             assert rel_l2(dp.cpu(), p) <= (1e-6 if dtype == torch.float32 else 2e-3)
-
-
-def test_packed_codes_with_an_odd_period_are_refused(cuda_device):
-    """Two blocks would share a byte (the reference resolves that with atomicCAS); this library
-    refuses instead of racing."""
-    from gefen_b200.kernels.automatic_gefen_fused import automatic_gefen_fused_update_from_vmean_cuda
-
-    nb, period = 4, 9
-    cb = torch.linspace(-1, 1, 16).to(cuda_device)
-    p, g, _, mag, v = (t.to(cuda_device) for t in _state(nb, period, torch.float32, torch.float32, seed=1))
-    packed = torch.zeros((nb * period + 1) // 2, dtype=torch.uint8, device=cuda_device)
-    with pytest.raises(NotImplementedError):
-        automatic_gefen_fused_update_from_vmean_cuda(p, g, packed, mag, v, cb, True, 0.9, 1e-3, 0.1, 0.001, 1e-8)
