@@ -11,8 +11,9 @@
 //   p_i  -= cb[code'_i] * mag' * step * lr,   step = (1/bc1) / (sqrt(v/bc2) + eps)
 //
 // Two kernels:
-//  * step_vec_kernel  - the fast path. One warp owns one block (several blocks when they are
-//    not longer than 1024 elements: see lanes_per_block). Codes and gradients are read once
+//  * step_vec_kernel  - the fast path, in two kinds that are compiled and launched separately: one warp
+//    owns one block, or several blocks when they are not longer than 1024 elements (see
+//    lanes_per_block). Codes and gradients are read once
 //    (128-bit loads), the updated momenta wait in the warp's slice of shared memory while the
 //    block's absmax is reduced with shuffles, then they are re-encoded and the parameters updated:
 //    codes, gradients and params cross HBM exactly once (8 B/element in bf16, 14 B/element in
