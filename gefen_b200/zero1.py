@@ -215,6 +215,30 @@ class GpuOps:
         return Gefen(named_pieces, **kwargs)
 
 
+def push_plan(layout, tensor_periods, q: int, n_buckets: int, element_size: int):
+    """Buckets of rank q's segment for the pushed reduce-scatter: runs of whole blocks of consecutive pieces,
+    about equal in bytes (`host_stream.cut_buckets`). Returns (pieces in address order, the period used for
+    each, the cuts, and per bucket the range of elements it covers relative to the start of the segment,
+    padded with empty ranges to `n_buckets`). A function of the layout and the periods only, so every rank
+    computes the same plan for every other rank."""
+    from .host_stream import cut_buckets
+
+    seg = layout.segment
+    pieces = sorted(layout.owned(q), key=lambda pc: pc.offset)
+    periods = []
+    for pc in pieces:
+        period = int(tensor_periods[pc.tensor])
+        periods.append(period if period > 1 and pc.numel % period == 0 else 1)
+    cuts = cut_buckets([pc.numel for pc in pieces], [element_size] * len(pieces), periods, n_buckets) if pieces else []
+    ranges = []
+    for bucket in cuts:
+        lo = min(pieces[i].offset + (0 if whole else b0 * periods[i]) for i, b0, b1, whole in bucket)
+        hi = max(pieces[i].offset + (pieces[i].numel if whole else b1 * periods[i]) for i, b0, b1, whole in bucket)
+        ranges.append((lo - q * seg, hi - q * seg))
+    ranges += [(0, 0)] * (n_buckets - len(ranges))
+    return pieces, periods, cuts, ranges
+
+
 class Zero1Gefen:
     """Gefen over ZeRO-1 sharded optimizer state.
 
@@ -574,25 +598,11 @@ class Zero1Gefen:
         the start of q's segment, `_push_steps[k]` what this rank steps once bucket k has arrived."""
         import os
 
-        from .host_stream import cut_buckets
-
-        seg = self.layout.segment
         n_buckets = max(1, int(os.environ.get("GEFEN_B200_ZERO1_PUSH_BUCKETS", "8")))
         esize = self.flat_grad.element_size()
         self._push_ranges, self._push_steps = {}, []
         for q in range(self.world):
-            pieces = sorted(self.layout.owned(q), key=lambda pc: pc.offset)
-            periods = []
-            for pc in pieces:
-                period = int(self.periods[pc.tensor])
-                periods.append(period if period > 1 and pc.numel % period == 0 else 1)
-            cuts = cut_buckets([pc.numel for pc in pieces], [esize] * len(pieces), periods, n_buckets) if pieces else []
-            ranges = []
-            for bucket in cuts:
-                lo = min(pieces[i].offset + (0 if whole else b0 * periods[i]) for i, b0, b1, whole in bucket)
-                hi = max(pieces[i].offset + (pieces[i].numel if whole else b1 * periods[i]) for i, b0, b1, whole in bucket)
-                ranges.append((lo - q * seg, hi - q * seg))
-            ranges += [(0, 0)] * (n_buckets - len(ranges))
+            pieces, periods, cuts, ranges = push_plan(self.layout, self.periods, q, n_buckets, esize)
             self._push_ranges[q] = ranges
             if q == self.rank:
                 by_offset = {pc.offset: prm for pc, prm in zip(self.pieces, self.piece_params)}

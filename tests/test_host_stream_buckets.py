@@ -41,3 +41,34 @@ def test_cut_buckets_balances_bytes():
     sizes = [sum((b1 - b0) * (PERIODS[i] if PERIODS[i] > 1 else numels[i]) * 2 for i, b0, b1, _ in b) for b in buckets]
     assert len(buckets) == 8
     assert max(sizes) <= 1.1 * (sum(sizes) / 8)
+
+
+@pytest.mark.parametrize("world,n_buckets", [(2, 8), (3, 4), (2, 1)])
+def test_push_plan_covers_every_owned_piece_once(world, n_buckets):
+    """Buckets of the pushed reduce-scatter of ZeRO-1 (host logic): for every rank the bucket ranges lie inside
+    its segment, do not overlap, ascend, and together contain every element of every piece it owns; the block
+    runs of the cuts cover every block exactly once."""
+    from gefen_b200.zero1 import FlatLayout, push_plan
+
+    shapes = [(96, 512), (64, 2048), (2048,), (40, 768), (33, 24), (7,), (128, 1024), (300, 2048)]
+    periods = {0: 512, 1: 2048, 2: 1, 3: 768, 4: 24, 5: 1, 6: 1024, 7: 2048}
+    layout = FlatLayout(shapes, world)
+    for q in range(world):
+        pieces, used, cuts, ranges = push_plan(layout, periods, q, n_buckets, 2)
+        assert len(ranges) == n_buckets
+        filled = [r for r in ranges if r[1] > r[0]]
+        assert all(0 <= lo < hi <= layout.segment for lo, hi in filled)
+        assert all(a[1] <= b[0] for a, b in zip(filled, filled[1:]))
+        for pc in pieces:   # every element of the piece lies in some bucket's range
+            lo, hi = pc.offset - q * layout.segment, pc.offset + pc.numel - q * layout.segment
+            covered = sorted((max(lo, a), min(hi, b)) for a, b in filled if a < hi and b > lo)
+            assert covered and covered[0][0] == lo and covered[-1][1] == hi
+            assert all(x[1] == y[0] for x, y in zip(covered, covered[1:]))
+        runs = {}
+        for bucket in cuts:
+            for i, b0, b1, whole in bucket:
+                runs.setdefault(i, []).append((b0, b1))
+        for i, pc in enumerate(pieces):
+            blocks = pc.numel // used[i] if used[i] > 1 else 1
+            r = runs[i]
+            assert r[0][0] == 0 and r[-1][1] == blocks and all(a[1] == b[0] for a, b in zip(r, r[1:]))
