@@ -309,7 +309,7 @@ class Zero1Gefen:
         use_grad_srcs = grad_ptrs is not None and (self._grad_mc_delta != 0 or peer_rs)
         self._grad_deltas = np.array([grad_ptrs[r] - grad_ptrs[self.rank] for r in range(self.world)], dtype=np.int64) \
             if use_grad_srcs else None
-        # Two or three ranks (no multicast): instead of NCCL's reduce-scatter, every rank pushes the segments it
+        # Two ranks (no multicast; three when asked): instead of NCCL's reduce-scatter, every rank pushes the segments it
         # does not own into a receive buffer on their owners with plain device-to-device copies (the copy
         # engines, at the full peer-copy rate), and the step kernels sum the local copies in rank order while
         # they read them. Costs (N-1)/N of one buffer in memory; off where that is too much.
@@ -370,7 +370,8 @@ class Zero1Gefen:
         nbytes = (self.world - 1) * seg * self.flat_grad.element_size()
         if requested is None and env == "auto":
             total_memory = torch.cuda.get_device_properties(self.device).total_memory
-            want = self.world <= 3 and nbytes * 6 <= total_memory and torch.cuda.mem_get_info(self.device)[0] > nbytes + (8 << 30)
+            # (measured and tested with two ranks; three ranks take it only when asked)
+            want = self.world == 2 and nbytes * 6 <= total_memory and torch.cuda.mem_get_info(self.device)[0] > nbytes + (8 << 30)
         votes = self._gather_objects(bool(want))
         if not all(votes):
             return
