@@ -405,21 +405,25 @@ __device__ __forceinline__ void first_pass_group(const S* g_blk, const uint2* co
 // First pass of a block whose gradient is averaged over up to NSRC buffers. kSlots 16-byte (fp32:
 // 32-byte) loads per lane are in flight at a time: U chunks x a batch of BS sources; the sources of
 // a chunk are added batch after batch, in the order given.
-template <typename S, int NSRC>
+// EXACT: there are exactly NSRC sources (no test per source).
+template <typename S, int NSRC, bool EXACT = false>
 __device__ __forceinline__ void reduce_pass(const StepLaunch& L, const S* g_blk, const uint2* codes_in, float4* stage_a,
                                             float4* stage_b, const float* rep, int lane, int LANES, int nchunks,
                                             float old_mag, float beta1, float omb1, float& absmax, float& sumsq) {
     constexpr int kSlots = sizeof(S) == 2 ? 4 : 2;
     constexpr int BS = NSRC < kSlots ? NSRC : kSlots;
     constexpr int U = kSlots / BS;
-    const int n_src = L.n_grad_srcs;
+    const int n_src = EXACT ? NSRC : L.n_grad_srcs;
     const float scale = L.grad_scale;
     for (int c0 = lane; c0 < nchunks; c0 += LANES * U) {
         float acc[U][8];
+        uint2 craw[U];   // the codes travel with the first batch of gradient loads
 #pragma unroll
-        for (int u = 0; u < U; ++u)
+        for (int u = 0; u < U; ++u) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) acc[u][i] = 0.0f;
+            if (c0 + LANES * u < nchunks) craw[u] = __ldcs(codes_in + c0 + LANES * u);
+        }
 #pragma unroll
         for (int r0 = 0; r0 < NSRC; r0 += BS) {
             if (r0 < n_src) {
@@ -450,17 +454,16 @@ __device__ __forceinline__ void reduce_pass(const StepLaunch& L, const S* g_blk,
         for (int u = 0; u < U; ++u) {
             const int c = c0 + LANES * u;
             if (c < nchunks) {
-                const uint2 craw = codes_in[c];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) acc[u][i] *= scale;
                 Chunk<S> rounded;
                 rounded.pack(acc[u]);
                 float g[8], m[8];
                 rounded.unpack(g);
-                const uint32_t cw[2] = {craw.x, craw.y};
+                const uint32_t cw[2] = {craw[u].x, craw[u].y};
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const uint32_t code = (cw[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+                    const uint32_t code = __byte_perm(cw[i >> 2], 0u, 0x4440u + (i & 3));   // byte i & 3, zero-extended
                     const float cur = old_mag * rep[code * kRepCopies];
                     m[i] = ema_update(beta1, cur, omb1, g[i]);
                     absmax = max_abs_nan(absmax, m[i]);
@@ -603,8 +606,10 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
         // peers', read over NVLink), summed in fp32 in rank order and rounded to the gradient dtype,
         // as a reduce-scatter into that dtype would leave it.
         const int n_src = L.n_grad_srcs;
-        if (n_src <= 2) reduce_pass<S, 2>(L, g_blk, codes_in, stage_a, stage_b, rep, lane, LANES, nchunks, old_mag, beta1, omb1, absmax, sumsq);
-        else if (n_src <= 4) reduce_pass<S, 4>(L, g_blk, codes_in, stage_a, stage_b, rep, lane, LANES, nchunks, old_mag, beta1, omb1, absmax, sumsq);
+        if (n_src == 2) reduce_pass<S, 2, true>(L, g_blk, codes_in, stage_a, stage_b, rep, lane, LANES, nchunks, old_mag, beta1, omb1, absmax, sumsq);
+        else if (n_src < 2) reduce_pass<S, 2>(L, g_blk, codes_in, stage_a, stage_b, rep, lane, LANES, nchunks, old_mag, beta1, omb1, absmax, sumsq);
+        else if (n_src == 4) reduce_pass<S, 4, true>(L, g_blk, codes_in, stage_a, stage_b, rep, lane, LANES, nchunks, old_mag, beta1, omb1, absmax, sumsq);
+        else if (n_src < 4) reduce_pass<S, 4>(L, g_blk, codes_in, stage_a, stage_b, rep, lane, LANES, nchunks, old_mag, beta1, omb1, absmax, sumsq);
         else reduce_pass<S, 8>(L, g_blk, codes_in, stage_a, stage_b, rep, lane, LANES, nchunks, old_mag, beta1, omb1, absmax, sumsq);
     } else {
         // up to four chunks in flight per lane (blocks of up to 256 elements have one chunk per lane). With the
