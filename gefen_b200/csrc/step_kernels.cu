@@ -615,7 +615,7 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
         // up to four chunks in flight per lane (blocks of up to 256 elements have one chunk per lane). With the
         // kernels of the two block kinds compiled apart, four fit the registers of both (measured on blocks of
         // 512 / 1024 bf16 elements: 0.549 -> 0.599 / 0.566 -> 0.620 of the copy bandwidth against one in flight)
-        constexpr int U = 4;
+        constexpr int U = (sizeof(S) == 4 && !FULL) ? 2 : 4;   // (fp32 blocks that share a warp: see vec_max_threads)
         // (a separate loop without bounds tests for the complete groups was measured: slower, it
         // costs registers)
         for (int c0 = lane; c0 < nchunks; c0 += LANES * U)
@@ -767,7 +767,11 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
 // fp32, whose wider chunks need the full 128.
 // The variant that averages gradients over NVLink holds more loads in flight per thread and is not
 // bound by occupancy: sixteen warps of 128 registers for every type.
-template <typename S, int GSRC> __host__ __device__ constexpr int vec_max_threads() {
+// fp32 tensors whose blocks share a warp are bound by the latency of their loads: there twenty warps of 96
+// registers with two chunks in flight beat sixteen of 128 with four (measured on 768-element blocks: 0.725
+// against 0.703 of the copy bandwidth).
+template <typename S, int GSRC, bool FULL> __host__ __device__ constexpr int vec_max_threads() {
+    if (sizeof(S) == 4 && GSRC == 0 && !FULL) return 640;
     return (sizeof(S) == 2 && GSRC != 1) ? 640 : 512;
 }
 
@@ -775,7 +779,7 @@ template <typename S, int GSRC> __host__ __device__ constexpr int vec_max_thread
 // otherwise none has. The two kinds are separate kernels so that each is compiled (registers, code size) for
 // its own loop structure.
 template <typename S, int GSRC, bool FULL>
-__global__ void __launch_bounds__(vec_max_threads<S, GSRC>(), 1) step_vec_kernel(const __grid_constant__ StepLaunch L,
+__global__ void __launch_bounds__(vec_max_threads<S, GSRC, FULL>(), 1) step_vec_kernel(const __grid_constant__ StepLaunch L,
                                                            const __grid_constant__ gefen_b200_step_tensor_t single) {
     extern __shared__ __align__(128) unsigned char smem[];
     SmemView s;
@@ -1148,7 +1152,7 @@ static int launch_vec_variant(StepLaunch L, const gefen_b200_step_tensor_t& sing
     // a warp stages one unit: one long block, or the 32 / lanes shorter blocks that share the warp
     // (max_period: the largest unit of the launch, see unit_elements)
     const long long stage_bytes = (max_period > 256 ? max_period : 256) * 4;
-    int max_warps = vec_max_threads<S, GSRC>() / 32;
+    int max_warps = vec_max_threads<S, GSRC, FULL>() / 32;
     if (warps_override() > 0 && warps_override() < max_warps) max_warps = warps_override();
     int warps = static_cast<int>((kMaxSmem - kStaticSmemSlack - kSmemWs - kSmemRep) / stage_bytes);
     if (warps > max_warps) warps = max_warps;
