@@ -236,3 +236,54 @@ def test_dtensor_like_parameters_and_async_gradients(cuda_device):
     torch.cuda.synchronize()
     assert torch.equal(sharded.to_local(), plain.detach())
     assert torch.equal(opt_sharded.state[sharded]["m_codebook"], opt_plain.state[plain]["m_codebook"])
+
+
+def test_steady_state_path_equals_the_general_path(cuda_device):
+    """A training loop whose tensors stay at the same addresses takes `Gefen._step_steady` (only the step
+    counters and the scalars derived from them are refreshed). Same results as the general path, also across the
+    events that must send a call back to it: a learning-rate change (stays steady, new scalars), gradients in
+    new tensors, a gradient that disappears and comes back, a parameter that joins late."""
+    from gefen_b200 import Gefen
+
+    dtype = torch.bfloat16
+
+    def build():
+        _, params = _setup(dtype, cuda_device)
+        for p in params:
+            p.grad = torch.zeros_like(p)
+        return params, Gefen([("p{}".format(i), p) for i, p in enumerate(params)], lr=1e-3, weight_decay=0.1)
+
+    fast_params, fast = build()
+    slow_params, slow = build()
+    took_steady = 0
+    for step in range(12):
+        grads = [g.to(cuda_device) for g in _grads(step, dtype)]
+        for k, (params, opt) in enumerate(((fast_params, fast), (slow_params, slow))):
+            for i, (p, g) in enumerate(zip(params, grads)):
+                if step in (5, 6) and i == 2:
+                    p.grad = None                      # a tensor without a gradient for two steps
+                elif step in (3, 8) or p.grad is None or (step < 2 and i == 4):
+                    p.grad = g.clone()                 # gradients in new tensors
+                else:
+                    p.grad.copy_(g)                    # the steady state: same tensors, new values
+            if step < 2:
+                params[4].grad = None                  # a parameter that joins at step 2
+            if step == 7:
+                for group in opt.param_groups:
+                    group["lr"] = 5e-4
+            if k == 1:
+                opt._steady = None                     # the general path, every step
+            else:
+                before = opt._steady
+            opt.step()
+            if k == 0 and before is not None and opt._steady is before:
+                took_steady += 1
+        torch.cuda.synchronize()
+        for p, q in zip(fast_params, slow_params):
+            assert torch.equal(p.detach(), q.detach()), step
+    assert took_steady >= 4        # (the steady path did run: it leaves its cache object in place)
+    for p, q in zip(fast_params, slow_params):
+        a, b = fast.state[p], slow.state[q]
+        assert a["step"] == b["step"]
+        for key in ("m_codebook", "m_magnitude", "vmean"):
+            assert torch.equal(a[key], b[key])
