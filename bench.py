@@ -295,6 +295,19 @@ def run_sharded_arm(args, cfg, rank, world, local_rank):
     except torch.OutOfMemoryError as exc:   # the check is an extra: the measured line must survive it
         result["n_vs_1"] = {"error": "out of memory in the check: {}".format(str(exc)[:120])}
 
+    # for scale: NCCL's own all-reduce of one buffer of this size (the traffic of reduce-scatter + all-gather, nothing
+    # computed), in place on the gradient buffer, whose values are not needed any more
+    try:
+        for _ in range(2):
+            dist.all_reduce(opt.flat_grad)
+        nccl_ms = timed(lambda: dist.all_reduce(opt.flat_grad), 5)
+        t = torch.tensor([nccl_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        breakdown["nccl_all_reduce_of_one_buffer_ms"] = float(t)
+    except RuntimeError as exc:
+        breakdown["nccl_all_reduce_of_one_buffer_ms"] = None
+        breakdown["nccl_all_reduce_error"] = str(exc)[:120]
+
     e2e = None
     if not args.no_e2e:
         # end to end at N ranks: every rank's gradients come from its own pinned host buffer and the full
@@ -953,6 +966,16 @@ def main():
         if "breakdown" in result:
             line["breakdown_ms"] = result["breakdown"]
             line["gpu_launches"] = result["breakdown"].get("kernel_launches_per_step", 0) * args.steps
+            # N > 1: the step kernels carry both collectives and the links bound them. achieved = the bytes a rank
+            # must move over NVLink per step (the larger direction) / the step time; peak = the measured rate of a
+            # peer copy on this pool (one direction; nominal 900 GB/s)
+            wire = result["breakdown"].get("wire_bytes_per_rank")
+            if wire:
+                line["roofline"] = {"bound": "nvlink", "kernel": "step kernels with both collectives on their accesses",
+                                    "achieved": result["breakdown"]["achieved_link_gbs"], "peak": 770.0,
+                                    "peak_kind": "measured peer copy, one direction", "unit": "GB/s",
+                                    "frac": result["breakdown"]["achieved_link_gbs"] / 770.0, "traffic": None,
+                                    "algorithmic_bytes_per_launch": max(wire["egress"], wire["ingress"])}
         if "n_vs_1" in result:
             line["n_vs_1"] = result["n_vs_1"]
         if "reference_cuda" in result:
