@@ -290,15 +290,16 @@ class Zero1Gefen:
                                                                     "all_gather")
         # The gradient buffer is symmetric as well unless fused_reduce_scatter=False. Averaging inside the step
         # kernels is the default when the buffer has a multicast address (one switch-reduced load per chunk).
-        # Over plain peer loads it must be asked for (fused_reduce_scatter=True or GEFEN_B200_ZERO1_FUSED_RS=1):
-        # NVLink's load latency then bounds the kernel, more so with more sources per element; that form is
-        # kept for its exactness (fp32 sum in rank order).
+        # Over plain peer loads (fused_reduce_scatter=True or GEFEN_B200_ZERO1_FUSED_RS=1) NVLink's load latency
+        # bounds the kernel, more so with more sources per element: that form, exact (fp32 sum in rank order),
+        # is taken by default only with two ranks and no room for the pushed form's receive buffer (see below;
+        # GEFEN_B200_ZERO1_FUSED_RS=0 keeps NCCL's reduce-scatter there).
         self.flat_grad, grad_ptrs, grad_mc = self._allocate_flat(False if fused_reduce_scatter is False else None,
                                                                  "GEFEN_B200_ZERO1_SYMMETRIC_GRADS", "reduce_scatter")
         if not want_mc:
             param_mc = grad_mc = 0
-        peer_rs = fused_reduce_scatter if fused_reduce_scatter is not None else \
-            os.environ.get("GEFEN_B200_ZERO1_FUSED_RS", "0") != "0"
+        env_peer = os.environ.get("GEFEN_B200_ZERO1_FUSED_RS", "auto")
+        peer_rs = fused_reduce_scatter if fused_reduce_scatter is not None else env_peer not in ("0", "auto")
         mc_rs = os.environ.get("GEFEN_B200_ZERO1_MULTICAST_RS", "1") != "0"
         # peers in ring order starting after this rank, so that concurrent ranks write to different GPUs
         self._peer_deltas = None if param_ptrs is None else np.array(
@@ -317,6 +318,12 @@ class Zero1Gefen:
         self._push_views = []
         if self._grad_deltas is None and grad_ptrs is not None and fused_reduce_scatter is None:
             self._setup_push(push_reduce_scatter, grad_ptrs)
+            # Two ranks without room for the receive buffer (a model that fills the GPUs): averaging by peer
+            # loads inside the step kernels still beats NCCL's reduce-scatter in front of them (Llama-32B:
+            # 113.7 ms against 118.5 ms per step) and needs no memory.
+            if self._recv is None and self.world == 2 and env_peer == "auto" and push_reduce_scatter is None:
+                self._grad_deltas = np.array([grad_ptrs[r] - grad_ptrs[self.rank] for r in range(self.world)],
+                                             dtype=np.int64)
         with torch.no_grad():
             for t, (n, p) in enumerate(self.named):
                 off = self.layout.tensor_offset[t]
