@@ -295,19 +295,6 @@ def run_sharded_arm(args, cfg, rank, world, local_rank):
     except torch.OutOfMemoryError as exc:   # the check is an extra: the measured line must survive it
         result["n_vs_1"] = {"error": "out of memory in the check: {}".format(str(exc)[:120])}
 
-    # for scale: NCCL's own all-reduce of one buffer of this size (the traffic of reduce-scatter + all-gather, nothing
-    # computed), in place on the gradient buffer, whose values are not needed any more
-    try:
-        for _ in range(2):
-            dist.all_reduce(opt.flat_grad)
-        nccl_ms = timed(lambda: dist.all_reduce(opt.flat_grad), 5)
-        t = torch.tensor([nccl_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        breakdown["nccl_all_reduce_of_one_buffer_ms"] = float(t)
-    except RuntimeError as exc:
-        breakdown["nccl_all_reduce_of_one_buffer_ms"] = None
-        breakdown["nccl_all_reduce_error"] = str(exc)[:120]
-
     e2e = None
     if not args.no_e2e:
         # end to end at N ranks: every rank's gradients come from its own pinned host buffer and the full
@@ -323,19 +310,55 @@ def run_sharded_arm(args, cfg, rank, world, local_rank):
         everyone = torch.tensor([1.0 if host_g is not None else 0.0], device=device)
         dist.all_reduce(everyone, op=dist.ReduceOp.MIN)
         if float(everyone) > 0:
+            # The read-back of step k runs on its own stream and overlaps the gradients of step k + 1 coming in
+            # (PCIe carries both directions at once); step k + 1 starts only when the read-back of step k has
+            # finished on this rank, and its opening barrier makes that true for every rank before any rank's
+            # kernels store new parameters into the others' buffers.
+            main = torch.cuda.current_stream(device)
+            out = torch.cuda.Stream(device)
+            left = [None]
+
             def e2e_step():
                 opt.flat_grad.copy_(host_g, non_blocking=True)
+                if left[0] is not None:
+                    main.wait_event(left[0])
                 step()
-                host_p.copy_(opt.flat_param, non_blocking=True)
+                stepped = torch.cuda.Event()
+                stepped.record(main)
+                out.wait_event(stepped)
+                with torch.cuda.stream(out):
+                    host_p.copy_(opt.flat_param, non_blocking=True)
+                    left[0] = torch.cuda.Event()
+                    left[0].record(out)
 
-            e2e_step()
+            def e2e_steps(k):
+                for _ in range(k):
+                    e2e_step()
+                main.wait_event(left[0])   # the timed region ends when the last parameters are on the host
+
+            e2e_steps(1)
             dist.barrier()
-            e2e_ms = timed(e2e_step, max(2, min(args.steps, 5)))
+            k = max(2, min(args.steps, 5))
+            e2e_ms = timed(lambda: e2e_steps(k), 1) / k
             t = torch.tensor([e2e_ms], device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             nbytes = opt.flat_grad.numel() * opt.flat_grad.element_size()
             e2e = {"value": float(t), "unit": "ms", "h2d_bytes_per_step": nbytes * world,
-                   "d2h_bytes_per_step": nbytes * world, "note": "per rank {} bytes each way".format(nbytes)}
+                   "d2h_bytes_per_step": nbytes * world, "note": "per rank {} bytes each way".format(nbytes),
+                   "host_params_match_device": bool(torch.equal(host_p[:1 << 20], opt.flat_param[:1 << 20].cpu()))}
+    # for scale: NCCL's own all-reduce of one buffer of this size (the traffic of reduce-scatter + all-gather, nothing
+    # computed), in place on the gradient buffer, whose values are not needed any more (last of all for that reason)
+    try:
+        for _ in range(2):
+            dist.all_reduce(opt.flat_grad)
+        nccl_ms = timed(lambda: dist.all_reduce(opt.flat_grad), 5)
+        t = torch.tensor([nccl_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        breakdown["nccl_all_reduce_of_one_buffer_ms"] = float(t)
+    except RuntimeError as exc:
+        breakdown["nccl_all_reduce_of_one_buffer_ms"] = None
+        breakdown["nccl_all_reduce_error"] = str(exc)[:120]
+
     return result, e2e
 
 
