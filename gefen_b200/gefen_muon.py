@@ -16,7 +16,7 @@ import torch
 import torch.nn as nn
 
 from . import _lib
-from .gefen import Gefen, _local, automatic_partition_view
+from .gefen import Gefen
 from .newton_schulz import orthogonalize_all
 
 EPS = 1e-7

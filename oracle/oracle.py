@@ -9,11 +9,9 @@ from __future__ import annotations
 
 import ctypes
 import math
-import os
 import subprocess
 from pathlib import Path
 
-import numpy as np
 import torch
 
 _HERE = Path(__file__).resolve().parent

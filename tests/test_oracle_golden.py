@@ -2,7 +2,6 @@
 tests/golden/make_golden.py from the reference's own code)."""
 from pathlib import Path
 
-import pytest
 import torch
 
 from tests.util import make_grad, make_param, rel_l2

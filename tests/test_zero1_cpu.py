@@ -6,7 +6,6 @@ import socket
 import sys
 from pathlib import Path
 
-import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
