@@ -752,7 +752,7 @@ def run_microbench(spec: str, steps: int, warmup: int):
     Small enough for profiler captures; prints one JSON line."""
     from gefen_b200.kernels.automatic_gefen_fused import automatic_gefen_fused_update_from_vmean_cuda
 
-    if spec.split(":")[0] in ("gemm", "gram", "hist", "scan", "ns", "dp", "lloyd"):
+    if spec.split(":")[0] in ("gemm", "gram", "hist", "scan", "ns", "dp", "lloyd", "vmean", "muonmom"):
         return run_microbench_other(spec, steps, warmup)
     name, period, blocks = spec.split(":")
     period, blocks = int(period), int(blocks)
@@ -803,6 +803,37 @@ def run_microbench_other(spec: str, steps: int, warmup: int):
         flops = ns_flops((rows, cols))
         out.update({"ms": res["tcgen05"], "tflops": flops / res["tcgen05"] / 1e9, "torch_ms": res["torch"],
                     "torch_tflops": flops / res["torch"] / 1e9})
+        print(json.dumps(out))
+        return
+    if parts[0] in ("vmean", "muonmom"):
+        # vmean:dtype:blocks:period - the stand-alone second-moment kernel (one read of the gradient);
+        # muonmom:dtype:blocks:period - GefenMuon's 8-bit momentum step (codes in and out, gradient in, the
+        # dequantised momentum out: 2 + 2 s bytes per element)
+        from gefen_b200.kernels.automatic_gefen_fused import automatic_gefen_muon_momentum_cuda
+        from gefen_b200.kernels.automatic_vmean import automatic_vmean_update_cuda
+
+        dtype = {"bf16": torch.bfloat16, "f32": torch.float32, "f16": torch.float16}[parts[1]]
+        blocks, period = int(parts[2]), int(parts[3])
+        g = (torch.randn(blocks, period, generator=gen, device=dev) * 1e-3).to(dtype)
+        esize = g.element_size()
+        if parts[0] == "vmean":
+            v = (torch.rand(blocks, 1, generator=gen, device=dev) * 1e-6 + 1e-9).to(dtype)
+            fn = lambda: automatic_vmean_update_cuda(v, g, 0.999)   # noqa: E731
+            nbytes = blocks * period * esize + blocks * 2 * esize
+        else:
+            inner = torch.sort(torch.tanh(torch.randn(254, generator=gen, device=dev) * 0.6)).values
+            cb = torch.cat([torch.tensor([-1.0], device=dev), inner, torch.tensor([1.0], device=dev)]).float().contiguous()
+            codes = torch.randint(0, 256, (blocks, period), dtype=torch.uint8, generator=gen, device=dev)
+            mag = (torch.rand(blocks, 1, generator=gen, device=dev) * 2e-3).to(dtype)
+            upd = torch.empty_like(g)
+            fn = lambda: automatic_gefen_muon_momentum_cuda(g, codes, mag, cb, upd, False, 0.95)   # noqa: E731
+            nbytes = blocks * period * (2 + 2 * esize) + blocks * 2 * esize
+        for _ in range(max(warmup, 3)):
+            fn()
+        ms = timed(fn, steps)
+        peak, kind = measured_peaks()
+        out.update({"ms": ms, "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / ms / 1e6,
+                    "frac_of_{}_peak".format(kind): nbytes / ms / 1e6 / peak})
         print(json.dumps(out))
         return
     if parts[0] == "dp":

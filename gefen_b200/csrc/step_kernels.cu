@@ -541,6 +541,62 @@ __device__ __forceinline__ void second_pass_common(const StepLaunch& L, const Sm
     }
 }
 
+// The same loop for GefenMuon's momentum step (finite block): the dequantised new momentum, Nesterov-blended
+// with the gradient when asked (torch: m.mul_(momentum).add_(g, alpha=1-momentum) on the rounded momentum,
+// reference gefen_muon.py:312-314; alpha travels in the descriptor's beta2), goes where the Gefen step keeps
+// the parameters. The gradient chunk of the next iteration is requested while this one is encoded.
+template <typename S, bool NESTEROV>
+__device__ __forceinline__ void second_pass_muon(const SmemView& s, const float* rep, const float4* stage_a,
+                                                 const float4* stage_b, uint2* codes_out, const S* g_blk, S* out_blk,
+                                                 int lane, int LANES, int nchunks, float absmax, float rinv,
+                                                 float beta1, float alpha) {
+    const float magic = lut_magic(s.lut);
+    Chunk<S> gnext;
+    if (NESTEROV && lane < nchunks) gnext.load(g_blk, lane);
+    for (int c = lane; c < nchunks; c += LANES) {
+        Chunk<S> graw = gnext;
+        if (NESTEROV && c + LANES < nchunks) gnext.load(g_blk, c + LANES);
+        float m[8];
+        staged_momenta(stage_a, stage_b, c, m);
+        uint32_t code[8];
+        uint32_t any = 0u;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float x = div_by_block_constant(m[i], absmax, rinv);
+            code[i] = lut_query_shared(x, magic);
+            any |= code[i];
+        }
+        if (any & kLutSlowBit) {   // rare: a cell with two thresholds, or values above the last entry
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (code[i] & kLutSlowBit) {
+                    const float x = div_by_block_constant(m[i], absmax, rinv);
+                    code[i] = static_cast<uint32_t>(entry_exact(x, s.thr, s.cb, s.k));
+                }
+            }
+        }
+        uint2 cw;
+        cw.x = __byte_perm(__byte_perm(code[0], code[1], 0x0040), __byte_perm(code[2], code[3], 0x0040), 0x5410);
+        cw.y = __byte_perm(__byte_perm(code[4], code[5], 0x0040), __byte_perm(code[6], code[7], 0x0040), 0x5410);
+        codes_out[c] = cw;
+        float q[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = rep[code[i] * kRepCopies] * absmax;
+        if (NESTEROV) {
+            float g[8];
+            graw.unpack(g);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float m1 = ScalarIO<S>::round(ScalarIO<S>::round(q[i]) * beta1);
+                q[i] = fmaf(alpha, g[i], m1);
+            }
+        }
+        Chunk<S> out;
+        out.pack(q);
+        out.store(out_blk, c);
+    }
+}
+
 // One warp, one unit: 32 / LANES consecutive blocks of t.period = 8 * nchunks elements, LANES lanes
 // each (LANES = lanes_per_block(t.period), uniform over the warp; FULL fixes it to 32 at compile
 // time, for blocks of more than 1024 elements). A block's slice of `stage` holds period floats: the first halves of all chunks, then the
@@ -681,8 +737,16 @@ __device__ __forceinline__ void warp_block_step(const gefen_b200_step_tensor_t& 
         __syncwarp();  // the staging slice is free for this warp's next block
         return;
     }
-    // Everything else (GefenMuon's momentum, lr == 0, blocks that are all zero or hold NaN or Inf, magnitudes
-    // outside the range of the reciprocal): the general loop.
+    if (GSRC == 0 && muon && __all_sync(0xffffffffu, fastdiv || !valid)) {
+        if (nesterov) second_pass_muon<S, true>(s, rep, stage_a, stage_b, codes_out, g_blk, p_blk, lane, LANES, nchunks, absmax,
+                                                rinv, beta1, nesterov_alpha);
+        else second_pass_muon<S, false>(s, rep, stage_a, stage_b, codes_out, g_blk, p_blk, lane, LANES, nchunks, absmax, rinv,
+                                        beta1, nesterov_alpha);
+        __syncwarp();  // the staging slice is free for this warp's next block
+        return;
+    }
+    // Everything else (lr == 0, blocks that are all zero or hold NaN or Inf, magnitudes outside the range of the
+    // reciprocal, GefenMuon's momentum over averaged gradients): the general loop.
     for (int c = lane; c < nchunks; c += LANES) {
         Chunk<S> praw = pnext;
         if (load_p && c + LANES < nchunks) pnext.load(p_blk, c + LANES);
