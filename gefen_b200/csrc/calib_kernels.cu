@@ -304,6 +304,91 @@ __global__ void __launch_bounds__(kThreads) regroup_sums_kernel(const double* __
     }
 }
 
+// ---- the same three kernels for all candidate periods of a scan at once (blockIdx.y = candidate): a scan of 72
+// candidates is then a dozen launches instead of two hundred. The arithmetic per candidate, and therefore every
+// score, is that of the single-candidate kernels above: an output of the regrouping depends on no launch
+// parameter, and the partial sums are cut by the candidate's own number of partials, not by the grid.
+struct ScanCandidate {
+    long long src;        // offset (in doubles from the scratch base) of the sums this candidate is regrouped from
+    long long dst;        // offset of its own sums
+    long long ratio;      // period / parent period; 0: the sums are the base sums themselves, nothing to regroup
+    long long nb;         // blocks of this period
+    long long partial;    // offset of its partial sums (n_partial doubles)
+    double period;
+    int n_partial;
+    int stats;            // index of its pair of outputs
+};
+
+__global__ void __launch_bounds__(kThreads) regroup_sums_batch_kernel(double* __restrict__ scratch,
+                                                                      const ScanCandidate* __restrict__ table, int first) {
+    const ScanCandidate c = table[first + blockIdx.y];
+    if (c.ratio == 0) return;
+    const double* in = scratch + c.src;
+    double* out = scratch + c.dst;
+    const long long ratio = c.ratio, num_out = c.nb;
+    const int lane = threadIdx.x & 31;
+    if (ratio >= 64) {
+        const long long w0 = static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+        const long long stride = static_cast<long long>(gridDim.x) * kWarps;
+        for (long long j = w0; j < num_out; j += stride) {
+            const double* src = in + j * ratio;
+            double acc = 0.0;
+            for (long long i = lane; i < ratio; i += 32) acc += src[i];
+            acc = warp_sum(acc);
+            if (lane == 0) out[j] = acc;
+        }
+    } else {
+        const long long t0 = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+        const long long stride = static_cast<long long>(gridDim.x) * kThreads;
+        for (long long j = t0; j < num_out; j += stride) {
+            const double* src = in + j * ratio;
+            double acc = 0.0;
+            for (long long i = 0; i < ratio; ++i) acc += src[i];
+            out[j] = acc;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) adjacent_diff_partial_batch_kernel(double* __restrict__ scratch,
+                                                                               const ScanCandidate* __restrict__ table) {
+    __shared__ double red[kWarps];
+    const ScanCandidate c = table[blockIdx.y];
+    if (static_cast<int>(blockIdx.x) >= c.n_partial) return;
+    const double* sums = scratch + c.dst;
+    const long long num_pairs = c.nb - 1;
+    const double period = c.period;
+    const long long per_cta = (num_pairs + c.n_partial - 1) / c.n_partial;
+    const long long begin = static_cast<long long>(blockIdx.x) * per_cta;
+    long long end = begin + per_cta;
+    if (end > num_pairs) end = num_pairs;
+    double acc = 0.0;
+    for (long long j = begin + threadIdx.x; j < end; j += kThreads) {
+        const double cur = sums[j] / period;
+        const double nxt = sums[j + 1] / period;
+        acc += fabs(nxt - cur);
+    }
+    acc = warp_sum(acc);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int w = 0; w < kWarps; ++w) t += red[w];
+        scratch[c.partial + blockIdx.x] = t;
+    }
+}
+
+__global__ void adjacent_diff_final_batch_kernel(const double* __restrict__ scratch, const ScanCandidate* __restrict__ table,
+                                                 const unsigned long long* __restrict__ invalid,
+                                                 double* __restrict__ stats) {
+    if (threadIdx.x != 0) return;
+    const ScanCandidate c = table[blockIdx.x];
+    const double* partial = scratch + c.partial;
+    double t = 0.0;
+    for (int i = 0; i < c.n_partial; ++i) t += partial[i];
+    stats[2 * c.stats] = t / static_cast<double>(c.nb - 1);
+    stats[2 * c.stats + 1] = static_cast<double>(*invalid);
+}
+
 // Mean within-block variance / coefficient of variation of x (= v or v*v), fp32 sums
 // (reference: period_variance_kernel.cu:13-106). One warp per block.
 template <typename S, bool SQUARED, bool COV>
@@ -564,6 +649,12 @@ static int check_flat(const void* values, int dtype, int64_t numel, int64_t peri
     }
 
 constexpr int kMaxPartials = 1024;
+static int partials_for(int64_t pairs) {
+    int n_partial = static_cast<int>((pairs + 4095) / 4096);
+    if (n_partial > kMaxPartials) n_partial = kMaxPartials;
+    if (n_partial < 1) n_partial = 1;
+    return n_partial;
+}
 
 static int launch_block_logsums(const void* values, int dtype, int64_t numel, int64_t period, bool squared, double eps,
                                 double* sums, unsigned long long* invalid, cudaStream_t stream) {
@@ -583,9 +674,7 @@ static int launch_block_logsums(const void* values, int dtype, int64_t numel, in
 static int launch_adjacent_score(const double* sums, int64_t nb, int64_t period, const unsigned long long* invalid,
                                  double* partial, double* stats, cudaStream_t stream) {
     const int64_t pairs = nb - 1;
-    int n_partial = static_cast<int>((pairs + 4095) / 4096);
-    if (n_partial > kMaxPartials) n_partial = kMaxPartials;
-    if (n_partial < 1) n_partial = 1;
+    const int n_partial = partials_for(pairs);
     adjacent_diff_partial_kernel<<<n_partial, kThreads, 0, stream>>>(sums, pairs, static_cast<double>(period), partial);
     GEFEN_CHECK_CUDA(cudaGetLastError());
     adjacent_diff_final_kernel<<<1, 32, 0, stream>>>(partial, n_partial, static_cast<double>(pairs), invalid, stats);
@@ -614,9 +703,14 @@ struct ScanPlan {
     std::vector<int> order;        // candidate indices by ascending period
     std::vector<int> parent;       // per candidate: index of the parent candidate, -1 = base
     std::vector<int64_t> offset;   // per candidate: offset of its sums (== base offset if period == base)
+    std::vector<int> level;        // per candidate: regrouping steps between the base sums and its own
+    std::vector<int> n_partial;    // per candidate: partial sums of its score
+    std::vector<int64_t> partial;  // per candidate: offset of those
+    int64_t table_offset;          // the device copy of the candidates' descriptors
     int64_t base_offset;
     int64_t total;
 };
+
 
 static ScanPlan make_scan_plan(int64_t numel, const int64_t* periods, int n) {
     ScanPlan plan;
@@ -639,6 +733,18 @@ static ScanPlan make_scan_plan(int64_t numel, const int64_t* periods, int n) {
         plan.offset[i] = cursor;
         cursor += numel / periods[i];
     }
+    plan.level.assign(n, 0);
+    plan.n_partial.assign(n, 1);
+    plan.partial.assign(n, 0);
+    for (int oi = 0; oi < n; ++oi) {   // ascending periods: a parent comes before its children
+        const int i = plan.order[oi];
+        plan.level[i] = periods[i] == plan.base ? 0 : (plan.parent[i] < 0 ? 1 : plan.level[plan.parent[i]] + 1);
+        plan.n_partial[i] = partials_for(numel / periods[i] - 1);
+        plan.partial[i] = cursor;
+        cursor += plan.n_partial[i];
+    }
+    plan.table_offset = cursor;
+    cursor += (static_cast<int64_t>(n) * static_cast<int64_t>(sizeof(ScanCandidate)) + 7) / 8;
     plan.total = cursor;
     return plan;
 }
@@ -760,28 +866,56 @@ int gefen_b200_period_scan(const void* values, int dtype, int64_t numel, int inp
     }
     const ScanPlan plan = make_scan_plan(numel, host_periods, n_periods);
     unsigned long long* invalid = reinterpret_cast<unsigned long long*>(scratch);
-    double* partial = scratch + 1;
     GEFEN_CHECK_CUDA(cudaMemsetAsync(invalid, 0, sizeof(unsigned long long), stream));
     // the only pass over the tensor: log sums at the base granularity
     int rc = launch_block_logsums(values, dtype, numel, plan.base, input_is_squared != 0, epsilon,
                                   scratch + plan.base_offset, invalid, stream);
     if (rc != GEFEN_B200_OK) return rc;
-    for (int oi = 0; oi < n_periods; ++oi) {
-        const int i = plan.order[oi];
+    // the candidates in the order of their launches: by regrouping level (a parent is one level above its
+    // children), so that each level is one launch over a run of the table
+    std::vector<int> exec(plan.order);
+    std::stable_sort(exec.begin(), exec.end(), [&](int x, int y) { return plan.level[x] < plan.level[y]; });
+    std::vector<ScanCandidate> table(n_periods);
+    int max_level = 0, max_partial = 1;
+    for (int e = 0; e < n_periods; ++e) {
+        const int i = exec[e];
         const int64_t p = host_periods[i];
-        const int64_t nb = numel / p;
-        double* sums = scratch + plan.offset[i];
-        if (p != plan.base) {
-            const int64_t q = plan.parent[i] < 0 ? plan.base : host_periods[plan.parent[i]];
-            const double* src = scratch + (plan.parent[i] < 0 ? plan.base_offset : plan.offset[plan.parent[i]]);
-            const int64_t ratio = p / q;
-            const int grid = ratio >= 64 ? persistent_grid(nb, kWarps, 8) : persistent_grid(nb, kThreads, 8);
-            regroup_sums_kernel<<<grid, kThreads, 0, stream>>>(src, ratio, nb, sums);
-            GEFEN_CHECK_CUDA(cudaGetLastError());
-        }
-        rc = launch_adjacent_score(sums, nb, p, invalid, partial, stats + 2 * i, stream);
-        if (rc != GEFEN_B200_OK) return rc;
+        ScanCandidate& c = table[e];
+        const int64_t q = plan.parent[i] < 0 ? plan.base : host_periods[plan.parent[i]];
+        c.src = plan.parent[i] < 0 ? plan.base_offset : plan.offset[plan.parent[i]];
+        c.dst = plan.offset[i];
+        c.ratio = p == plan.base ? 0 : p / q;
+        c.nb = numel / p;
+        c.partial = plan.partial[i];
+        c.period = static_cast<double>(p);
+        c.n_partial = plan.n_partial[i];
+        c.stats = i;
+        max_level = std::max(max_level, plan.level[i]);
+        max_partial = std::max(max_partial, c.n_partial);
     }
+    ScanCandidate* dev_table = reinterpret_cast<ScanCandidate*>(scratch + plan.table_offset);
+    GEFEN_CHECK_CUDA(cudaMemcpyAsync(dev_table, table.data(), sizeof(ScanCandidate) * n_periods, cudaMemcpyHostToDevice, stream));
+    for (int level = 1; level <= max_level; ++level) {
+        int first = -1, count = 0;
+        int64_t most = 1;
+        for (int e = 0; e < n_periods; ++e) {
+            if (plan.level[exec[e]] != level) continue;
+            if (first < 0) first = e;
+            ++count;
+            const int64_t groups = table[e].ratio >= 64 ? (table[e].nb + kWarps - 1) / kWarps : (table[e].nb + kThreads - 1) / kThreads;
+            most = std::max(most, groups);
+        }
+        if (count == 0) continue;
+        const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+        const dim3 grid(static_cast<unsigned>(std::min(most, cap)), static_cast<unsigned>(count));
+        regroup_sums_batch_kernel<<<grid, kThreads, 0, stream>>>(scratch, dev_table, first);
+        GEFEN_CHECK_CUDA(cudaGetLastError());
+    }
+    adjacent_diff_partial_batch_kernel<<<dim3(static_cast<unsigned>(max_partial), static_cast<unsigned>(n_periods)), kThreads, 0,
+                                         stream>>>(scratch, dev_table);
+    GEFEN_CHECK_CUDA(cudaGetLastError());
+    adjacent_diff_final_batch_kernel<<<n_periods, 32, 0, stream>>>(scratch, dev_table, invalid, stats);
+    GEFEN_CHECK_CUDA(cudaGetLastError());
     return GEFEN_B200_OK;
 }
 
