@@ -23,16 +23,19 @@ import torch
 from .gefen import Gefen
 
 
-def cut_buckets(numels, element_sizes, periods, n_buckets):
-    """Cuts a model, in parameter order, into at most `n_buckets` runs of about equal bytes. A tensor larger
-    than what is left of a bucket is cut at a block boundary (the blocks of a tensor are independent in
-    the step), so that no bucket is much larger than the others: the first bucket's copy-in and the last
-    bucket's copy-out are the parts of a step that nothing overlaps. Period-1 tensors (tiny) stay whole.
+def cut_buckets(numels, element_sizes, periods, n_buckets, weights=None):
+    """Cuts a model, in parameter order, into at most `n_buckets` runs of about equal bytes (or, with
+    `weights`, of bytes in proportion to one weight per bucket). A tensor larger than what is left of a bucket
+    is cut at a block boundary (the blocks of a tensor are independent in the step), so that no bucket is much
+    larger than its share. Period-1 tensors (tiny) stay whole.
     Returns a list of buckets; a bucket is a list of (parameter index, first block, end block, whole
     tensor?) in which a parameter appears at most once."""
     sizes = [n * e for n, e in zip(numels, element_sizes)]
-    target = max(1, sum(sizes) // max(1, n_buckets))
-    buckets, cur, room = [], [], target
+    n_buckets = max(1, n_buckets)
+    if weights is None:
+        weights = [1.0] * n_buckets
+    targets = [max(1, int(sum(sizes) * w / sum(weights))) for w in weights]
+    buckets, cur, room = [], [], targets[0]
     for i, (numel, esize, period) in enumerate(zip(numels, element_sizes, periods)):
         nb = numel // period if period > 1 else 1
         block_bytes = (period if period > 1 else numel) * esize
@@ -48,7 +51,7 @@ def cut_buckets(numels, element_sizes, periods, n_buckets):
             b0 = b1
             if room <= 0 and not last:
                 buckets.append(cur)
-                cur, room = [], target
+                cur, room = [], targets[len(buckets)]
     if cur:
         buckets.append(cur)
     return buckets
@@ -84,8 +87,13 @@ class HostStreamedGefen:
 
     def _build_buckets(self) -> None:
         periods = [int(self.opt.state[p]["automatic_period"]) for p in self.params]
+        # The first bucket's copy-in and the last bucket's copy-out are the parts of a step that nothing
+        # overlaps: the buckets at both ends are small (1/8, 1/4, 1/2 of the others).
+        n = self.n_buckets
+        ramp = [0.125, 0.25, 0.5]
+        weights = ramp + [1.0] * (n - 6) + ramp[::-1] if n >= 8 else None
         self.buckets = cut_buckets([p.numel() for p in self.params], [p.element_size() for p in self.params],
-                                   periods, self.n_buckets)
+                                   periods, n, weights)
         buckets = self.buckets
         self._ids = [set(id(self.params[i]) for i, _, _, _ in b) for b in buckets]
         self._ranges = [{id(self.params[i]): (b0, b1) for i, b0, b1, whole in b if not whole} for b in buckets]

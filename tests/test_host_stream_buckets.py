@@ -72,3 +72,15 @@ def test_push_plan_covers_every_owned_piece_once(world, n_buckets):
             blocks = pc.numel // used[i] if used[i] > 1 else 1
             r = runs[i]
             assert r[0][0] == 0 and r[-1][1] == blocks and all(a[1] == b[0] for a, b in zip(r, r[1:]))
+
+
+def test_cut_buckets_follows_weights():
+    numels = [math.prod(s) for s in SHAPES]
+    weights = [0.125, 0.25, 0.5, 1, 1, 1, 1, 1, 1, 1, 0.5, 0.25, 0.125]
+    buckets = cut_buckets(numels, [2] * len(numels), PERIODS, len(weights), weights)
+    sizes = [sum((b1 - b0) * (PERIODS[i] if PERIODS[i] > 1 else numels[i]) * 2 for i, b0, b1, _ in b) for b in buckets]
+    assert len(buckets) == len(weights)
+    total = sum(sizes)
+    for size, w in zip(sizes[:-1], weights[:-1]):   # a bucket closes with the block that fills it: up to one block over
+        assert 0 <= size - total * w / sum(weights) <= 4096 + 8
+    assert 0 < sizes[-1] <= total * weights[-1] / sum(weights)   # the last one takes what is left
