@@ -172,3 +172,32 @@ def test_whole_tensor_layout_invariants():
         assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:]))
         loads = [sum(p.numel for p in layout.owned(r)) for r in range(world)]
         assert sum(loads) == total and max(loads) - min(loads) <= max(workloads.numel(s) for s in shapes)
+
+
+def test_kernel_class_of_a_table_row():
+    """Which kernel a tensor gets is host logic of the library (no GPU): 1 = staged path with blocks that
+    take a whole warp (more than 1024 elements, or 17 to 32 chunks of eight), 2 = staged path with several blocks per warp pass, 0 / -1 =
+    generic warp / CTA per block (periods that are not multiples of 8, unaligned tensors, 4-bit codes,
+    period-1 tensors)."""
+    import numpy as np
+
+    from gefen_b200 import _lib
+
+    lib = _lib.load()
+
+    def cls(period, dtype=_lib.BF16, flags=0, p=0x10000, g=0x20000, codes=0x30000):
+        row = np.zeros(1, dtype=_lib.STEP_TENSOR_DTYPE)
+        row["p"], row["g"], row["codes"], row["mag"], row["v"] = p, g, codes, 0x40000, 0x50000
+        row["period"], row["num_blocks"], row["flags"] = period, 4, flags
+        return lib.gefen_b200_step_tensor_class(row.ctypes.data, dtype)
+
+    assert [cls(p) for p in (2048, 1032, 4096, 8192)] == [1, 1, 1, 1]
+    assert cls(256) == 1 and cls(248) == 1                   # 32 and 31 chunks: one per lane of a whole warp
+    assert [cls(p) for p in (8, 64, 128, 512, 768, 1024)] == [2, 2, 2, 2, 2, 2]
+    assert [cls(p, _lib.F32) for p in (768, 1536)] == [2, 1]
+    assert [cls(p) for p in (9, 12, 100, 2044)] == [0, 0, 0, 0]
+    assert cls(4100) == -1 and cls(8200) == -1               # long blocks off the staged path: a CTA per block
+    assert cls(2048, flags=_lib.STEP_PERIOD1) == 0
+    assert cls(2048, flags=_lib.STEP_PACKED) == 0
+    assert cls(2048, p=0x10008) == 0 and cls(2048, g=0x20002) == 0 and cls(2048, codes=0x30004) == 0
+    assert cls(2048, _lib.F64) == 0
