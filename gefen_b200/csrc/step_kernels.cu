@@ -316,14 +316,17 @@ __device__ __forceinline__ uint32_t lut_query_shared(float x, float magic) {
     return below + (x > __uint_as_float(thr_bits) ? 1u : 0u);
 }
 
-// Lanes that share one block, a power of two, so that a warp works on 32 / lanes blocks at once. Blocks of
-// up to 256 elements: the smallest power of two that covers the block's chunks (one chunk per lane). Longer
-// blocks: about eight chunks per lane, as in a 2048-element block, so that the per-block work (reductions,
-// step size, reciprocal, descriptor reads) is shared by as many elements: 8 lanes for 512 elements, 16 for
-// 1024, all 32 from 1032 elements on (measured on 512-element blocks: 0.43 ms -> 0.32 ms per 134 M elements).
+// Lanes that share one block, a power of two, so that a warp works on 32 / lanes blocks at once. A lane takes
+// several chunks of its block, which keeps as many loads in flight and shares the per-block work (reductions,
+// step size, reciprocal, descriptor reads) between more elements: about eight chunks per lane for blocks of
+// more than 256 elements, as in a 2048-element block (8 lanes for 512 elements, 16 for 1024, all 32 from 1032
+// elements on; measured on 512-element blocks: 0.43 ms -> 0.32 ms per 134 M elements), up to four for 136 to
+// 256 elements (8 lanes; 256-element bf16 blocks: 0.25 -> 0.50 of the copy bandwidth against one chunk per
+// lane), two below that (bf16, 128 / 64 / 32 elements: 0.23 -> 0.37 / 0.36 / 0.35; four per lane there puts the
+// staging slices of a warp's blocks on the same shared-memory banks and is slower for 2-byte elements).
 __host__ __device__ __forceinline__ int lanes_per_block(long long period) {
     const long long nchunks = period >> 3;
-    const long long want = nchunks > 32 ? (nchunks + 7) >> 3 : nchunks;
+    const long long want = nchunks > 32 ? (nchunks + 7) >> 3 : (nchunks > 16 ? (nchunks + 3) >> 2 : (nchunks + 1) >> 1);
     int lanes = 1;
     while (lanes < 32 && lanes < want) lanes <<= 1;
     return lanes;

@@ -176,7 +176,7 @@ def test_whole_tensor_layout_invariants():
 
 def test_kernel_class_of_a_table_row():
     """Which kernel a tensor gets is host logic of the library (no GPU): 1 = staged path with blocks that
-    take a whole warp (more than 1024 elements, or 17 to 32 chunks of eight), 2 = staged path with several blocks per warp pass, 0 / -1 =
+    take a whole warp (more than 1024 elements), 2 = staged path with several blocks per warp pass, 0 / -1 =
     generic warp / CTA per block (periods that are not multiples of 8, unaligned tensors, 4-bit codes,
     period-1 tensors)."""
     import numpy as np
@@ -192,8 +192,7 @@ def test_kernel_class_of_a_table_row():
         return lib.gefen_b200_step_tensor_class(row.ctypes.data, dtype)
 
     assert [cls(p) for p in (2048, 1032, 4096, 8192)] == [1, 1, 1, 1]
-    assert cls(256) == 1 and cls(248) == 1                   # 32 and 31 chunks: one per lane of a whole warp
-    assert [cls(p) for p in (8, 64, 128, 512, 768, 1024)] == [2, 2, 2, 2, 2, 2]
+    assert [cls(p) for p in (8, 64, 128, 248, 256, 512, 768, 1024)] == [2, 2, 2, 2, 2, 2, 2, 2]
     assert [cls(p, _lib.F32) for p in (768, 1536)] == [2, 1]
     assert [cls(p) for p in (9, 12, 100, 2044)] == [0, 0, 0, 0]
     assert cls(4100) == -1 and cls(8200) == -1               # long blocks off the staged path: a CTA per block
